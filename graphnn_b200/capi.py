@@ -1,0 +1,261 @@
+"""ctypes binding of libs2v_b200.so (the C ABI declared in include/s2v_b200.h).
+
+torch is used only to own device memory and streams; every computation goes through
+the shared library.  There is no fallback: if the library is missing, or no B200 is
+present, the calls raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libs2v_b200.so")
+
+_i32p = C.POINTER(C.c_int32)
+_i64p = C.POINTER(C.c_int64)
+_f32p = C.POINTER(C.c_float)
+
+
+class S2VError(RuntimeError):
+    def __init__(self, status: int, text: str):
+        super().__init__(f"s2v_b200 status {status}: {text}")
+        self.status = status
+
+
+class Model(C.Structure):
+    _fields_ = [("num_feat", C.c_int), ("d", C.c_int), ("levels", C.c_int), ("hidden", C.c_int),
+                ("num_class", C.c_int), ("w_n2l", C.c_void_p), ("p_node_conv", C.c_void_p),
+                ("h1_weight", C.c_void_p), ("h2_weight", C.c_void_p)]
+
+
+class Batch(C.Structure):
+    _fields_ = [("num_graphs", C.c_int64), ("num_nodes", C.c_int64), ("num_edges", C.c_int64),
+                ("n2n_row_ptr", C.c_void_p), ("n2n_col_idx", C.c_void_p), ("n2n_val", C.c_void_p),
+                ("graph_ptr", C.c_void_p), ("tags", C.c_void_p), ("x_dense", C.c_void_p)]
+
+
+_lib = None
+
+
+def load_library():
+    """Loads the shared library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise FileNotFoundError(f"{LIB_PATH} not found: build it with `python -m graphnn_b200.build`")
+    lib = C.CDLL(LIB_PATH)
+    vp, i64, i32, f32 = C.c_void_p, C.c_int64, C.c_int, C.c_float
+    sig = {
+        "s2v_ctx_create": (i32, [i32, C.POINTER(vp)]),
+        "s2v_ctx_destroy": (i32, [vp]),
+        "s2v_ctx_device": (i32, [vp]),
+        "s2v_ctx_stream": (vp, [vp]),
+        "s2v_ctx_synchronize": (i32, [vp]),
+        "s2v_status_str": (C.c_char_p, [i32]),
+        "s2v_last_error": (C.c_char_p, [vp]),
+        "s2v_launch_count": (C.c_uint64, [vp]),
+        "s2v_level_f32": (i32, [vp, vp, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp]),
+        "s2v_level_rp64_f32": (i32, [vp, vp, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp]),
+        "s2v_level_lookup_f32": (i32, [vp, vp, i64, i64, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp]),
+        "s2v_spmm_csr_f32": (i32, [vp, vp, i64, i64, i32, vp, vp, vp, vp, f32, f32, vp]),
+        "s2v_gemm_f32": (i32, [vp, vp, i32, i32, i64, i64, i64, f32, vp, i64, vp, i64, f32, vp, i64]),
+        "s2v_axpy_f32": (i32, [vp, vp, i64, f32, vp, vp]),
+        "s2v_scale_f32": (i32, [vp, vp, i64, f32, vp]),
+        "s2v_relu_f32": (i32, [vp, vp, i64, vp, vp]),
+        "s2v_softmax_f32": (i32, [vp, vp, i64, i32, vp, vp]),
+        "s2v_argmax_f32": (i32, [vp, vp, i64, i32, vp, vp]),
+        "s2v_segment_sum_f32": (i32, [vp, vp, i64, i32, vp, vp, vp]),
+        "s2v_readout_f32": (i32, [vp, vp, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp]),
+        "s2v_input_proj_onehot_f32": (i32, [vp, vp, i64, i32, i32, vp, vp, vp, vp]),
+        "s2v_input_proj_dense_f32": (i32, [vp, vp, i64, i32, i32, vp, vp, vp, vp]),
+        "s2v_forward_workspace_bytes": (C.c_size_t, [i64, i64, i32]),
+        "s2v_forward_f32": (i32, [vp, vp, C.POINTER(Model), C.POINTER(Batch), vp, C.c_size_t, vp, vp, vp, vp]),
+        "s2v_build_n2n_csr_host": (i32, [i64, i64, vp, vp, i32, vp, vp, vp]),
+        "s2v_validate_csr_host": (i32, [i64, i64, i64, vp, vp]),
+        "s2v_infer_host_f32": (i32, [vp, C.POINTER(Model), C.POINTER(Batch), vp, vp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    lib._s2v_signatures = sig
+    _lib = lib
+    return lib
+
+
+def exported_symbols() -> list[str]:
+    return sorted(load_library()._s2v_signatures)
+
+
+def _ptr(t):
+    """Device (torch) or host (numpy) address of an array, None -> NULL."""
+    if t is None:
+        return None
+    if isinstance(t, np.ndarray):
+        return t.ctypes.data
+    return t.data_ptr()
+
+
+def build_n2n_csr_host(num_nodes: int, edge_src: np.ndarray, edge_dst: np.ndarray, average: bool = False,
+                       with_val: bool = True):
+    """Host CSR of the node-to-node matrix, bit-identical to the reference's builder."""
+    lib = load_library()
+    E = int(edge_src.shape[0])
+    es = np.ascontiguousarray(edge_src, np.int32)
+    ed = np.ascontiguousarray(edge_dst, np.int32)
+    row_ptr = np.empty(num_nodes + 1, np.int32)
+    col_idx = np.empty(max(E, 1), np.int32)
+    val = np.empty(max(E, 1), np.float32) if with_val else None
+    rc = lib.s2v_build_n2n_csr_host(num_nodes, E, _ptr(es), _ptr(ed), int(average), _ptr(row_ptr), _ptr(col_idx),
+                                    _ptr(val))
+    if rc != 0:
+        raise S2VError(rc, lib.s2v_status_str(rc).decode())
+    return row_ptr, col_idx[:E], (val[:E] if with_val else None)
+
+
+def validate_csr_host(m: int, k: int, row_ptr: np.ndarray, col_idx: np.ndarray) -> int:
+    lib = load_library()
+    rp = np.ascontiguousarray(row_ptr, np.int32)
+    ci = np.ascontiguousarray(col_idx, np.int32)
+    return lib.s2v_validate_csr_host(m, k, int(ci.shape[0]), _ptr(rp), _ptr(ci))
+
+
+class Context:
+    """One s2v_ctx: a device, its stream and the library's launch counter."""
+
+    def __init__(self, device: int = 0):
+        self.lib = load_library()
+        h = C.c_void_p()
+        rc = self.lib.s2v_ctx_create(int(device), C.byref(h))
+        if rc != 0:
+            raise S2VError(rc, self.lib.s2v_status_str(rc).decode())
+        self.h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.s2v_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- helpers
+    def check(self, rc: int):
+        if rc != 0:
+            raise S2VError(rc, f"{self.lib.s2v_status_str(rc).decode()}: {self.lib.s2v_last_error(self.h).decode()}")
+
+    def call(self, name: str, *args):
+        rc = getattr(self.lib, name)(self.h, *args)
+        self.check(rc)
+
+    @property
+    def stream(self) -> int:
+        return self.lib.s2v_ctx_stream(self.h)
+
+    def synchronize(self):
+        self.check(self.lib.s2v_ctx_synchronize(self.h))
+
+    @property
+    def launches(self) -> int:
+        return int(self.lib.s2v_launch_count(self.h))
+
+    # -- operators (device tensors in, device tensors out; `stream` = raw cudaStream_t or None)
+    def level(self, row_ptr, col_idx, val, H, W, X, out, n_src=None, stream=None):
+        n_rows, d = out.shape
+        n_src = H.shape[0] if n_src is None else n_src
+        name = "s2v_level_rp64_f32" if row_ptr.element_size() == 8 else "s2v_level_f32"
+        self.call(name, stream, n_rows, n_src, d, _ptr(row_ptr), _ptr(col_idx), _ptr(val), _ptr(H), _ptr(W), _ptr(X),
+                  _ptr(out))
+        return out
+
+    def level_lookup(self, row_ptr, col_idx, val, H, W, table, x_index, out, stream=None):
+        n_rows, d = out.shape
+        self.call("s2v_level_lookup_f32", stream, n_rows, H.shape[0], d, _ptr(row_ptr), _ptr(col_idx), _ptr(val),
+                  _ptr(H), _ptr(W), _ptr(table), table.shape[0], _ptr(x_index), _ptr(out))
+        return out
+
+    def spmm(self, m, k, row_ptr, col_idx, val, B, C_out, alpha=1.0, beta=0.0, stream=None):
+        self.call("s2v_spmm_csr_f32", stream, m, k, B.shape[1], _ptr(row_ptr), _ptr(col_idx), _ptr(val), _ptr(B),
+                  alpha, beta, _ptr(C_out))
+        return C_out
+
+    def gemm(self, A, B, C_out, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, stream=None):
+        m = A.shape[1] if trans_a else A.shape[0]
+        k = A.shape[0] if trans_a else A.shape[1]
+        n = B.shape[0] if trans_b else B.shape[1]
+        self.call("s2v_gemm_f32", stream, int(trans_a), int(trans_b), m, n, k, alpha, _ptr(A), A.shape[1], _ptr(B),
+                  B.shape[1], beta, _ptr(C_out), C_out.shape[1])
+        return C_out
+
+    def axpy(self, a, x, y, stream=None):
+        self.call("s2v_axpy_f32", stream, x.numel(), a, _ptr(x), _ptr(y))
+        return y
+
+    def scale(self, a, x, stream=None):
+        self.call("s2v_scale_f32", stream, x.numel(), a, _ptr(x))
+        return x
+
+    def relu(self, x, out, stream=None):
+        self.call("s2v_relu_f32", stream, x.numel(), _ptr(x), _ptr(out))
+        return out
+
+    def softmax(self, x, out, stream=None):
+        self.call("s2v_softmax_f32", stream, x.shape[0], x.shape[1], _ptr(x), _ptr(out))
+        return out
+
+    def argmax(self, x, out, stream=None):
+        self.call("s2v_argmax_f32", stream, x.shape[0], x.shape[1], _ptr(x), _ptr(out))
+        return out
+
+    def segment_sum(self, seg_ptr, H, Y, stream=None):
+        self.call("s2v_segment_sum_f32", stream, Y.shape[0], H.shape[1], _ptr(seg_ptr), _ptr(H), _ptr(Y))
+        return Y
+
+    def readout(self, Y, W1, W2, logits, probs=None, pred=None, stream=None):
+        self.call("s2v_readout_f32", stream, Y.shape[0], Y.shape[1], W1.shape[1], W2.shape[1], _ptr(Y), _ptr(W1),
+                  _ptr(W2), _ptr(logits), _ptr(probs), _ptr(pred))
+        return logits
+
+    def input_proj_onehot(self, tags, W_in, msg, h0, stream=None):
+        self.call("s2v_input_proj_onehot_f32", stream, tags.shape[0], W_in.shape[0], W_in.shape[1], _ptr(tags),
+                  _ptr(W_in), _ptr(msg), _ptr(h0))
+
+    def input_proj_dense(self, X, W_in, msg, h0, stream=None):
+        self.call("s2v_input_proj_dense_f32", stream, X.shape[0], X.shape[1], W_in.shape[1], _ptr(X), _ptr(W_in),
+                  _ptr(msg), _ptr(h0))
+
+    # -- whole model
+    @staticmethod
+    def make_model(levels: int, w_n2l, p_node_conv, h1_weight, h2_weight) -> Model:
+        """`w_*` are DEVICE tensors (kept alive by the caller)."""
+        return Model(w_n2l.shape[0], w_n2l.shape[1], levels, h1_weight.shape[1], h2_weight.shape[1],
+                     _ptr(w_n2l), _ptr(p_node_conv), _ptr(h1_weight), _ptr(h2_weight))
+
+    @staticmethod
+    def make_batch(num_graphs, num_nodes, row_ptr, col_idx, val, graph_ptr, tags=None, x_dense=None) -> Batch:
+        """Arrays are torch device tensors (device entry) or numpy arrays (host entry)."""
+        return Batch(num_graphs, num_nodes, int(col_idx.shape[0]), _ptr(row_ptr), _ptr(col_idx), _ptr(val),
+                     _ptr(graph_ptr), _ptr(tags), _ptr(x_dense))
+
+    def workspace_bytes(self, num_nodes, num_graphs, d) -> int:
+        return int(self.lib.s2v_forward_workspace_bytes(num_nodes, num_graphs, d))
+
+    def forward(self, model: Model, batch: Batch, workspace, logits, probs=None, pred=None, embed_out=None,
+                stream=None):
+        self.call("s2v_forward_f32", stream, C.byref(model), C.byref(batch), _ptr(workspace),
+                  workspace.numel() * workspace.element_size(), _ptr(logits), _ptr(probs), _ptr(pred),
+                  _ptr(embed_out))
+
+    def infer_host(self, model: Model, batch_host: Batch, logits_host: np.ndarray | None,
+                   pred_host: np.ndarray | None):
+        rc = self.lib.s2v_infer_host_f32(self.h, C.byref(model), C.byref(batch_host), _ptr(logits_host),
+                                         _ptr(pred_host))
+        self.check(rc)

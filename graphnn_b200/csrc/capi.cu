@@ -1,0 +1,382 @@
+// C ABI glue of s2v_b200: context life cycle, argument validation, the whole-model
+// pipelines (device buffers and host buffers) and the host-side CSR builders.
+#include <algorithm>
+#include <cstring>
+#include <new>
+#include <thread>
+#include <vector>
+
+#include "common.cuh"
+
+namespace
+{
+
+const char* status_text(int s)
+{
+    switch (s) {
+        case S2V_OK: return "ok";
+        case S2V_ERR_INVALID_ARG: return "invalid argument";
+        case S2V_ERR_UNSUPPORTED: return "unsupported shape";
+        case S2V_ERR_CUDA: return "CUDA runtime error";
+        case S2V_ERR_BAD_CSR: return "malformed CSR matrix";
+        case S2V_ERR_WORKSPACE: return "workspace too small";
+        case S2V_ERR_NO_DEVICE: return "no CUDA device";
+        case S2V_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+        default: return "unknown status";
+    }
+}
+
+inline size_t align_up(size_t v, size_t a)
+{
+    return (v + a - 1) / a * a;
+}
+
+int check_level_args(s2v_ctx* ctx, int64_t n_rows, int64_t n_src, int d, const void* row_ptr, const int32_t* col_idx,
+                     const float* H, const float* W, const float* X, const float* out)
+{
+    if (n_rows < 0 || n_src < 0 || d <= 0) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level: negative size");
+    if (n_rows == 0) return S2V_OK;
+    if (!row_ptr || !W || !out) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level: NULL pointer");
+    if (n_src > 0 && (!H || !col_idx)) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level: NULL H or col_idx");
+    if (d != 32 && d != 64 && d != 128)
+        return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "fused level kernel supports d in {32, 64, 128}");
+    if (!s2v_aligned16(H) || !s2v_aligned16(W) || !s2v_aligned16(X) || !s2v_aligned16(out))
+        return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level: H, W, X, out must be 16-byte aligned");
+    if (out == H) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level: out must not alias H");
+    return S2V_OK;
+}
+
+int ensure_staging(s2v_ctx* ctx, size_t dev_bytes, size_t pinned_bytes)
+{
+    s2v_staging& s = ctx->staging;
+    if (dev_bytes > s.dev_bytes) {
+        if (s.dev) cudaFree(s.dev);
+        s.dev = nullptr;
+        s.dev_bytes = 0;
+        const size_t want = align_up(dev_bytes + dev_bytes / 4, 1 << 20);
+        S2V_CUDA_OK(ctx, cudaMalloc(&s.dev, want));
+        s.dev_bytes = want;
+    }
+    if (pinned_bytes > s.pinned_bytes) {
+        if (s.pinned) cudaFreeHost(s.pinned);
+        s.pinned = nullptr;
+        s.pinned_bytes = 0;
+        const size_t want = align_up(pinned_bytes + pinned_bytes / 4, 1 << 16);
+        S2V_CUDA_OK(ctx, cudaMallocHost(&s.pinned, want));
+        s.pinned_bytes = want;
+    }
+    return S2V_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* s2v_status_str(int status)
+{
+    return status_text(status);
+}
+
+int s2v_ctx_create(int device, s2v_ctx** out)
+{
+    if (!out) return S2V_ERR_INVALID_ARG;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return S2V_ERR_NO_DEVICE;
+    }
+    if (device < 0 || device >= count) return S2V_ERR_INVALID_ARG;
+    s2v_ctx* ctx = new (std::nothrow) s2v_ctx();
+    if (!ctx) return S2V_ERR_CUDA;
+    ctx->device = device;
+    s2v_device_guard guard(device);
+    cudaDeviceProp prop;
+    if (!guard.ok || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+        delete ctx;
+        return S2V_ERR_CUDA;
+    }
+    if (prop.major != 10) {  // the kernels are built for sm_100a only
+        delete ctx;
+        return S2V_ERR_NO_DEVICE;
+    }
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->smem_optin = prop.sharedMemPerBlockOptin;
+    bool ok = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaEventCreateWithFlags(&ctx->ev_upload, cudaEventDisableTiming) == cudaSuccess &&
+              cudaHostAlloc((void**)&ctx->dstatus_host, sizeof(s2v_device_status), cudaHostAllocMapped) == cudaSuccess &&
+              cudaHostGetDevicePointer((void**)&ctx->dstatus_dev, ctx->dstatus_host, 0) == cudaSuccess;
+    if (!ok) {
+        s2v_ctx_destroy(ctx);
+        return S2V_ERR_CUDA;
+    }
+    ctx->dstatus_host->code = 0;
+    ctx->dstatus_host->where = 0;
+    *out = ctx;
+    return S2V_OK;
+}
+
+int s2v_ctx_destroy(s2v_ctx* ctx)
+{
+    if (!ctx) return S2V_OK;
+    {
+        s2v_device_guard guard(ctx->device);
+        if (ctx->stream) { cudaStreamSynchronize(ctx->stream); cudaStreamDestroy(ctx->stream); }
+        if (ctx->copy_stream) { cudaStreamSynchronize(ctx->copy_stream); cudaStreamDestroy(ctx->copy_stream); }
+        if (ctx->ev_upload) cudaEventDestroy(ctx->ev_upload);
+        if (ctx->dstatus_host) cudaFreeHost(ctx->dstatus_host);
+        if (ctx->staging.dev) cudaFree(ctx->staging.dev);
+        if (ctx->staging.pinned) cudaFreeHost(ctx->staging.pinned);
+    }
+    delete ctx;
+    return S2V_OK;
+}
+
+int s2v_ctx_device(const s2v_ctx* ctx)
+{
+    return ctx ? ctx->device : S2V_ERR_INVALID_ARG;
+}
+
+s2v_stream s2v_ctx_stream(const s2v_ctx* ctx)
+{
+    return ctx ? static_cast<s2v_stream>(ctx->stream) : nullptr;
+}
+
+int s2v_ctx_synchronize(s2v_ctx* ctx)
+{
+    S2V_ENTER(ctx);
+    S2V_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->dstatus_host->code != 0) {
+        const int code = ctx->dstatus_host->code, where = ctx->dstatus_host->where;
+        ctx->dstatus_host->code = 0;
+        ctx->dstatus_host->where = 0;
+        return s2v_fail(ctx, code, "a kernel reported status " + std::to_string(code) + " at site " + std::to_string(where));
+    }
+    return S2V_OK;
+}
+
+const char* s2v_last_error(const s2v_ctx* ctx)
+{
+    return ctx ? ctx->last_error.c_str() : "no context";
+}
+
+uint64_t s2v_launch_count(const s2v_ctx* ctx)
+{
+    return ctx ? ctx->launches.load() : 0;
+}
+
+// ---------------------------------------------------------------- fused level
+int s2v_level_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_t n_src, int d, const int32_t* row_ptr,
+                  const int32_t* col_idx, const float* val, const float* H, const float* W, const float* X,
+                  float* out)
+{
+    S2V_ENTER(ctx);
+    int rc = check_level_args(ctx, n_rows, n_src, d, row_ptr, col_idx, H, W, X, out);
+    if (rc != S2V_OK || n_rows == 0) return rc;
+    return s2v_launch_level(ctx, s2v_pick_stream(ctx, stream), n_rows, n_src, d, row_ptr, false, col_idx, val, H, W, X,
+                            nullptr, nullptr, out);
+}
+
+int s2v_level_rp64_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_t n_src, int d, const int64_t* row_ptr,
+                       const int32_t* col_idx, const float* val, const float* H, const float* W, const float* X,
+                       float* out)
+{
+    S2V_ENTER(ctx);
+    int rc = check_level_args(ctx, n_rows, n_src, d, row_ptr, col_idx, H, W, X, out);
+    if (rc != S2V_OK || n_rows == 0) return rc;
+    return s2v_launch_level(ctx, s2v_pick_stream(ctx, stream), n_rows, n_src, d, row_ptr, true, col_idx, val, H, W, X,
+                            nullptr, nullptr, out);
+}
+
+int s2v_level_lookup_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_t n_src, int d,
+                         const int32_t* row_ptr, const int32_t* col_idx, const float* val, const float* H,
+                         const float* W, const float* table, int n_table, const int32_t* x_index, float* out)
+{
+    S2V_ENTER(ctx);
+    int rc = check_level_args(ctx, n_rows, n_src, d, row_ptr, col_idx, H, W, table, out);
+    if (rc != S2V_OK || n_rows == 0) return rc;
+    if (!table || !x_index || n_table <= 0) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level_lookup: NULL table or index");
+    return s2v_launch_level(ctx, s2v_pick_stream(ctx, stream), n_rows, n_src, d, row_ptr, false, col_idx, val, H, W,
+                            nullptr, table, x_index, out);
+}
+
+// ---------------------------------------------------------------- whole model, device buffers
+size_t s2v_forward_workspace_bytes(int64_t num_nodes, int64_t num_graphs, int d)
+{
+    if (num_nodes < 0 || num_graphs < 0 || d <= 0) return 0;
+    const size_t nd = align_up(sizeof(float) * (size_t)num_nodes * d, 256);
+    const size_t gd = align_up(sizeof(float) * (size_t)num_graphs * d, 256);
+    return 3 * nd + gd + 256;
+}
+
+int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, const s2v_batch* batch, void* workspace,
+                    size_t workspace_bytes, float* logits, float* probs, int32_t* pred, float* embed_out)
+{
+    S2V_ENTER(ctx);
+    if (!model || !batch) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "forward: NULL model or batch");
+    const int64_t N = batch->num_nodes, G = batch->num_graphs;
+    const int d = model->d, L = model->levels;
+    if (N < 0 || G < 0 || L < 0 || d <= 0 || model->hidden <= 0 || model->num_class <= 0 || model->num_feat <= 0)
+        return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "forward: bad shape");
+    if (!model->w_n2l || !model->p_node_conv || !model->h1_weight || !model->h2_weight)
+        return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "forward: NULL weight");
+    if (G == 0) return S2V_OK;
+    if (!logits || !batch->graph_ptr || (!batch->tags && !batch->x_dense) || (N > 0 && !batch->n2n_row_ptr))
+        return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "forward: NULL batch array or output");
+    if (workspace_bytes < s2v_forward_workspace_bytes(N, G, d) || !workspace)
+        return s2v_fail(ctx, S2V_ERR_WORKSPACE, "forward: workspace smaller than s2v_forward_workspace_bytes");
+    cudaStream_t st = s2v_pick_stream(ctx, stream);
+
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    ws = reinterpret_cast<unsigned char*>(align_up(reinterpret_cast<uintptr_t>(ws), 256));
+    const size_t nd = align_up(sizeof(float) * (size_t)N * d, 256);
+    float* msg = reinterpret_cast<float*>(ws);
+    float* ha = reinterpret_cast<float*>(ws + nd);
+    float* hb = reinterpret_cast<float*>(ws + 2 * nd);
+    float* y = reinterpret_cast<float*>(ws + 3 * nd);
+
+    int rc;
+    // With one-hot tags the X term of every level is a lookup in W_in, so `msg` is
+    // never materialised; a dense X needs it.
+    const bool onehot = batch->tags != nullptr && d % 4 == 0;
+    if (onehot)
+        rc = s2v_input_proj_onehot_f32(ctx, st, N, model->num_feat, d, batch->tags, model->w_n2l, nullptr, ha);
+    else if (batch->tags)
+        return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "forward: one-hot input needs d % 4 == 0");
+    else
+        rc = s2v_input_proj_dense_f32(ctx, st, N, model->num_feat, d, batch->x_dense, model->w_n2l, msg, ha);
+    if (rc != S2V_OK) return rc;
+
+    float* cur = ha;
+    float* nxt = hb;
+    for (int lv = 0; lv < L; ++lv) {
+        float* dst = (lv == L - 1 && embed_out) ? embed_out : nxt;
+        if (onehot)
+            rc = s2v_level_lookup_f32(ctx, st, N, N, d, batch->n2n_row_ptr, batch->n2n_col_idx, batch->n2n_val, cur,
+                                      model->p_node_conv, model->w_n2l, model->num_feat, batch->tags, dst);
+        else
+            rc = s2v_level_f32(ctx, st, N, N, d, batch->n2n_row_ptr, batch->n2n_col_idx, batch->n2n_val, cur,
+                               model->p_node_conv, msg, dst);
+        if (rc != S2V_OK) return rc;
+        if (dst == nxt) std::swap(cur, nxt); else cur = dst;
+    }
+    if (L == 0 && embed_out)
+        S2V_CUDA_OK(ctx, cudaMemcpyAsync(embed_out, cur, sizeof(float) * (size_t)N * d, cudaMemcpyDeviceToDevice, st));
+    rc = s2v_segment_sum_f32(ctx, st, G, d, batch->graph_ptr, cur, y);
+    if (rc != S2V_OK) return rc;
+    return s2v_readout_f32(ctx, st, G, d, model->hidden, model->num_class, y, model->h1_weight, model->h2_weight, logits,
+                           probs, pred);
+}
+
+// ---------------------------------------------------------------- host-side CSR
+int s2v_build_n2n_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* edge_src, const int32_t* edge_dst,
+                           int average, int32_t* row_ptr, int32_t* col_idx, float* val)
+{
+    if (num_nodes < 0 || num_edges < 0 || !row_ptr) return S2V_ERR_INVALID_ARG;
+    if (num_edges > 0 && (!edge_src || !edge_dst || !col_idx)) return S2V_ERR_INVALID_ARG;
+    if (num_edges >= (int64_t)INT32_MAX || num_nodes >= (int64_t)INT32_MAX) return S2V_ERR_UNSUPPORTED;
+    // Stable counting sort by destination: row y receives its sources in edge order,
+    // which is the order GraphStruct::AddEdge appended them to in_edges[y].
+    std::vector<int32_t> fill((size_t)num_nodes + 1, 0);
+    for (int64_t e = 0; e < num_edges; ++e) {
+        const int32_t y = edge_dst[e], x = edge_src[e];
+        if (y < 0 || y >= num_nodes || x < 0 || x >= num_nodes) return S2V_ERR_BAD_CSR;
+        fill[(size_t)y + 1]++;
+    }
+    for (int64_t i = 0; i < num_nodes; ++i) fill[i + 1] += fill[i];
+    std::memcpy(row_ptr, fill.data(), sizeof(int32_t) * ((size_t)num_nodes + 1));
+    for (int64_t e = 0; e < num_edges; ++e) col_idx[fill[edge_dst[e]]++] = edge_src[e];
+    if (val) {
+        for (int64_t i = 0; i < num_nodes; ++i) {
+            const int32_t deg = row_ptr[i + 1] - row_ptr[i];
+            const float v = average ? (float)(1.0 / deg) : 1.0f;
+            for (int32_t t = row_ptr[i]; t < row_ptr[i + 1]; ++t) val[t] = v;
+        }
+    }
+    return S2V_OK;
+}
+
+int s2v_validate_csr_host(int64_t m, int64_t k, int64_t nnz, const int32_t* row_ptr, const int32_t* col_idx)
+{
+    if (m < 0 || k < 0 || nnz < 0 || !row_ptr || (nnz > 0 && !col_idx)) return S2V_ERR_INVALID_ARG;
+    if (row_ptr[0] != 0 || row_ptr[m] != nnz) return S2V_ERR_BAD_CSR;
+    for (int64_t i = 0; i < m; ++i)
+        if (row_ptr[i + 1] < row_ptr[i]) return S2V_ERR_BAD_CSR;
+    for (int64_t t = 0; t < nnz; ++t)
+        if (col_idx[t] < 0 || col_idx[t] >= k) return S2V_ERR_BAD_CSR;
+    return S2V_OK;
+}
+
+// ---------------------------------------------------------------- whole model, host buffers
+int s2v_infer_host_f32(s2v_ctx* ctx, const s2v_model* model, const s2v_batch* hb, float* logits_host,
+                       int32_t* pred_host)
+{
+    S2V_ENTER(ctx);
+    if (!model || !hb) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_host: NULL model or batch");
+    const int64_t N = hb->num_nodes, G = hb->num_graphs, E = hb->num_edges;
+    const int d = model->d, C = model->num_class, F = model->num_feat;
+    if (N < 0 || G < 0 || E < 0 || d <= 0 || C <= 0 || F <= 0)
+        return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_host: bad shape");
+    if (G == 0) return S2V_OK;
+    if (!hb->graph_ptr || !hb->n2n_row_ptr || (E > 0 && !hb->n2n_col_idx) || (!hb->tags && !hb->x_dense))
+        return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_host: NULL batch array");
+    // cheap structural check on the host (full validation is s2v_validate_csr_host)
+    if (hb->n2n_row_ptr[0] != 0 || hb->n2n_row_ptr[N] != E || hb->graph_ptr[0] != 0 || hb->graph_ptr[G] != N)
+        return s2v_fail(ctx, S2V_ERR_BAD_CSR, "infer_host: row_ptr / graph_ptr ends do not match the sizes");
+
+    // device layout: [row_ptr | col_idx | val? | graph_ptr | tags or X | logits | pred | workspace]
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
+    const size_t o_rp = take(sizeof(int32_t) * (size_t)(N + 1));
+    const size_t o_ci = take(sizeof(int32_t) * (size_t)E);
+    const size_t o_val = hb->n2n_val ? take(sizeof(float) * (size_t)E) : 0;
+    const size_t o_gp = take(sizeof(int32_t) * (size_t)(G + 1));
+    const size_t o_in = hb->tags ? take(sizeof(int32_t) * (size_t)N) : take(sizeof(float) * (size_t)N * F);
+    const size_t o_logits = take(sizeof(float) * (size_t)G * C);
+    const size_t o_pred = take(sizeof(int32_t) * (size_t)G);
+    const size_t ws_bytes = s2v_forward_workspace_bytes(N, G, d);
+    const size_t o_ws = take(ws_bytes);
+    int rc = ensure_staging(ctx, off, sizeof(float) * (size_t)G * C + sizeof(int32_t) * (size_t)G + 512);
+    if (rc != S2V_OK) return rc;
+    unsigned char* dev = static_cast<unsigned char*>(ctx->staging.dev);
+    cudaStream_t st = ctx->stream;
+
+    S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_rp, hb->n2n_row_ptr, sizeof(int32_t) * (size_t)(N + 1), cudaMemcpyHostToDevice, st));
+    if (E > 0)
+        S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_ci, hb->n2n_col_idx, sizeof(int32_t) * (size_t)E, cudaMemcpyHostToDevice, st));
+    if (hb->n2n_val && E > 0)
+        S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_val, hb->n2n_val, sizeof(float) * (size_t)E, cudaMemcpyHostToDevice, st));
+    S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_gp, hb->graph_ptr, sizeof(int32_t) * (size_t)(G + 1), cudaMemcpyHostToDevice, st));
+    if (hb->tags)
+        S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_in, hb->tags, sizeof(int32_t) * (size_t)N, cudaMemcpyHostToDevice, st));
+    else
+        S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_in, hb->x_dense, sizeof(float) * (size_t)N * F, cudaMemcpyHostToDevice, st));
+
+    s2v_batch db = *hb;
+    db.n2n_row_ptr = reinterpret_cast<const int32_t*>(dev + o_rp);
+    db.n2n_col_idx = reinterpret_cast<const int32_t*>(dev + o_ci);
+    db.n2n_val = hb->n2n_val ? reinterpret_cast<const float*>(dev + o_val) : nullptr;
+    db.graph_ptr = reinterpret_cast<const int32_t*>(dev + o_gp);
+    db.tags = hb->tags ? reinterpret_cast<const int32_t*>(dev + o_in) : nullptr;
+    db.x_dense = hb->tags ? nullptr : reinterpret_cast<const float*>(dev + o_in);
+    float* d_logits = reinterpret_cast<float*>(dev + o_logits);
+    int32_t* d_pred = reinterpret_cast<int32_t*>(dev + o_pred);
+    rc = s2v_forward_f32(ctx, st, model, &db, dev + o_ws, ws_bytes, d_logits, nullptr, d_pred, nullptr);
+    if (rc != S2V_OK) return rc;
+
+    float* p_logits = static_cast<float*>(ctx->staging.pinned);
+    int32_t* p_pred = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(ctx->staging.pinned) +
+                                                 align_up(sizeof(float) * (size_t)G * C, 256));
+    if (logits_host)
+        S2V_CUDA_OK(ctx, cudaMemcpyAsync(p_logits, d_logits, sizeof(float) * (size_t)G * C, cudaMemcpyDeviceToHost, st));
+    if (pred_host)
+        S2V_CUDA_OK(ctx, cudaMemcpyAsync(p_pred, d_pred, sizeof(int32_t) * (size_t)G, cudaMemcpyDeviceToHost, st));
+    rc = s2v_ctx_synchronize(ctx);
+    if (rc != S2V_OK) return rc;
+    if (logits_host) std::memcpy(logits_host, p_logits, sizeof(float) * (size_t)G * C);
+    if (pred_host) std::memcpy(pred_host, p_pred, sizeof(int32_t) * (size_t)G);
+    return S2V_OK;
+}
+
+}  // extern "C"

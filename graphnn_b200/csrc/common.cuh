@@ -1,0 +1,132 @@
+// Shared declarations of the s2v_b200 library: context object, status plumbing,
+// small device helpers.  Everything here targets sm_100a only.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <cstdio>
+#include <mutex>
+#include <string>
+
+#include "s2v_b200.h"
+
+// Device-side status word (mapped, host-visible) written by kernels whose bounded
+// waits give up.  0 = fine.
+struct s2v_device_status {
+    int code;
+    int where;
+};
+
+struct s2v_staging {  // grow-only buffers owned by a context (host-buffer entry point)
+    void* dev = nullptr;
+    size_t dev_bytes = 0;
+    void* pinned = nullptr;
+    size_t pinned_bytes = 0;
+};
+
+struct s2v_ctx {
+    int device = 0;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    cudaStream_t stream = nullptr;       // the context's own non-blocking stream
+    cudaStream_t copy_stream = nullptr;  // uploads of the host-buffer entry point
+    cudaEvent_t ev_upload = nullptr;
+    s2v_device_status* dstatus_host = nullptr;  // pinned + mapped
+    s2v_device_status* dstatus_dev = nullptr;
+    std::atomic<uint64_t> launches{0};
+    std::string last_error;
+    std::mutex mu;
+    s2v_staging staging;
+    bool level_attr_set[8] = {false, false, false, false, false, false, false, false};
+};
+
+inline int s2v_fail(s2v_ctx* ctx, int status, const std::string& msg)
+{
+    if (ctx) {
+        std::lock_guard<std::mutex> g(ctx->mu);
+        ctx->last_error = msg;
+    }
+    return status;
+}
+
+#define S2V_CUDA_OK(ctx, expr)                                                                         \
+    do {                                                                                               \
+        cudaError_t e__ = (expr);                                                                      \
+        if (e__ != cudaSuccess)                                                                        \
+            return s2v_fail((ctx), S2V_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e__)); \
+    } while (0)
+
+inline bool s2v_aligned16(const void* p)
+{
+    return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+inline cudaStream_t s2v_pick_stream(s2v_ctx* ctx, s2v_stream s)
+{
+    return s ? static_cast<cudaStream_t>(s) : ctx->stream;
+}
+
+// RAII device switch: every entry point runs with the context's device current and
+// restores the caller's device on return.
+struct s2v_device_guard {
+    int prev = -1;
+    bool ok = true;
+    explicit s2v_device_guard(int dev)
+    {
+        if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+        if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+    }
+    ~s2v_device_guard()
+    {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+#define S2V_ENTER(ctx)                                                                   \
+    if (!(ctx)) return S2V_ERR_INVALID_ARG;                                              \
+    s2v_device_guard guard__((ctx)->device);                                             \
+    if (!guard__.ok) return s2v_fail((ctx), S2V_ERR_CUDA, "cannot select the context's device")
+
+#define S2V_CHECK_LAUNCH(ctx, name)                                                                        \
+    do {                                                                                                   \
+        cudaError_t e__ = cudaGetLastError();                                                              \
+        if (e__ != cudaSuccess)                                                                            \
+            return s2v_fail((ctx), S2V_ERR_CUDA, std::string("launch of ") + name + ": " + cudaGetErrorString(e__)); \
+        (ctx)->launches.fetch_add(1, std::memory_order_relaxed);                                           \
+    } while (0)
+
+// ---------------------------------------------------------------- device helpers
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float4 ld_nc_f4(const float4* p)
+{
+    return __ldg(p);
+}
+// streaming (evict-first) accesses for data touched once per launch
+__device__ __forceinline__ float4 ld_stream_f4(const float4* p)
+{
+    return __ldcs(p);
+}
+__device__ __forceinline__ void st_stream_f4(float4* p, float4 v)
+{
+    __stcs(p, v);
+}
+__device__ __forceinline__ float relu_ref(float v)
+{
+    // `if (x < 0) x = 0`: keeps -0.0 and NaN like the reference functor
+    return v < 0.0f ? 0.0f : v;
+}
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+#endif  // __CUDACC__
+
+// launchers implemented in the .cu files (host side)
+int s2v_launch_level(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int64_t n_src, int d, const void* row_ptr,
+                     bool rp64, const int32_t* col_idx, const float* val, const float* H, const float* W,
+                     const float* X, const float* table, const int32_t* x_index, float* out);
