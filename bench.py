@@ -1,0 +1,375 @@
+"""Benchmark of the s2v mean-field inference path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload molecules|proteins]
+
+A step is one inference pass (input projection, L fused levels, pooling, readout, logits
+gather) over one batch of synthetic graphs that is already resident in HBM.  Default
+workload: the batched molecule-like configuration (16,384 graphs per GPU, latent 128,
+4 levels), sharded by graph: every rank owns its own 16,384-graph shard of a
+16,384 x N-graph job (weak scaling) and the only collective is the final gather of
+the logits.  Rank 0 prints ONE JSON line.
+
+`value` is graphs/s over all ranks with inputs on the device; `e2e` is the same metric
+through the host-buffer entry point (edge list -> CSR on the host, upload, forward,
+download) ; `roofline` describes the fused level kernel inside the timed region;
+`level_cfg2` is the single fused level on the 1M-node / 8M-edge Erdos-Renyi problem;
+`cpu_baseline` is the reference's own CPU code on this machine's cores.
+
+`--impl reference` times the reference's CPU implementation (oracle/_ref, MKL replaced
+by plain OpenMP loops) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+if REPO not in sys.path:
+    sys.path.insert(0, REPO)
+
+from graphnn_b200 import synth  # noqa: E402
+
+WEIGHT_SEED = 20240
+METRIC = "s2v_inference_graphs_per_sec"
+
+
+def make_workload(name: str, seed: int):
+    if name == "molecules":
+        return synth.molecules_16k(seed=seed, weight_seed=WEIGHT_SEED)
+    if name == "proteins":
+        return synth.proteins_4k(seed=seed, weight_seed=WEIGHT_SEED)
+    raise SystemExit(f"unknown workload {name}")
+
+
+def measured_peaks():
+    p = os.path.join(REPO, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [x.strip() for x in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(float(s[0]) for s in self.samples)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower() == "active" for s in self.samples)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(self.samples[0][1]), "reasons": reasons,
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ byte models
+def level_bytes(n_rows, nnz, d, model: str, x_form: str) -> int:
+    """Algorithmic bytes of one fused level.  `gather`: every neighbour row fetched once
+    per edge; `compulsory`: every H row fetched once.  x_form: dense (X read as
+    [N x d]), lookup (tags + table) or none."""
+    b_csr = 4 * (n_rows + 1) + 4 * nnz          # val == NULL form: no value array
+    b_h = 4 * nnz * d if model == "gather" else 4 * n_rows * d
+    b_x = {"dense": 4 * n_rows * d, "lookup": 4 * n_rows, "none": 0}[x_form]
+    return b_csr + b_h + b_x + 4 * n_rows * d + 4 * d * d
+
+
+# ------------------------------------------------------------------ reference arm
+def run_reference(args, rank: int, world: int):
+    if rank != 0:
+        return
+    from oracle import bindings as ob
+    kind = "reference" if ob.have_reference() else "port"
+    impl = "reference" if kind == "reference" else "oracle"
+    cores = os.cpu_count() or 1
+    ob.set_threads(cores, impl)
+    sample_graphs = 4096 if args.workload == "molecules" else 512
+    full = make_workload(args.workload, 0)
+    lo, hi = 0, sample_graphs
+    off = full.graph_offsets().astype(np.int64)
+    sel = full.edge_src < off[hi]
+    sample = synth.GraphBatch(full.nodes_per_graph[lo:hi].copy(), full.edge_src[sel].copy(), full.edge_dst[sel].copy(),
+                              full.tags[: off[hi]].copy(), full.num_tags, full.d, full.levels, full.hidden,
+                              full.num_class, full.weights, full.name + f"[first {sample_graphs}]")
+    iters = args.warmup + args.steps
+    out = ob.forward(sample, impl, iters=iters, want_levels=False)
+    secs = np.asarray(out["seconds"][args.warmup:])
+    total = float(secs.sum())
+    value = sample.num_graphs * len(secs) / total
+    line = {
+        "metric": METRIC, "value": value, "unit": "graphs/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total / len(secs), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
+        "config": {"workload": f"{args.workload}: 16,384 molecule-like graphs per GPU, d=128, L=4, hidden=256"
+                   if args.workload == "molecules" else "proteins: 4,096 protein-like graphs per GPU, d=64, L=5",
+                   "sample": f"first {sample.num_graphs} graphs ({sample.num_nodes} nodes, {sample.num_edges} edges) per step"},
+        "cpu_baseline": {"value": value, "unit": "graphs/s", "cores": cores, "kind": kind,
+                         "sample": f"FactorGraph::FeedForward on the first {sample.num_graphs} graphs of the batch, "
+                                   f"{len(secs)} timed runs; MKL replaced by OpenMP plain loops"},
+        "e2e": {"value": value, "unit": "graphs/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ our arm
+def cpu_baseline(args, full):
+    """Reference CPU code on a bounded sample (rank 0, N=1 only)."""
+    from oracle import bindings as ob
+    kind = "reference" if ob.have_reference() else "port"
+    impl = "reference" if kind == "reference" else "oracle"
+    cores = os.cpu_count() or 1
+    ob.set_threads(cores, impl)
+    n = 2048 if args.workload == "molecules" else 256
+    off = full.graph_offsets().astype(np.int64)
+    sel = full.edge_src < off[n]
+    sample = synth.GraphBatch(full.nodes_per_graph[:n].copy(), full.edge_src[sel].copy(), full.edge_dst[sel].copy(),
+                              full.tags[: off[n]].copy(), full.num_tags, full.d, full.levels, full.hidden,
+                              full.num_class, full.weights, "sample")
+    out = ob.forward(sample, impl, iters=4, want_levels=False)
+    secs = np.asarray(out["seconds"][1:])
+    return {"value": sample.num_graphs * len(secs) / float(secs.sum()), "unit": "graphs/s", "cores": cores,
+            "kind": kind,
+            "sample": f"FactorGraph::FeedForward on the first {n} graphs of the batch ({sample.num_nodes} nodes), "
+                      f"3 timed runs after 1 warm-up; MKL replaced by OpenMP plain loops"}, out
+
+
+def level_cfg2(ctx, torch, peak_gbs, peak_kind):
+    """The single fused level on the 1,048,576-node / 8,388,608-edge Erdos-Renyi problem."""
+    p = synth.erdos_renyi_level()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    rp = torch.from_numpy(p.row_ptr).to(dev)
+    ci = torch.from_numpy(p.col_idx).to(dev)
+    H, W, X = (torch.from_numpy(a).to(dev) for a in (p.H, p.W, p.X))
+    out = torch.empty_like(X)
+    st = torch.cuda.current_stream().cuda_stream
+    assert st != 0, "the caller must make a non-default torch stream current (handle 0 selects the context's stream)"
+    torch.cuda.synchronize()
+    for _ in range(5):
+        ctx.level(rp, ci, None, H, W, X, out, stream=st)
+    iters = 30
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    torch.cuda.synchronize()
+    for a, b in evs:
+        a.record()
+        ctx.level(rp, ci, None, H, W, X, out, stream=st)
+        b.record()
+    torch.cuda.synchronize()
+    ms = sorted(a.elapsed_time(b) for a, b in evs)
+    mean_ms = float(np.mean(ms))
+    gather = level_bytes(p.n_rows, p.nnz, p.d, "gather", "dense")
+    comp = level_bytes(p.n_rows, p.nnz, p.d, "compulsory", "dense")
+    ach = gather / (mean_ms * 1e-3) / 1e9
+    return {"workload": "fused level, Erdos-Renyi n=1048576 nnz=8388608 d=64, ReLU(A*H*W+X)", "ms": mean_ms,
+            "ms_min": ms[0], "bound": "hbm", "achieved": ach, "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs,
+            "peak_kind": peak_kind, "bytes_gather_model": gather, "bytes_compulsory_model": comp,
+            "edges_per_sec": p.nnz / (mean_ms * 1e-3), "traffic": None, "launches": iters,
+            "l2_note": "H (268 MB) + X + out exceed the 126 MB L2"}
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+    from graphnn_b200 import capi, engine
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: the CUDA library has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    full = make_workload(args.workload, seed=rank)      # this rank's shard of the 16,384 x N-graph job
+    eng = engine.S2VInference(full.weights, full.levels, device=local_rank)
+    ctx = eng.ctx
+    hb = engine.build_host_batch(full)
+    db = eng.to_device(hb)
+    G, N, E, d, L = full.num_graphs, full.num_nodes, full.num_edges, full.d, full.levels
+    C = full.num_class
+    w = eng.w
+    # the step, composed from the library's operators so that each fused-level launch can
+    # be bracketed by CUDA events on the launching stream
+    ha = torch.empty((N, d), device=dev)
+    hbuf = torch.empty((N, d), device=dev)
+    Y = torch.empty((G, d), device=dev)
+    logits = torch.empty((G, C), device=dev)
+    pred = torch.empty((G,), dtype=torch.int32, device=dev)
+    gathered = torch.empty((world * G, C), device=dev) if world > 1 else None
+    # A stream of torch's own (non-zero handle: handle 0 would select the library's
+    # context stream, which torch events cannot see), made current for everything below.
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.synchronize()
+    torch.cuda.set_stream(stream)
+    st = stream.cuda_stream
+    level_events = []
+
+    def step(timed: bool):
+        ctx.input_proj_onehot(db.tags, w["w_n2l"], None, ha, stream=st)
+        cur, nxt = ha, hbuf
+        for _ in range(L):
+            if timed:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+            ctx.level_lookup(db.row_ptr, db.col_idx, None, cur, w["p_node_conv"], w["w_n2l"], db.tags, nxt, stream=st)
+            if timed:
+                b.record(stream)
+                level_events.append((a, b))
+            cur, nxt = nxt, cur
+        ctx.segment_sum(db.graph_ptr, cur, Y, stream=st)
+        ctx.readout(Y, w["h1_weight"], w["h2_weight"], logits, None, pred, stream=st)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, logits)     # the final logits gather
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step(False)
+    barrier()
+    launches0 = ctx.launches
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        t0.record(stream)
+        for _ in range(args.steps):
+            step(True)
+        t1.record(stream)
+        barrier()
+    elapsed_ms = t0.elapsed_time(t1)
+    launches = ctx.launches - launches0
+    level_ms = float(np.mean([a.elapsed_time(b) for a, b in level_events]))
+
+    # ---- end to end through the host-buffer entry point: edge list -> CSR (host) -> upload -> forward -> download
+    es = np.ascontiguousarray(full.edge_src, np.int32)
+    ed = np.ascontiguousarray(full.edge_dst, np.int32)
+    logits_h = np.empty((G, C), np.float32)
+    pred_h = np.empty((G,), np.int32)
+
+    def e2e_step():
+        lib = ctx.lib
+        rc = lib.s2v_build_n2n_csr_host(N, E, es.ctypes.data, ed.ctypes.data, 0, hb.row_ptr.data_ptr(),
+                                        hb.col_idx.data_ptr(), None)
+        assert rc == 0
+        eng.infer_host(hb, logits_h, pred_h)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e2e_steps = max(3, min(args.steps, 20))
+    w0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - w0) * 1e3
+    assert np.array_equal(pred_h, pred.cpu().numpy()), "host-buffer path and device path disagree"
+
+    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = (float(x) for x in times.cpu())
+
+    if rank == 0:
+        peak_gbs, peak_kind = measured_peaks()
+        comp = level_bytes(N, E, d, "compulsory", "lookup")
+        survey = level_bytes(N, E, d, "compulsory", "dense")
+        ach = comp / (level_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": world * G * args.steps / (elapsed_ms * 1e-3), "unit": "graphs/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": ("molecules_16k: 16,384 molecule-like graphs per GPU (20-40 nodes, tree + 10% edges, "
+                                    "82 Zipf(1.2) tags), d=128, L=4, hidden=256, C=2, sum pooling" if args.workload == "molecules"
+                                    else "proteins_4k: 4,096 protein-like graphs per GPU (100-620 nodes, mean degree ~7.4), "
+                                    "d=64, L=5, hidden=128"),
+                       "graphs_per_gpu": G, "nodes_per_gpu": N, "edges_per_gpu": E, "parallelism": f"shard-by-graph x{world}",
+                       "l2": "per-step working set (3 x [N x d] fp32, > 700 MB) exceeds the 126 MB L2; no flush needed",
+                       "input_digest": full.digest()},
+            "e2e": {"value": world * G * e2e_steps / (e2e_ms * 1e-3), "unit": "graphs/s",
+                    "h2d_bytes_per_step": hb.nbytes(), "d2h_bytes_per_step": int(logits_h.nbytes + pred_h.nbytes),
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                    "includes": "host CSR build from the edge list, pinned uploads, forward, download of logits and predictions"},
+            "gpu_launches": int(launches),
+            "roofline": {"kernel": "s2v_level_kernel<128> (X looked up from W_in by tag)", "bound": "hbm", "achieved": ach,
+                         "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs, "peak_kind": peak_kind, "traffic": None,
+                         "ms_per_launch": level_ms, "launches": len(level_events), "bytes_per_launch": comp,
+                         "model": "compulsory (each H row once) + CSR + tags + out + W",
+                         "achieved_with_dense_X_model": survey / (level_ms * 1e-3) / 1e9},
+            "clocks": clocks.summary(),
+        }
+        if world == 1:
+            base, ref_out = cpu_baseline(args, full)
+            line["cpu_baseline"] = base
+            n = ref_out["argmax"].shape[0]
+            line["parity_vs_cpu_sample"] = {"graphs": int(n), "argmax_equal": bool(np.array_equal(ref_out["argmax"], pred_h[:n])),
+                                            "max_abs_logit_diff": float(np.abs(ref_out["logits"] - logits_h[:n]).max())}
+            if not args.skip_level:
+                line["level_cfg2"] = level_cfg2(ctx, torch, peak_gbs, peak_kind)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="molecules", choices=["molecules", "proteins"])
+    ap.add_argument("--skip-level", action="store_true", help="leave out the 1M-node fused-level measurement")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world == 1 and args.gpus > 1 and "RANK" not in os.environ:
+        # convenience: relaunch under torchrun
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29511", os.path.abspath(__file__)] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    if args.impl == "reference":
+        args.warmup = max(args.warmup, 1)   # the reference's first FeedForward of a batch size is many times slower
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

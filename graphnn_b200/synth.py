@@ -104,8 +104,11 @@ def _weights(rng, F, d, hidden, C, std):
     return {"w_n2l": n(F, d), "p_node_conv": n(d, d), "h1_weight": n(d, hidden), "h2_weight": n(hidden, C)}
 
 
-def _finish(name, sizes, und_src, und_dst, tags, F, d, L, hidden, C, rng, std):
-    """Symmetrise undirected edges (global ids) and order them as GetBatch would add them."""
+def _finish(name, sizes, und_src, und_dst, tags, F, d, L, hidden, C, rng, std, weight_seed=None):
+    """Symmetrise undirected edges (global ids) and order them as GetBatch would add them.
+    Weights continue the graph generator's stream unless `weight_seed` names their own."""
+    if weight_seed is not None:
+        rng = np.random.default_rng(weight_seed)
     s = np.concatenate([und_src, und_dst]).astype(np.int64)
     t = np.concatenate([und_dst, und_src]).astype(np.int64)
     N = int(sizes.sum())
@@ -137,7 +140,7 @@ def _tree_plus_extra(rng, n: int, extra_frac: float):
 
 
 def molecule_like(num_graphs, n_lo, n_hi, num_tags, d, levels, hidden, num_class, weight_std, tag_dist="uniform",
-                  seed=0, name="molecule") -> GraphBatch:
+                  seed=0, name="molecule", weight_seed=None) -> GraphBatch:
     rng = np.random.default_rng(seed)
     sizes = rng.integers(n_lo, n_hi + 1, size=num_graphs).astype(np.int64)
     us, vs = [], []
@@ -154,7 +157,7 @@ def molecule_like(num_graphs, n_lo, n_hi, num_tags, d, levels, hidden, num_class
         p = 1.0 / np.arange(1, num_tags + 1, dtype=np.float64) ** float(tag_dist)
         tags = rng.choice(num_tags, size=N, p=p / p.sum())
     return _finish(name, sizes, np.concatenate(us), np.concatenate(vs), tags, num_tags, d, levels, hidden,
-                   num_class, rng, weight_std)
+                   num_class, rng, weight_std, weight_seed)
 
 
 def mutag_like(seed=0, num_graphs=64) -> GraphBatch:
@@ -162,12 +165,12 @@ def mutag_like(seed=0, num_graphs=64) -> GraphBatch:
     return molecule_like(num_graphs, 10, 28, 7, 64, 3, 128, 2, 0.1, "uniform", seed, "mutag_like")
 
 
-def molecules_16k(seed=0, num_graphs=16384) -> GraphBatch:
+def molecules_16k(seed=0, num_graphs=16384, weight_seed=None) -> GraphBatch:
     """16,384 graphs, 20..40 nodes, tree + 10 % edges, 82 tags ~ Zipf(1.2), d 128, 4 levels, hidden 256."""
-    return molecule_like(num_graphs, 20, 40, 82, 128, 4, 256, 2, 0.05, 1.2, seed, "molecules_16k")
+    return molecule_like(num_graphs, 20, 40, 82, 128, 4, 256, 2, 0.05, 1.2, seed, "molecules_16k", weight_seed)
 
 
-def proteins_4k(seed=0, num_graphs=4096, n_lo=100, n_hi=620) -> GraphBatch:
+def proteins_4k(seed=0, num_graphs=4096, n_lo=100, n_hi=620, weight_seed=None) -> GraphBatch:
     """Random geometric graphs in the unit cube, radius for mean degree ~7.4, 3 uniform tags, d 64, 5 levels."""
     rng = np.random.default_rng(seed)
     sizes = rng.integers(n_lo, n_hi + 1, size=num_graphs).astype(np.int64)
@@ -184,7 +187,8 @@ def proteins_4k(seed=0, num_graphs=4096, n_lo=100, n_hi=620) -> GraphBatch:
         vs.append(v.astype(np.int64) + off)
         off += n
     tags = rng.integers(0, 3, size=int(sizes.sum()))
-    return _finish("proteins_4k", sizes, np.concatenate(us), np.concatenate(vs), tags, 3, 64, 5, 128, 2, rng, 0.05)
+    return _finish("proteins_4k", sizes, np.concatenate(us), np.concatenate(vs), tags, 3, 64, 5, 128, 2, rng, 0.05,
+                   weight_seed)
 
 
 @dataclass

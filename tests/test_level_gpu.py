@@ -107,7 +107,7 @@ def test_level_relu_keeps_negative_zero_and_nan(gpu_ctx):
     p = LevelProblem(16, 16, row_ptr, np.array([0], np.int32), H, W, X)
     out = run_level(gpu_ctx, p)
     assert np.isnan(out[0, 0])
-    assert np.signbit(out[1]).all() and (out[1] == 0).all()     # -0.0 is not < 0
+    assert (out[1] == 0).all() and not np.signbit(out[1]).any()  # (+0) + (-0) = +0, as in the reference's CopyFrom + Axpy
     assert (out[2] == 0).all() and not np.signbit(out[2]).any()
 
 
@@ -178,6 +178,12 @@ def test_elementwise_softmax_argmax(gpu_ctx, oracle_lib):
     gpu_ctx.synchronize()
     assert_close(y.cpu().numpy(), y0 + np.float32(0.75) * x, "axpy")
     assert np.array_equal(r.cpu().numpy(), np.where(x < 0, np.float32(0), x))
+    special = np.array([-0.0, np.nan, -1.0, 2.0], np.float32)     # `if (x < 0) x = 0` keeps -0.0 and NaN
+    rs = torch.empty(4, device="cuda")
+    gpu_ctx.relu(dev(special), rs)
+    gpu_ctx.synchronize()
+    rs = rs.cpu().numpy()
+    assert rs[0] == 0 and np.signbit(rs[0]) and np.isnan(rs[1]) and rs[2] == 0 and rs[3] == 2
     assert (s.cpu().numpy() == 0).all()
     for cols in (2, 5, 33, 1023):
         l = rng.standard_normal((37, cols), dtype=np.float32) * 3
