@@ -9,18 +9,24 @@
 //
 // Shape of the kernel (HBM-bound gather + small dense product):
 //   * persistent CTAs, grid = #SMs x resident CTAs; W [d x d] is staged once per CTA
-//     into shared memory with one bulk-async (TMA) copy completing on an mbarrier;
+//     into shared memory by bulk-async (TMA) row copies completing on one mbarrier,
+//     into rows padded by 8 floats so that tensor-core B fragments load conflict-free;
 //   * each WARP owns tiles of TILE_R = 16 consecutive rows and runs on its own, with
 //     only __syncwarp between phases, so warps of one SM sit in different phases and
-//     the gather of one overlaps the FMAs of another:
+//     the gather of one overlaps the matrix product of another:
 //       1. the tile's row offsets and column indices are fetched coalesced into a
 //          per-warp shared buffer (removes one dependent-load level from the gather),
 //       2. gather: d/4 lanes per row, float4 loads of neighbour rows, U loads in
 //          flight per lane, fp32 accumulation in CSR order,
-//       3. the 16 x d tile of sums goes to shared memory and the warp multiplies it by
-//          W from shared memory (4 rows x d/8 columns per lane, k ascending),
-//       4. epilogue adds X (streamed, or looked up in a small table), applies ReLU and
-//          stores 128 contiguous bytes per row per instruction.
+//       3. the 16 x d tile of sums goes to shared memory and is multiplied by W on the
+//          tensor cores as 3xTF32 (m16n8k8 MMA; every operand split into a TF32 head
+//          and a TF32 tail, the three significant partial products accumulated in
+//          fp32), which keeps the result within fp32 rounding of an FFMA product.
+//          The plain-FFMA form of this stage saturated the FMA pipe (47 % of its peak
+//          at 10 % DRAM utilisation for d = 128), which is what moved it here;
+//       4. the product goes back through the same shared tile so that the epilogue
+//          (add X -- streamed, or looked up in a small table --, ReLU, store) touches
+//          global memory in whole 128..512-byte rows.
 #include "common.cuh"
 
 namespace
@@ -47,15 +53,37 @@ struct LevelCfg<128> {
 
 template <int D>
 struct LevelSmem {
-    static constexpr int S_STRIDE = D + 4;
-    static constexpr size_t W_BYTES = sizeof(float) * D * D;
+    static constexpr int S_STRIDE = D + 4;   // A fragments (rows g, g+8; cols tig, tig+4) hit 32 distinct banks
+    static constexpr int W_STRIDE = D + 8;   // B fragments (rows tig, tig+4; col g) hit 32 distinct banks
+    static constexpr size_t W_BYTES = sizeof(float) * D * W_STRIDE;
     static constexpr size_t WARP_BYTES = sizeof(float) * TILE_R * S_STRIDE + sizeof(int) * IDX_CAP + sizeof(float) * IDX_CAP;
     static constexpr size_t total(int warps) { return W_BYTES + 16 + WARP_BYTES * warps; }
 };
 
-__device__ __forceinline__ float f4_get(const float4& v, int i)
+// TF32 split helpers.  head = value rounded to TF32, tail = (value - head) cut to TF32.
+__device__ __forceinline__ uint32_t tf32_round(float v)
 {
-    return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return r;
+}
+__device__ __forceinline__ void tf32_split_rn(float v, uint32_t& head, uint32_t& tail)
+{
+    head = tf32_round(v);
+    tail = tf32_round(v - __uint_as_float(head));
+}
+// cheaper form for W, applied on every use: head by truncation (the subtraction is exact)
+__device__ __forceinline__ void tf32_split_trunc(float v, uint32_t& head, uint32_t& tail)
+{
+    head = __float_as_uint(v) & 0xffffe000u;
+    tail = __float_as_uint(v - __uint_as_float(head)) & 0xffffe000u;
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
 // --- mbarrier + bulk-async copy (TMA, non-tensor form) ---------------------------
@@ -99,8 +127,8 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
     constexpr int RPP = 32 / LPR;       // rows gathered side by side per pass
     constexpr int NPASS = TILE_R / RPP;
     constexpr int S_STRIDE = LevelSmem<D>::S_STRIDE;
-    constexpr int RI = TILE_R / 4;      // rows per lane in the dense phase
-    constexpr int NJ = D / 32;          // float4 column chunks per lane
+    constexpr int W_STRIDE = LevelSmem<D>::W_STRIDE;
+    constexpr int NT = D / 8;           // 8-column MMA tiles across the output row
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float* Ws = reinterpret_cast<float*>(smem_raw);
@@ -116,8 +144,9 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
     if (threadIdx.x == 0) {
         mbar_init(bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        mbar_expect_tx(bar, (uint32_t)LevelSmem<D>::W_BYTES);
-        bulk_copy_g2s(smem_u32(Ws), W, (uint32_t)LevelSmem<D>::W_BYTES, bar);
+        mbar_expect_tx(bar, (uint32_t)(sizeof(float) * D * D));
+        for (int k = 0; k < D; ++k)  // one bulk copy per row of W, into the padded layout
+            bulk_copy_g2s(smem_u32(Ws + k * W_STRIDE), W + k * D, (uint32_t)(sizeof(float) * D), bar);
     }
     __syncthreads();  // barrier initialised before anyone polls it
     {
@@ -137,7 +166,7 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
 
     const float4* __restrict__ H4 = reinterpret_cast<const float4*>(H);
     const int sub = lane / LPR, sl = lane % LPR;
-    const int rg = lane >> 3, cg = lane & 7;
+    const int g = lane >> 2, tig = lane & 3;   // MMA fragment coordinates
 
     for (int64_t tile = (int64_t)blockIdx.x * WARPS + warp; tile < num_tiles; tile += (int64_t)gridDim.x * WARPS) {
         const int64_t r0 = tile * TILE_R;
@@ -209,57 +238,53 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
         }
         __syncwarp();
 
-        // ---- 3. [16 x D] * W[D x D]; lane (rg, cg) owns rows rg+4i and columns cg*4+32j..+3
-        float o[RI][NJ * 4];
+        // ---- 3. [16 x D] * W[D x D] on the tensor cores, 3xTF32
+        float c[NT][4];
 #pragma unroll
-        for (int i = 0; i < RI; ++i)
+        for (int nt = 0; nt < NT; ++nt) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
+#pragma unroll 1
+        for (int ks = 0; ks < D / 8; ++ks) {
+            uint32_t ah[4], al[4];
+            const float* sa = S + g * S_STRIDE + ks * 8 + tig;
+            tf32_split_rn(sa[0], ah[0], al[0]);
+            tf32_split_rn(sa[8 * S_STRIDE], ah[1], al[1]);
+            tf32_split_rn(sa[4], ah[2], al[2]);
+            tf32_split_rn(sa[8 * S_STRIDE + 4], ah[3], al[3]);
+            const float* wb = Ws + (ks * 8 + tig) * W_STRIDE + g;
 #pragma unroll
-            for (int c = 0; c < NJ * 4; ++c) o[i][c] = 0.f;
-#pragma unroll 2
-        for (int k = 0; k < D; k += 4) {
-            float4 s[RI];
-#pragma unroll
-            for (int i = 0; i < RI; ++i) s[i] = *reinterpret_cast<const float4*>(S + (rg + 4 * i) * S_STRIDE + k);
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-                float4 w[NJ];
-#pragma unroll
-                for (int j = 0; j < NJ; ++j) w[j] = *reinterpret_cast<const float4*>(Ws + (k + kk) * D + cg * 4 + 32 * j);
-#pragma unroll
-                for (int i = 0; i < RI; ++i) {
-                    const float sv = f4_get(s[i], kk);
-#pragma unroll
-                    for (int j = 0; j < NJ; ++j) {
-                        o[i][4 * j + 0] = fmaf(sv, w[j].x, o[i][4 * j + 0]);
-                        o[i][4 * j + 1] = fmaf(sv, w[j].y, o[i][4 * j + 1]);
-                        o[i][4 * j + 2] = fmaf(sv, w[j].z, o[i][4 * j + 2]);
-                        o[i][4 * j + 3] = fmaf(sv, w[j].w, o[i][4 * j + 3]);
-                    }
-                }
+            for (int nt = 0; nt < NT; ++nt) {
+                uint32_t bh0, bl0, bh1, bl1;
+                tf32_split_trunc(wb[nt * 8], bh0, bl0);
+                tf32_split_trunc(wb[4 * W_STRIDE + nt * 8], bh1, bl1);
+                mma_tf32(c[nt], al, bh0, bh1);   // small terms first
+                mma_tf32(c[nt], ah, bl0, bl1);
+                mma_tf32(c[nt], ah, bh0, bh1);
             }
         }
+        __syncwarp();  // every lane is done reading S
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            *reinterpret_cast<float2*>(S + g * S_STRIDE + nt * 8 + 2 * tig) = make_float2(c[nt][0], c[nt][1]);
+            *reinterpret_cast<float2*>(S + (g + 8) * S_STRIDE + nt * 8 + 2 * tig) = make_float2(c[nt][2], c[nt][3]);
+        }
+        __syncwarp();
 
-        // ---- 4. + X, ReLU, store
+        // ---- 4. + X, ReLU, store: whole rows, d/4 lanes per row
 #pragma unroll
-        for (int i = 0; i < RI; ++i) {
-            const int64_t row = r0 + rg + 4 * i;
+        for (int p = 0; p < NPASS; ++p) {
+            const int lr = p * RPP + sub;
+            const int64_t row = r0 + lr;
             if (row < n_rows) {
-                const float4* xrow = nullptr;
-                if (XMODE == 1) xrow = reinterpret_cast<const float4*>(X) + row * LPR;
-                if (XMODE == 2) xrow = reinterpret_cast<const float4*>(X) + (int64_t)__ldg(x_index + row) * LPR;
-                float4* orow = reinterpret_cast<float4*>(out) + row * LPR;
-#pragma unroll
-                for (int j = 0; j < NJ; ++j) {
-                    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (XMODE == 1) x = ld_stream_f4(xrow + cg + 8 * j);
-                    if (XMODE == 2) x = ld_nc_f4(xrow + cg + 8 * j);
-                    float4 r;
-                    r.x = relu_ref(o[i][4 * j + 0] + x.x);
-                    r.y = relu_ref(o[i][4 * j + 1] + x.y);
-                    r.z = relu_ref(o[i][4 * j + 2] + x.z);
-                    r.w = relu_ref(o[i][4 * j + 3] + x.w);
-                    orow[cg + 8 * j] = r;
-                }
+                const float4 o = *reinterpret_cast<const float4*>(S + lr * S_STRIDE + sl * 4);
+                float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (XMODE == 1) x = ld_stream_f4(reinterpret_cast<const float4*>(X) + row * LPR + sl);
+                if (XMODE == 2) x = ld_nc_f4(reinterpret_cast<const float4*>(X) + (int64_t)__ldg(x_index + row) * LPR + sl);
+                float4 r;
+                r.x = relu_ref(o.x + x.x);
+                r.y = relu_ref(o.y + x.y);
+                r.z = relu_ref(o.z + x.z);
+                r.w = relu_ref(o.w + x.w);
+                reinterpret_cast<float4*>(out)[row * LPR + sl] = r;
             }
         }
         __syncwarp();  // S and idx_s are rewritten by the next tile
