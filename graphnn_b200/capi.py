@@ -74,6 +74,7 @@ def load_library():
         "s2v_input_proj_dense_f32": (i32, [vp, vp, i64, i32, i32, vp, vp, vp, vp]),
         "s2v_forward_workspace_bytes": (C.c_size_t, [i64, i64, i32]),
         "s2v_forward_f32": (i32, [vp, vp, C.POINTER(Model), C.POINTER(Batch), vp, C.c_size_t, vp, vp, vp, vp]),
+        "s2v_forward_static_f32": (i32, [vp, vp, C.POINTER(Model), C.POINTER(Batch), vp, vp, vp, vp]),
         "s2v_build_n2n_csr_host": (i32, [i64, i64, vp, vp, i32, vp, vp, vp]),
         "s2v_validate_csr_host": (i32, [i64, i64, i64, vp, vp]),
         "s2v_infer_host_f32": (i32, [vp, C.POINTER(Model), C.POINTER(Batch), vp, vp]),
@@ -253,6 +254,11 @@ class Context:
         self.call("s2v_forward_f32", stream, C.byref(model), C.byref(batch), _ptr(workspace),
                   workspace.numel() * workspace.element_size(), _ptr(logits), _ptr(probs), _ptr(pred),
                   _ptr(embed_out))
+
+    def forward_static(self, model: Model, batch: Batch, logits, probs=None, pred=None, embed_out=None, stream=None):
+        """s2v_forward_static_f32: like forward() but with the library's built-in scratch array."""
+        self.call("s2v_forward_static_f32", stream, C.byref(model), C.byref(batch), _ptr(logits), _ptr(probs),
+                  _ptr(pred), _ptr(embed_out))
 
     def infer_host(self, model: Model, batch_host: Batch, logits_host: np.ndarray | None,
                    pred_host: np.ndarray | None):

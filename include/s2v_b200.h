@@ -169,6 +169,21 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
                     void* workspace, size_t workspace_bytes, float* logits, float* probs, int32_t* pred,
                     float* embed_out);
 
+/* ---- the whole classifier for callers that cannot allocate device memory.
+ * No counterpart in the reference (its tensors call cudaMalloc through MemHolder).
+ * Same arguments and results as s2v_forward_f32 minus the workspace: the scratch lives
+ * in a fixed S2V_STATIC_SCRATCH_BYTES array inside the loaded module, so no cudaMalloc /
+ * cudaFree happens on this path.  Meant for hosts whose device memory is owned
+ * entirely by another pool, or that may not call the allocator because it
+ * synchronises the whole device.  Batches whose s2v_forward_workspace_bytes exceeds
+ * the array are rejected with S2V_ERR_WORKSPACE.  The first call on a device resolves
+ * the array's address (do it at set-up, before any stream capture begins).  All calls
+ * on a GPU share the array and keep its last contents; nothing needs zeroing, but
+ * calls that overlap on the same GPU race and must be serialised by the caller. */
+#define S2V_STATIC_SCRATCH_BYTES (16u << 20)
+int s2v_forward_static_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, const s2v_batch* batch,
+                           float* logits, float* probs, int32_t* pred, float* embed_out);
+
 /* ---- host-side batch construction, bit-identical to the reference ----
  * Node-to-node CSR from a directed edge list in AddEdge order: row y lists the sources
  * of edges x->y in insertion order (GraphStruct::AddEdge, src/util/graph_struct.cpp:62-70
