@@ -1,6 +1,7 @@
 // C ABI glue of s2v_b200: context life cycle, argument validation, the whole-model
 // pipelines (device buffers and host buffers) and the host-side CSR builders.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <thread>
@@ -114,6 +115,8 @@ int s2v_ctx_create(int device, s2v_ctx** out)
     }
     ctx->dstatus_host->code = 0;
     ctx->dstatus_host->where = 0;
+    // S2V_LEVEL_TC = 0 | 1 | 2 : never / automatic / always use the tcgen05 level kernel (d = 128)
+    if (const char* e = std::getenv("S2V_LEVEL_TC")) ctx->tc_mode = (e[0] == '0') ? 0 : (e[0] == '2' ? 2 : 1);
     *out = ctx;
     return S2V_OK;
 }

@@ -39,7 +39,7 @@ struct s2v_ctx {
     std::string last_error;
     std::mutex mu;
     s2v_staging staging;
-    bool level_attr_set[8] = {false, false, false, false, false, false, false, false};
+    int tc_mode = 1;  // tcgen05 level kernel: 0 never, 1 when the batch is large enough, 2 whenever the shape allows
 };
 
 inline int s2v_fail(s2v_ctx* ctx, int status, const std::string& msg)
@@ -126,7 +126,13 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p)
 
 #endif  // __CUDACC__
 
+// Rows from which the d = 128 level goes to the tcgen05 kernel (128-row tiles, one CTA per SM).
+constexpr int64_t S2V_TC_MIN_ROWS = 16384;
+
 // launchers implemented in the .cu files (host side)
+int s2v_launch_level_tc(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int d, const int32_t* row_ptr,
+                        const int32_t* col_idx, const float* val, const float* H, const float* W, const float* X,
+                        const float* table, const int32_t* x_index, float* out);
 int s2v_launch_level(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int64_t n_src, int d, const void* row_ptr,
                      bool rp64, const int32_t* col_idx, const float* val, const float* H, const float* W,
                      const float* X, const float* table, const int32_t* x_index, float* out);

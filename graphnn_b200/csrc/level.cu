@@ -16,8 +16,9 @@
 //     the gather of one overlaps the matrix product of another:
 //       1. the tile's row offsets and column indices are fetched coalesced into a
 //          per-warp shared buffer (removes one dependent-load level from the gather),
-//       2. gather: d/4 lanes per row, float4 loads of neighbour rows, U loads in
-//          flight per lane, fp32 accumulation in CSR order,
+//       2. gather: d/4 lanes per row, float4 loads of neighbour rows; each lane group
+//          walks the non-zeros of its rows as one stream so that U loads are in flight
+//          per lane whatever the row lengths; fp32 accumulation in CSR order,
 //       3. the 16 x d tile of sums goes to shared memory and is multiplied by W on the
 //          tensor cores as 3xTF32 (m16n8k8 MMA; every operand split into a TF32 head
 //          and a TF32 tail, the three significant partial products accumulated in
@@ -40,15 +41,18 @@ template <int D>
 struct LevelCfg;
 template <>
 struct LevelCfg<32> {
-    static constexpr int WARPS = 8, MIN_BLOCKS = 4, U = 8;
+    static constexpr int WARPS = 8, MIN_BLOCKS = 3, U = 8;
+    static constexpr bool FLAT = false;
 };
 template <>
 struct LevelCfg<64> {
     static constexpr int WARPS = 8, MIN_BLOCKS = 3, U = 8;
+    static constexpr bool FLAT = false;   // measured: per-row passes are faster at degree ~8, d = 64
 };
 template <>
 struct LevelCfg<128> {
-    static constexpr int WARPS = 12, MIN_BLOCKS = 1, U = 4;
+    static constexpr int WARPS = 12, MIN_BLOCKS = 1, U = 8;
+    static constexpr bool FLAT = true;    // measured: the flat stream is faster at degree ~2, d = 128
 };
 
 template <int D>
@@ -56,7 +60,7 @@ struct LevelSmem {
     static constexpr int S_STRIDE = D + 4;   // A fragments (rows g, g+8; cols tig, tig+4) hit 32 distinct banks
     static constexpr int W_STRIDE = D + 8;   // B fragments (rows tig, tig+4; col g) hit 32 distinct banks
     static constexpr size_t W_BYTES = sizeof(float) * D * W_STRIDE;
-    static constexpr size_t WARP_BYTES = sizeof(float) * TILE_R * S_STRIDE + sizeof(int) * IDX_CAP + sizeof(float) * IDX_CAP;
+    static constexpr size_t WARP_BYTES = sizeof(float) * TILE_R * S_STRIDE + sizeof(int) * IDX_CAP + sizeof(float) * IDX_CAP + sizeof(int) * 32;
     static constexpr size_t total(int warps) { return W_BYTES + 16 + WARP_BYTES * warps; }
 };
 
@@ -126,6 +130,7 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
     constexpr int LPR = D / 4;          // lanes that cover one row with float4
     constexpr int RPP = 32 / LPR;       // rows gathered side by side per pass
     constexpr int NPASS = TILE_R / RPP;
+    constexpr int RPS = TILE_R / RPP;   // rows per lane group in the gather
     constexpr int S_STRIDE = LevelSmem<D>::S_STRIDE;
     constexpr int W_STRIDE = LevelSmem<D>::W_STRIDE;
     constexpr int NT = D / 8;           // 8-column MMA tiles across the output row
@@ -138,6 +143,7 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
     float* S = reinterpret_cast<float*>(wbase);
     int* idx_s = reinterpret_cast<int*>(wbase + sizeof(float) * TILE_R * S_STRIDE);
     float* val_s = reinterpret_cast<float*>(idx_s + IDX_CAP);
+    int* rp_s = reinterpret_cast<int*>(val_s + IDX_CAP);   // the tile's 17 relative row offsets
 
     // ---- stage W: one bulk-async copy per CTA, completion on an mbarrier
     const uint32_t bar = smem_u32(mbar);
@@ -170,13 +176,14 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
 
     for (int64_t tile = (int64_t)blockIdx.x * WARPS + warp; tile < num_tiles; tile += (int64_t)gridDim.x * WARPS) {
         const int64_t r0 = tile * TILE_R;
-        // ---- 1. row offsets (lane l holds row_ptr[r0 + l], clamped) and the tile's indices
+        // ---- 1. row offsets (relative to the tile's first non-zero) and the tile's indices
         int64_t rpi = r0 + lane;
         if (rpi > n_rows) rpi = n_rows;
         const RpT rp_abs = lane <= TILE_R ? row_ptr[rpi] : (RpT)0;
         const RpT base = __shfl_sync(0xffffffffu, rp_abs, 0);
         const int rp_rel = (int)(rp_abs - base);
         const int tile_nnz = __shfl_sync(0xffffffffu, rp_rel, TILE_R);
+        if (lane <= TILE_R) rp_s[lane] = rp_rel;
         const bool fits = tile_nnz <= IDX_CAP;
         const int* ip;
         const float* vp;
@@ -193,12 +200,72 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
         }
         __syncwarp();
 
-        // ---- 2. gather + sum in CSR order
+        // ---- 2. gather + sum in CSR order.
+        //   FLAT (low-degree, wide rows): each group of LPR lanes walks the non-zeros of its
+        //   RPS consecutive rows as ONE stream, U loads in flight whatever the row lengths; a
+        //   row's sum is flushed to the shared tile when the stream crosses its end.
+        //   Otherwise: one row per lane group per pass, chunks of U neighbours.
+        if constexpr (LevelCfg<D>::FLAT) {
+            int row = sub * RPS;
+            const int row_stop = row + RPS;
+            int t = rp_s[row];
+            const int ee = rp_s[row_stop];
+            int row_end = rp_s[row + 1];
+            float* srow = S + row * S_STRIDE + sl * 4;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#define S2V_FLUSH_ROWS(pos)                                                  \
+    while ((pos) == row_end) {                                               \
+        *reinterpret_cast<float4*>(srow) = acc;                              \
+        acc = make_float4(0.f, 0.f, 0.f, 0.f);                               \
+        ++row;                                                               \
+        srow += S_STRIDE;                                                    \
+        row_end = rp_s[row + 1];                                             \
+    }
+#define S2V_ACCUM(u)                                                         \
+    if (HAS_VAL) {                                                           \
+        const float a = vp[t + (u)];                                         \
+        acc.x = fmaf(a, v[u].x, acc.x); acc.y = fmaf(a, v[u].y, acc.y);      \
+        acc.z = fmaf(a, v[u].z, acc.z); acc.w = fmaf(a, v[u].w, acc.w);      \
+    } else {                                                                 \
+        acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;  \
+    }
+            for (; t + U <= ee; t += U) {
+                float4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) v[u] = ld_nc_f4(H4 + (int64_t)ip[t + u] * LPR + sl);
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    S2V_FLUSH_ROWS(t + u)
+                    S2V_ACCUM(u)
+                }
+            }
+            if (t < ee) {
+                float4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (t + u < ee) v[u] = ld_nc_f4(H4 + (int64_t)ip[t + u] * LPR + sl);
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (t + u < ee) {
+                        S2V_FLUSH_ROWS(t + u)
+                        S2V_ACCUM(u)
+                    }
+                }
+            }
+#undef S2V_FLUSH_ROWS
+#undef S2V_ACCUM
+            while (row < row_stop) {  // the open row, then empty rows behind it
+                *reinterpret_cast<float4*>(srow) = acc;
+                acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                ++row;
+                srow += S_STRIDE;
+            }
+        } else {
 #pragma unroll 1
         for (int p = 0; p < NPASS; ++p) {
             const int lr = p * RPP + sub;
-            const int beg = __shfl_sync(0xffffffffu, rp_rel, lr);
-            const int end = __shfl_sync(0xffffffffu, rp_rel, lr + 1);
+            const int beg = rp_s[lr];
+            const int end = rp_s[lr + 1];
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             int t = beg;
             for (; t + U <= end; t += U) {
@@ -235,6 +302,7 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
                 }
             }
             *reinterpret_cast<float4*>(S + lr * S_STRIDE + sl * 4) = acc;
+        }
         }
         __syncwarp();
 
@@ -340,6 +408,11 @@ int s2v_launch_level(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int64_t n_sr
 {
     (void)n_src;
     if (n_rows == 0) return S2V_OK;
+    if (d == 128 && !rp64 && (ctx->tc_mode == 2 || (ctx->tc_mode == 1 && n_rows >= S2V_TC_MIN_ROWS))) {
+        const int rc = s2v_launch_level_tc(ctx, st, n_rows, d, (const int32_t*)row_ptr, col_idx, val, H, W, X, table,
+                                           x_index, out);
+        if (rc != S2V_ERR_UNSUPPORTED) return rc;
+    }
 #define S2V_D(DD)                                                                                                  \
     case DD:                                                                                                       \
         return rp64 ? launch_d<DD, int64_t>(ctx, st, n_rows, (const int64_t*)row_ptr, col_idx, val, H, W, X, table, \
