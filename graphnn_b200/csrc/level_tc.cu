@@ -55,7 +55,15 @@ constexpr size_t TC_GW_BYTES = 2 * (sizeof(int) * TC_IDX_CAP + sizeof(int) * 32)
 constexpr size_t TC_OFF_BAR = TC_OFF_GW + TC_GW_BYTES * TC_GW;
 constexpr size_t TC_SMEM_BYTES = TC_OFF_BAR + 128 + 1024;   // + barriers/flags + alignment slack
 
-enum { BAR_FULL = 0, BAR_SFREE, BAR_AREADY, BAR_MMA0, BAR_MMA1, BAR_DFREE0, BAR_DFREE1, BAR_COUNT };
+// mbarriers.  FULL/SFREE exist per tensor-memory lane quarter (32 rows = two gather warps, one operand warp).
+enum {
+    BAR_FULL0 = 0,                   // +q : the quarter's 32 rows of the staging tile are written
+    BAR_SFREE0 = 4,                  // +q : the quarter's rows have been read back and may be overwritten
+    BAR_AREADY = 8,                  // all four quarters of the A operand are in tensor memory
+    BAR_MMA0, BAR_MMA1,              // the MMAs into accumulator buffer 0 / 1 are complete
+    BAR_DFREE0, BAR_DFREE1,          // accumulator buffer 0 / 1 has been read by the epilogue
+    BAR_COUNT
+};
 
 __device__ __forceinline__ void tc_mbar_init(uint32_t bar, int count)
 {
@@ -158,8 +166,10 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
 
     // ---- set-up: barriers, tensor memory, W^T split into TF32 head/tail in the MMA layout
     if (threadIdx.x == 0) {
-        tc_mbar_init(bar(BAR_FULL), TC_GW);
-        tc_mbar_init(bar(BAR_SFREE), TC_AW);
+        for (int qq = 0; qq < 4; ++qq) {
+            tc_mbar_init(bar(BAR_FULL0 + qq), TC_GW / 4);
+            tc_mbar_init(bar(BAR_SFREE0 + qq), 1);
+        }
         tc_mbar_init(bar(BAR_AREADY), TC_AW);
         tc_mbar_init(bar(BAR_MMA0), 1);
         tc_mbar_init(bar(BAR_MMA1), 1);
@@ -277,8 +287,8 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
         }                                                                                          \
     }
             TC_LOAD(va, 0)
-            // the staging tile is free once the operand warps have read tile it-1
-            if (it > 0 && !tc_wait(bar(BAR_SFREE), (uint32_t)((it - 1) & 1), abort_flag, status, 10)) break;
+            // my quarter of the staging tile is free once its operand warp has read tile it-1
+            if (it > 0 && !tc_wait(bar(BAR_SFREE0 + warp / (TC_GW / 4)), (uint32_t)((it - 1) & 1), abort_flag, status, 10)) break;
             TC_TRACE(1);
             while (t < ee) {
                 TC_LOAD(vb, t + TC_U)
@@ -298,7 +308,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                 srow += TC_STAGE_STRIDE;
             }
             __syncwarp();
-            if (lane == 0) tc_mbar_arrive(bar(BAR_FULL));
+            if (lane == 0) tc_mbar_arrive(bar(BAR_FULL0 + warp / (TC_GW / 4)));
             {   // publish the prefetched slice of tile it+1 in the other buffer
                 int* nb = idx_buf[(it + 1) & 1];
                 if (lane <= TC_ROWS_PER_GW) nb[TC_IDX_CAP + lane] = rel1;
@@ -321,7 +331,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
         TC_TRACE_DECL();
         for (int64_t it = 0; it < my_tiles; ++it) {
             const int b = (int)(it & 1);
-            if (!tc_wait(bar(BAR_FULL), (uint32_t)(it & 1), abort_flag, status, 20)) break;
+            if (!tc_wait(bar(BAR_FULL0 + q), (uint32_t)(it & 1), abort_flag, status, 20)) break;
             TC_TRACE(0);
             // the previous tile's MMAs must be done reading the A operand in tensor memory
             if (it > 0 && !tc_wait(bar(BAR_MMA0 + (int)((it - 1) & 1)), (uint32_t)(((it - 1) >> 1) & 1), abort_flag, status, 21)) break;
@@ -353,7 +363,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             __syncwarp();
-            if (lane == 0) tc_mbar_arrive(bar(BAR_SFREE));    // my 32 rows of the staging tile are consumed
+            if (lane == 0) tc_mbar_arrive(bar(BAR_SFREE0 + q));   // my 32 rows of the staging tile are consumed
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             if (lane == 0) tc_mbar_arrive(bar(BAR_AREADY));   // my quarter of the A operand is in tensor memory
             TC_TRACE(2);
