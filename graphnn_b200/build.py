@@ -56,5 +56,33 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+CXX_DIR = os.path.join(PKG, "cxx")
+CXX_BIN = os.path.join(CXX_DIR, "bin")
+
+
+def build_cxx(force: bool = False) -> dict:
+    """Compiles the host-side C++ programs that use the graphnn operator interface this
+    package provides (cxx/include): the inference driver and the host-only interface test."""
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    os.makedirs(CXX_BIN, exist_ok=True)
+    headers = [h for h in glob.glob(os.path.join(CXX_DIR, "include", "**", "*.h"), recursive=True)]
+    headers.append(os.path.join(REPO, "include", "s2v_b200.h"))
+    out = {}
+    for name, src in (("s2v_mean_field", os.path.join(CXX_DIR, "examples", "s2v_mean_field.cpp")),
+                      ("host_interface_test", os.path.join(CXX_DIR, "tests", "host_interface_test.cpp"))):
+        exe = os.path.join(CXX_BIN, name)
+        if force or _stale(exe, [src, LIB] + headers):
+            cmd = ["g++", "-std=c++14", "-O2", "-Wall", "-I", os.path.join(REPO, "include"), "-I",
+                   os.path.join(CXX_DIR, "include"), "-I", os.path.join(cuda, "include"), src, "-o", exe,
+                   "-L", PKG, "-ls2v_b200", "-L", os.path.join(cuda, "lib64"), "-lcudart",
+                   "-Wl,-rpath,$ORIGIN/../..", "-Wl,-rpath," + PKG, "-Wl,-rpath," + os.path.join(cuda, "lib64")]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"g++ failed on {src}:\n{r.stdout}\n{r.stderr}")
+        out[name] = exe
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_cxx(force="--force" in sys.argv))
