@@ -37,6 +37,12 @@ if REPO not in sys.path:
 from graphnn_b200 import synth  # noqa: E402
 
 WEIGHT_SEED = 20240
+WORKLOAD_TEXT = {
+    "molecules": "molecules_16k: 16,384 molecule-like graphs per GPU (20-40 nodes, tree + 10% edges, 82 Zipf(1.2) tags), "
+                 "d=128, L=4, hidden=256, C=2, sum pooling",
+    "proteins": "proteins_4k: 4,096 protein-like graphs per GPU (100-620 nodes, random geometric, mean degree ~7.4, 3 tags), "
+                "d=64, L=5, hidden=128, C=2, sum pooling",
+}
 METRIC = "s2v_inference_graphs_per_sec"
 
 
@@ -58,31 +64,71 @@ def measured_peaks():
 
 # ------------------------------------------------------------------ clocks
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clocks and throttle reasons of one GPU while the timed region runs
+    (NVML through pynvml every 20 ms; falls back to polling nvidia-smi)."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
     def __init__(self, index: int):
         self.index = index
-        self.samples = []
+        self.sm = []
+        self.sm_max = None
+        self.reason_bits = 0
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
 
-    def _run(self):
+    def _run_nvml(self) -> bool:
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = self.index
+            if visible:
+                ids = [v for v in visible.split(",") if v.strip()]
+                if idx < len(ids) and ids[idx].strip().isdigit():
+                    idx = int(ids[idx])
+            h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            return False
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                self.reason_bits |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+            except Exception:
+                try:
+                    self.reason_bits |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                except Exception:
+                    pass
+            self._stop.wait(0.02)
+        return True
+
+    def _run_smi(self):
+        fields = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                  "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={fields}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout
                 parts = [x.strip() for x in out.strip().split(",")]
                 if len(parts) >= 6:
-                    self.samples.append(parts)
+                    self.sm.append(float(parts[0]))
+                    self.sm_max = float(parts[1])
+                    for i, n in enumerate(names):
+                        if parts[2 + i].lower() == "active":
+                            self.reason_bits |= self.REASONS[n]
             except Exception:
                 pass
             self._stop.wait(0.05)
 
+    def _run(self):
+        if not self._run_nvml():
+            self._run_smi()
+
     def __enter__(self):
         self._thread.start()
+        time.sleep(0.05)     # let the first sample land before the timed region starts
         return self
 
     def __exit__(self, *a):
@@ -90,13 +136,11 @@ class ClockSampler:
         self._thread.join(timeout=6)
 
     def summary(self) -> dict:
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        sm = sorted(float(s[0]) for s in self.samples)
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower() == "active" for s in self.samples)]
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(self.samples[0][1]), "reasons": reasons,
-                "samples": len(sm)}
+        if not self.sm:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": ["no samples"]}
+        sm = sorted(self.sm)
+        reasons = [n for n, bit in self.REASONS.items() if self.reason_bits & bit]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": self.sm_max, "reasons": reasons, "samples": len(sm)}
 
 
 # ------------------------------------------------------------------ byte models
@@ -136,8 +180,7 @@ def run_reference(args, rank: int, world: int):
         "metric": METRIC, "value": value, "unit": "graphs/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * total / len(secs), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
-        "config": {"workload": f"{args.workload}: 16,384 molecule-like graphs per GPU, d=128, L=4, hidden=256"
-                   if args.workload == "molecules" else "proteins: 4,096 protein-like graphs per GPU, d=64, L=5",
+        "config": {"workload": WORKLOAD_TEXT[args.workload],
                    "sample": f"first {sample.num_graphs} graphs ({sample.num_nodes} nodes, {sample.num_edges} edges) per step"},
         "cpu_baseline": {"value": value, "unit": "graphs/s", "cores": cores, "kind": kind,
                          "sample": f"FactorGraph::FeedForward on the first {sample.num_graphs} graphs of the batch, "
@@ -314,10 +357,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "metric": METRIC, "value": world * G * args.steps / (elapsed_ms * 1e-3), "unit": "graphs/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": ("molecules_16k: 16,384 molecule-like graphs per GPU (20-40 nodes, tree + 10% edges, "
-                                    "82 Zipf(1.2) tags), d=128, L=4, hidden=256, C=2, sum pooling" if args.workload == "molecules"
-                                    else "proteins_4k: 4,096 protein-like graphs per GPU (100-620 nodes, mean degree ~7.4), "
-                                    "d=64, L=5, hidden=128"),
+            "config": {"workload": WORKLOAD_TEXT[args.workload],
                        "graphs_per_gpu": G, "nodes_per_gpu": N, "edges_per_gpu": E, "parallelism": f"shard-by-graph x{world}",
                        "l2": "per-step working set (3 x [N x d] fp32, > 700 MB) exceeds the 126 MB L2; no flush needed",
                        "input_digest": full.digest()},
@@ -347,13 +387,92 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+def run_giant(args, rank: int, world: int, local_rank: int):
+    """Single giant R-MAT graph, row-partitioned: 2 levels of ReLU(A*H*W), d = 128, one NCCL
+    all-gather of the embedding slabs per level, pipelined against the compute."""
+    import torch
+    import torch.distributed as dist
+    from graphnn_b200 import capi, giant
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = capi.Context(local_rank)
+    d, levels, scale = 128, 2, args.scale
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.synchronize()
+    torch.cuda.set_stream(stream)
+    shard = giant.rmat_shard_on_device(scale, 16 << scale, rank, world, dev, seed=0)
+    plan = giant.plan_hubs(shard, threshold=2048, piece=512)
+    spmm_fn, segsum_fn = giant.make_gpu_hub_fns(ctx)
+    g = giant.GiantGraphLevels(shard, d, rank, world, giant.make_gpu_level_fn(ctx), chunks=4, hub_plan=plan,
+                               spmm_fn=spmm_fn, segsum_fn=segsum_fn)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    slab0 = torch.randn((shard.rows, d), device=dev, generator=gen)
+    gen.manual_seed(99)
+    W = torch.randn((d, d), device=dev, generator=gen) * 0.05
+    nnz_local = torch.tensor([shard.nnz], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(nnz_local)
+    nnz_total = int(nnz_local.item())
+
+    def step():
+        g.set_input(slab0)
+        g.run(W, levels)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches0 = ctx.launches
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        t0.record(stream)
+        for _ in range(args.steps):
+            step()
+        t1.record(stream)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    times = torch.tensor([t0.elapsed_time(t1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms = float(times.item())
+    if rank == 0:
+        peak_gbs, peak_kind = measured_peaks()
+        n = 1 << scale
+        per_level = 4 * (n + 1) + 4 * nnz_total + 4 * nnz_total * d + 4 * n * d + 4 * d * d   # gather model, all ranks
+        sec_per_level = ms * 1e-3 / args.steps / levels
+        line = {"metric": "s2v_level_edges_per_sec", "value": nnz_total * levels * args.steps / (ms * 1e-3), "unit": "edges/s",
+                "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": f"giant R-MAT(0.57,0.19,0.19,0.05) scale {scale}, {16 << scale} generated edges, symmetrised + deduplicated "
+                                       f"to nnz={nnz_total}, d=128, 2 levels of ReLU(A*H*W), row-partitioned x{world}",
+                           "all_gather_bytes_per_gpu_per_level": g.all_gather_bytes_per_level(), "chunks": 4,
+                           "hub_rows_rank0": 0 if plan is None else plan.n_hub,
+                           "l2": "H (N x 128 fp32) far exceeds the 126 MB L2"},
+                "gpu_launches": int(ctx.launches - launches0),
+                "roofline": {"kernel": "fused level, gather model, time includes the pipelined all-gather", "bound": "hbm",
+                             "achieved": per_level / world / sec_per_level / 1e9, "peak": peak_gbs, "unit": "GB/s",
+                             "frac": per_level / world / sec_per_level / 1e9 / peak_gbs, "peak_kind": peak_kind, "traffic": None},
+                "clocks": clocks.summary()}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="molecules", choices=["molecules", "proteins"])
+    ap.add_argument("--workload", default="molecules", choices=["molecules", "proteins", "giant"])
+    ap.add_argument("--scale", type=int, default=24, help="giant workload: log2 of the node count (26 = the full configuration)")
     ap.add_argument("--skip-level", action="store_true", help="leave out the 1M-node fused-level measurement")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -364,6 +483,14 @@ def main():
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29511", os.path.abspath(__file__)] + sys.argv[1:]
         raise SystemExit(subprocess.call(cmd))
+    if args.workload == "giant":
+        if args.impl == "reference":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the reference is int32 and single-GPU; the giant-graph "
+                                  "configuration has no reference run at this size (scale-20 parity is in tests/test_giant_graph.py)"}))
+            return
+        run_giant(args, rank, world, local_rank)
+        return
     if args.impl == "reference":
         args.warmup = max(args.warmup, 1)   # the reference's first FeedForward of a batch size is many times slower
         run_reference(args, rank, world)

@@ -1,0 +1,272 @@
+"""One giant graph, row-partitioned over the ranks of a job.
+
+Rank p owns rows [p*N/P, (p+1)*N/P) of the CSR matrix A (all columns) and of every
+embedding matrix.  A level needs the whole H as its gather source, so each level is
+
+    all-gather of the [N/P x d] slabs  ->  fused level kernel on the local rows (n_src = N)
+
+The only exchange step of the path is that all-gather (NCCL over NVLink; the reference has
+no multi-GPU code at all).  It is pipelined against the compute: the local rows are cut
+into `chunks` row blocks and block k of level l is all-gathered (on a side stream) while
+block k+1 is still being computed, so that level l+1 finds H complete soon after level l's
+last block.  Remote rows always land in local HBM first; the kernel never reads peer memory.
+
+The compute step is injectable (`level_fn`) so that the partition / exchange logic can be
+exercised on CPU ranks (gloo) with any reference implementation of a level.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def row_range(n_rows: int, rank: int, world: int) -> tuple[int, int]:
+    """Equal row slabs (N must be divisible by the world size; pad the graph otherwise)."""
+    if n_rows % world:
+        raise ValueError(f"{n_rows} rows do not divide over {world} ranks; pad the graph with isolated nodes")
+    per = n_rows // world
+    return rank * per, (rank + 1) * per
+
+
+@dataclass
+class CsrShard:
+    """Rows [row_lo, row_hi) of a CSR matrix with n_cols columns; row_ptr is rebased to 0."""
+
+    row_lo: int
+    row_hi: int
+    n_cols: int
+    row_ptr: torch.Tensor   # int32 or int64 [rows+1]
+    col_idx: torch.Tensor   # int32 [nnz_local]
+
+    @property
+    def rows(self) -> int:
+        return self.row_hi - self.row_lo
+
+    @property
+    def nnz(self) -> int:
+        return int(self.col_idx.shape[0])
+
+
+def shard_csr(row_ptr: np.ndarray, col_idx: np.ndarray, n_cols: int, rank: int, world: int, device=None) -> CsrShard:
+    n_rows = len(row_ptr) - 1
+    lo, hi = row_range(n_rows, rank, world)
+    rp = row_ptr[lo:hi + 1].astype(np.int64)
+    base = int(rp[0])
+    ci = col_idx[base:int(rp[-1])]
+    rp = rp - base
+    rp = rp.astype(np.int32 if rp[-1] < 2 ** 31 else np.int64)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device) if device is not None else torch.from_numpy(np.ascontiguousarray(a))
+    return CsrShard(lo, hi, n_cols, t(rp), t(ci.astype(np.int32)))
+
+
+def rmat_shard_on_device(scale: int, num_edges: int, rank: int, world: int, device, a=0.57, b=0.19, c=0.19, seed=0,
+                         chunk=1 << 26) -> CsrShard:
+    """Symmetrised, deduplicated R-MAT(a,b,c,d) graph with 2^scale nodes, generated on the
+    device: every rank draws the same edge stream (counter-based: the generator is re-seeded
+    per chunk with (seed, chunk index)) and keeps the directed copies whose row falls in its
+    slab, then sorts and deduplicates only those.  Self loops are kept as generated."""
+    n = 1 << scale
+    lo, hi = row_range(n, rank, world)
+    keys = []
+    gen = torch.Generator(device=device)
+    for ci, start in enumerate(range(0, num_edges, chunk)):
+        m = min(chunk, num_edges - start)
+        gen.manual_seed(seed * 1000003 + ci)
+        s = torch.zeros(m, dtype=torch.int64, device=device)
+        t = torch.zeros(m, dtype=torch.int64, device=device)
+        for _ in range(scale):
+            r = torch.rand(m, device=device, generator=gen)
+            right = ((r >= a) & (r < a + b)) | (r >= a + b + c)
+            down = r >= a + b
+            s = (s << 1) | down
+            t = (t << 1) | right
+        for row, col in ((s, t), (t, s)):
+            keep = (row >= lo) & (row < hi)
+            keys.append(((row[keep] - lo) << scale) | col[keep])
+        del s, t, r, right, down, keep
+    key = torch.unique(torch.cat(keys))          # sorted by (local row, column), duplicates removed
+    del keys
+    rows_local = key >> scale
+    col = (key & (n - 1)).to(torch.int32)
+    counts = torch.bincount(rows_local, minlength=hi - lo)
+    row_ptr = torch.zeros(hi - lo + 1, dtype=torch.int64, device=device)
+    torch.cumsum(counts, 0, out=row_ptr[1:])
+    if int(row_ptr[-1]) < 2 ** 31:
+        row_ptr = row_ptr.to(torch.int32)
+    return CsrShard(lo, hi, n, row_ptr, col)
+
+
+@dataclass
+class HubPlan:
+    """Rows whose degree exceeds a threshold ("hubs" of a power-law graph) would each be summed
+    by a single warp.  They are taken out of the level's CSR: a hub row keeps ONE entry that
+    points at an extra source row N + h, and that row is filled, before the level runs, by
+    two small launches that sum the hub's neighbours in parallel: partial sums over
+    sub-rows of `piece` entries (CSR x dense), then an in-order sum of each hub's partials
+    (segmented sum).  Deterministic; no atomics."""
+
+    n_hub: int
+    light: CsrShard            # the shard with hub rows collapsed to one entry (columns may be >= n_cols)
+    sub_row_ptr: torch.Tensor  # int32 [n_sub+1]  sub-rows of the hubs' entries
+    sub_col_idx: torch.Tensor  # int32 [hub nnz]
+    hub_seg_ptr: torch.Tensor  # int32 [n_hub+1]  consecutive sub-rows of every hub
+
+    @property
+    def n_sub(self) -> int:
+        return int(self.sub_row_ptr.shape[0]) - 1
+
+
+def plan_hubs(shard: CsrShard, threshold: int = 2048, piece: int = 512) -> HubPlan | None:
+    rp = shard.row_ptr.to(torch.int64)
+    deg = rp[1:] - rp[:-1]
+    is_hub = deg > threshold
+    n_hub = int(is_hub.sum())
+    if n_hub == 0:
+        return None
+    dev = rp.device
+    hub_rows = torch.nonzero(is_hub).flatten()
+    hub_deg = deg[hub_rows]
+    # entries that belong to hub rows, in CSR order
+    row_of_edge = torch.repeat_interleave(torch.arange(shard.rows, device=dev), deg)
+    edge_is_hub = is_hub[row_of_edge]
+    sub_col = shard.col_idx[edge_is_hub].contiguous()
+    # sub-rows: every hub is cut into ceil(deg/piece) consecutive pieces
+    pieces = (hub_deg + piece - 1) // piece
+    hub_seg = torch.zeros(n_hub + 1, dtype=torch.int64, device=dev)
+    torch.cumsum(pieces, 0, out=hub_seg[1:])
+    n_sub = int(hub_seg[-1])
+    hub_of_sub = torch.repeat_interleave(torch.arange(n_hub, device=dev), pieces)
+    idx_in_hub = torch.arange(n_sub, device=dev) - hub_seg[hub_of_sub]
+    hub_start = torch.zeros(n_hub + 1, dtype=torch.int64, device=dev)
+    torch.cumsum(hub_deg, 0, out=hub_start[1:])
+    sub_len = torch.minimum(torch.full_like(idx_in_hub, piece), hub_deg[hub_of_sub] - idx_in_hub * piece)
+    sub_rp = torch.zeros(n_sub + 1, dtype=torch.int64, device=dev)
+    torch.cumsum(sub_len, 0, out=sub_rp[1:])
+    # light CSR: hub rows keep one entry -> extra source row n_cols + h
+    new_deg = torch.where(is_hub, torch.ones_like(deg), deg)
+    light_rp = torch.zeros(shard.rows + 1, dtype=torch.int64, device=dev)
+    torch.cumsum(new_deg, 0, out=light_rp[1:])
+    light_col = torch.empty(int(light_rp[-1]), dtype=torch.int32, device=dev)
+    keep = ~edge_is_hub
+    new_pos_light = light_rp[:-1][row_of_edge[keep]] + (torch.arange(shard.nnz, device=dev)[keep] - rp[:-1][row_of_edge[keep]])
+    light_col[new_pos_light] = shard.col_idx[keep]
+    light_col[light_rp[:-1][hub_rows]] = (shard.n_cols + torch.arange(n_hub, device=dev)).to(torch.int32)
+    rp_dtype = torch.int32 if int(light_rp[-1]) < 2 ** 31 else torch.int64
+    light = CsrShard(shard.row_lo, shard.row_hi, shard.n_cols, light_rp.to(rp_dtype), light_col)
+    return HubPlan(n_hub, light, sub_rp.to(torch.int32), sub_col, hub_seg.to(torch.int32))
+
+
+class GiantGraphLevels:
+    """L levels  H <- ReLU(A*H*W [+ X])  on a row-partitioned graph."""
+
+    def __init__(self, shard: CsrShard, d: int, rank: int, world: int, level_fn, chunks: int = 4, group=None,
+                 hub_plan: HubPlan | None = None, spmm_fn=None, segsum_fn=None):
+        self.hub = hub_plan
+        self.spmm_fn, self.segsum_fn = spmm_fn, segsum_fn
+        if hub_plan is not None:
+            assert spmm_fn is not None and segsum_fn is not None
+            shard = hub_plan.light
+        self.shard, self.d, self.rank, self.world, self.level_fn = shard, d, rank, world, level_fn
+        self.chunks = max(1, min(chunks, shard.rows))
+        self.group = group
+        dev = shard.col_idx.device
+        self.device = dev
+        extra = hub_plan.n_hub if hub_plan is not None else 0       # rank-private source rows N .. N+n_hub
+        self.full = [torch.empty((shard.n_cols + extra, d), dtype=torch.float32, device=dev) for _ in range(2)]
+        self.partial = torch.empty((hub_plan.n_sub, d), dtype=torch.float32, device=dev) if hub_plan is not None else None
+        self.comm_stream = torch.cuda.Stream(device=dev) if dev.type == "cuda" else None
+        # row blocks of the local slab
+        rows = shard.rows
+        edges = [rows * k // self.chunks for k in range(self.chunks + 1)]
+        self.blocks = [(edges[k], edges[k + 1]) for k in range(self.chunks) if edges[k + 1] > edges[k]]
+        rp = shard.row_ptr
+        self._block_rp = []
+        for lo, hi in self.blocks:
+            seg = rp[lo:hi + 1]
+            self._block_rp.append((seg - seg[0]).contiguous())
+        self._block_base = [int(rp[lo]) for lo, _ in self.blocks]
+        self._block_nnz = [int(rp[hi]) - int(rp[lo]) for lo, hi in self.blocks]
+
+    def all_gather_bytes_per_level(self) -> int:
+        return (self.world - 1) * self.shard.rows * self.d * 4
+
+    def _gather_block(self, full: torch.Tensor, lo: int, hi: int):
+        """All-gather rows [lo, hi) of every rank's slab into `full` (in place).  Block k of rank r
+        lives at rows r*rows + [lo, hi); the ranks' pieces are not contiguous in `full`, so the
+        collective runs on views collected in a list."""
+        if self.world == 1:
+            return
+        rows = self.shard.rows
+        outs = [full[r * rows + lo:r * rows + hi] for r in range(self.world)]
+        dist.all_gather(outs, full[self.rank * rows + lo:self.rank * rows + hi], group=self.group)
+
+    def set_input(self, slab: torch.Tensor):
+        """Local slab of H0 -> full H0 on every rank."""
+        rows = self.shard.rows
+        self.full[0][self.rank * rows:(self.rank + 1) * rows].copy_(slab)
+        self._gather_block(self.full[0], 0, rows)
+        self.cur = 0
+
+    def run(self, W: torch.Tensor, levels: int, X_slab: torch.Tensor | None = None) -> torch.Tensor:
+        """Returns the local slab of H_L (a view into the rank's full copy)."""
+        rows = self.shard.rows
+        for _ in range(levels):
+            src, dst = self.full[self.cur], self.full[1 - self.cur]
+            events = []
+            if self.hub is not None:   # hub sums of this level -> the extra source rows of `src`
+                n = self.shard.n_cols
+                self.spmm_fn(self.hub.sub_row_ptr, self.hub.sub_col_idx, src[:n], self.partial)
+                self.segsum_fn(self.hub.hub_seg_ptr, self.partial, src[n:])
+            for k, (lo, hi) in enumerate(self.blocks):
+                out_rows = dst[self.rank * rows + lo:self.rank * rows + hi]
+                base = self._block_base[k]
+                nnz = self._block_nnz[k]
+                self.level_fn(self._block_rp[k], self.shard.col_idx[base:base + nnz], src, W,
+                              None if X_slab is None else X_slab[lo:hi], out_rows)
+                if self.world > 1:
+                    if self.comm_stream is not None:
+                        ev = torch.cuda.Event()
+                        ev.record(torch.cuda.current_stream())
+                        with torch.cuda.stream(self.comm_stream):
+                            self.comm_stream.wait_event(ev)
+                            self._gather_block(dst, lo, hi)
+                            done = torch.cuda.Event()
+                            done.record(self.comm_stream)
+                        events.append(done)
+                    else:
+                        self._gather_block(dst, lo, hi)
+            for ev in events:          # the next level reads every row of dst
+                torch.cuda.current_stream().wait_event(ev)
+            self.cur = 1 - self.cur
+        return self.full[self.cur][self.rank * rows:(self.rank + 1) * rows]
+
+
+def make_gpu_hub_fns(ctx):
+    """(spmm_fn, segsum_fn) for HubPlan on the library's kernels, torch's current stream."""
+
+    def spmm_fn(row_ptr, col_idx, H, out):
+        st = torch.cuda.current_stream().cuda_stream
+        assert st != 0
+        ctx.spmm(out.shape[0], H.shape[0], row_ptr, col_idx, None, H, out, stream=st)
+
+    def segsum_fn(seg_ptr, partial, out):
+        st = torch.cuda.current_stream().cuda_stream
+        assert st != 0
+        ctx.segment_sum(seg_ptr, partial, out, stream=st)
+
+    return spmm_fn, segsum_fn
+
+
+def make_gpu_level_fn(ctx):
+    """level_fn running the library's fused level kernel on torch's current stream (which must
+    not be the legacy default stream: handle 0 selects the library's own stream)."""
+
+    def level_fn(row_ptr, col_idx, H_full, W, X, out_rows):
+        st = torch.cuda.current_stream().cuda_stream
+        assert st != 0, "make a torch.cuda.Stream current before running giant-graph levels"
+        ctx.level(row_ptr, col_idx, None, H_full, W, X, out_rows, n_src=H_full.shape[0], stream=st)
+
+    return level_fn
