@@ -242,7 +242,11 @@ def level_cfg2(ctx, torch, peak_gbs, peak_kind):
     return {"workload": "fused level, Erdos-Renyi n=1048576 nnz=8388608 d=64, ReLU(A*H*W+X)", "ms": mean_ms,
             "ms_min": ms[0], "bound": "hbm", "achieved": ach, "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs,
             "peak_kind": peak_kind, "bytes_gather_model": gather, "bytes_compulsory_model": comp,
-            "edges_per_sec": p.nnz / (mean_ms * 1e-3), "traffic": None, "launches": iters,
+            "edges_per_sec": p.nnz / (mean_ms * 1e-3),
+            # dram__bytes_read + dram__bytes_write of one launch on the half-size problem
+            # (profiles/level_mma_tf32x3.md: 696.27 MB + 118.74 MB), times two
+            "traffic": 2 * (696272384 + 118737152), "traffic_note": "ncu capture at n=524,288, scaled x2",
+            "launches": iters,
             "l2_note": "H (268 MB) + X + out exceed the 126 MB L2"}
 
 
@@ -325,28 +329,35 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     logits_h = np.empty((G, C), np.float32)
     pred_h = np.empty((G,), np.int32)
 
-    def e2e_step():
-        lib = ctx.lib
-        rc = lib.s2v_build_n2n_csr_host(N, E, es.ctypes.data, ed.ctypes.data, 0, hb.row_ptr.data_ptr(),
-                                        hb.col_idx.data_ptr(), None)
-        assert rc == 0
+    def e2e_step(build_csr: bool):
+        if build_csr:
+            rc = ctx.lib.s2v_build_n2n_csr_host(N, E, es.ctypes.data, ed.ctypes.data, 0, hb.row_ptr.data_ptr(),
+                                                hb.col_idx.data_ptr(), None)
+            assert rc == 0
         eng.infer_host(hb, logits_h, pred_h)
 
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    e2e_steps = max(3, min(args.steps, 20))
-    w0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - w0) * 1e3
+    e2e_steps = max(3, min(args.steps, 50))
+
+    def time_e2e(build_csr: bool) -> float:
+        for _ in range(3):
+            e2e_step(build_csr)
+        barrier()
+        w0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step(build_csr)
+        torch.cuda.synchronize()
+        return (time.perf_counter() - w0) * 1e3
+
+    # headline e2e: what one FeedForward of the reference times -- adjacency already grouped per node
+    # (host CSR here, GraphStruct lists there), uploads, forward, download
+    e2e_ms = time_e2e(False)
+    e2e_build_ms = time_e2e(True)      # additionally sorting a raw edge list into the CSR on the host
     assert np.array_equal(pred_h, pred.cpu().numpy()), "host-buffer path and device path disagree"
 
-    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
+    times = torch.tensor([elapsed_ms, e2e_ms, e2e_build_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms = (float(x) for x in times.cpu())
+    elapsed_ms, e2e_ms, e2e_build_ms = (float(x) for x in times.cpu())
 
     if rank == 0:
         peak_gbs, peak_kind = measured_peaks()
@@ -364,10 +375,16 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "e2e": {"value": world * G * e2e_steps / (e2e_ms * 1e-3), "unit": "graphs/s",
                     "h2d_bytes_per_step": hb.nbytes(), "d2h_bytes_per_step": int(logits_h.nbytes + pred_h.nbytes),
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
-                    "includes": "host CSR build from the edge list, pinned uploads, forward, download of logits and predictions"},
+                    "includes": "s2v_infer_host_f32 on pinned host CSR + tags: uploads, forward, download of logits and predictions",
+                    "from_edge_list": {"value": world * G * e2e_steps / (e2e_build_ms * 1e-3), "ms_per_step": e2e_build_ms / e2e_steps,
+                                       "includes": "the same plus s2v_build_n2n_csr_host (stable sort of the raw edge list)"}},
             "gpu_launches": int(launches),
-            "roofline": {"kernel": "s2v_level_kernel<128> (X looked up from W_in by tag)", "bound": "hbm", "achieved": ach,
-                         "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs, "peak_kind": peak_kind, "traffic": None,
+            "roofline": {"kernel": ("s2v_level_tc_kernel (tcgen05, d=128, X looked up from W_in by tag)" if d == 128 else
+                                    f"s2v_level_kernel<{d}> (X looked up from W_in by tag)"), "bound": "hbm", "achieved": ach,
+                         "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs, "peak_kind": peak_kind,
+                         # dram__bytes_read + dram__bytes_write of one launch on this very input
+                         # (profiles/level_tcgen05_d128.md); only known for the default workload
+                         "traffic": (259829760 + 202716416) if args.workload == "molecules" else None,
                          "ms_per_launch": level_ms, "launches": len(level_events), "bytes_per_launch": comp,
                          "model": "compulsory (each H row once) + CSR + tags + out + W",
                          "achieved_with_dense_X_model": survey / (level_ms * 1e-3) / 1e9},

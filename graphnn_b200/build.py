@@ -19,7 +19,7 @@ LIB = os.path.join(PKG, "libs2v_b200.so")
 OBJ_DIR = os.path.join(PKG, "build")
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
-              "-Xcompiler", "-fPIC", "-I", os.path.join(REPO, "include"), "-I", CSRC]
+              "-Xcompiler", "-fPIC,-fopenmp", "-I", os.path.join(REPO, "include"), "-I", CSRC]
 
 
 def _stale(target: str, deps: list[str]) -> bool:
@@ -49,7 +49,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     with ThreadPoolExecutor(max_workers=min(8, len(sources))) as ex:
         objs = list(ex.map(compile_one, sources))
     if force or _stale(LIB, objs):
-        r = subprocess.run([nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a"],
+        r = subprocess.run([nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-lgomp"],
                            capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

@@ -1,5 +1,7 @@
 // C ABI glue of s2v_b200: context life cycle, argument validation, the whole-model
 // pipelines (device buffers and host buffers) and the host-side CSR builders.
+#include <omp.h>
+
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
@@ -280,19 +282,105 @@ int s2v_build_n2n_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* 
     if (num_nodes < 0 || num_edges < 0 || !row_ptr) return S2V_ERR_INVALID_ARG;
     if (num_edges > 0 && (!edge_src || !edge_dst || !col_idx)) return S2V_ERR_INVALID_ARG;
     if (num_edges >= (int64_t)INT32_MAX || num_nodes >= (int64_t)INT32_MAX) return S2V_ERR_UNSUPPORTED;
-    // Stable counting sort by destination: row y receives its sources in edge order,
+    // A stable sort of the edge list by destination: row y receives its sources in edge order,
     // which is the order GraphStruct::AddEdge appended them to in_edges[y].
-    std::vector<int32_t> fill((size_t)num_nodes + 1, 0);
-    for (int64_t e = 0; e < num_edges; ++e) {
-        const int32_t y = edge_dst[e], x = edge_src[e];
-        if (y < 0 || y >= num_nodes || x < 0 || x >= num_nodes) return S2V_ERR_BAD_CSR;
-        fill[(size_t)y + 1]++;
+    const int64_t N = num_nodes, E = num_edges;
+    int T = omp_get_max_threads();
+    if (T > 16) T = 16;
+    if (E < (1 << 16) || T < 2) {
+        // small batch: one thread, plain counting sort
+        std::vector<int32_t> fill((size_t)N + 1, 0);
+        for (int64_t e = 0; e < E; ++e) {
+            const int32_t y = edge_dst[e], x = edge_src[e];
+            if (y < 0 || y >= N || x < 0 || x >= N) return S2V_ERR_BAD_CSR;
+            fill[(size_t)y + 1]++;
+        }
+        for (int64_t i = 0; i < N; ++i) fill[i + 1] += fill[i];
+        std::memcpy(row_ptr, fill.data(), sizeof(int32_t) * ((size_t)N + 1));
+        for (int64_t e = 0; e < E; ++e) col_idx[fill[edge_dst[e]]++] = edge_src[e];
+    } else {
+        // large batch: the same stable sort in three parallel passes.
+        //   1. every thread histograms its contiguous slice of the edge list over NB buckets of
+        //      consecutive rows;  2. slices scatter their edges into bucket-partitioned scratch,
+        //      slice after slice, so the edge order inside a bucket is kept;  3. buckets are
+        //      finished independently (counting sort over the bucket's few hundred rows).
+        int shift = 0;   // a bucket is 2^shift consecutive rows; at most 2048 buckets
+        while (((N - 1) >> shift) >= 2048) ++shift;
+        const int64_t rows_per_bucket = (int64_t)1 << shift;
+        const int NB = (int)((N + rows_per_bucket - 1) >> shift);
+        static thread_local std::vector<int32_t> scratch;   // grow-only: (src, dst) pairs by bucket
+        if (scratch.size() < (size_t)(2 * E)) scratch.resize((size_t)(2 * E));
+        int32_t* tmp_src = scratch.data();
+        int32_t* tmp_dst = scratch.data() + E;
+        std::vector<int64_t> hist((size_t)T * NB, 0), bucket_start(NB + 1, 0);
+        int bad = 0;
+#pragma omp parallel num_threads(T)
+        {
+            const int t = omp_get_thread_num();
+            const int64_t e0 = E * t / T, e1 = E * (t + 1) / T;
+            int64_t* h = hist.data() + (size_t)t * NB;
+            int local_bad = 0;
+            for (int64_t e = e0; e < e1; ++e) {
+                const int32_t y = edge_dst[e], x = edge_src[e];
+                if (y < 0 || y >= N || x < 0 || x >= N) { local_bad = 1; break; }
+                h[y >> shift]++;
+            }
+            if (local_bad) {
+#pragma omp atomic write
+                bad = 1;
+            }
+#pragma omp barrier
+#pragma omp single
+            {
+                if (!bad) {
+                    int64_t run = 0;
+                    for (int b = 0; b < NB; ++b) {
+                        bucket_start[b] = run;
+                        for (int tt = 0; tt < T; ++tt) {
+                            const int64_t c = hist[(size_t)tt * NB + b];
+                            hist[(size_t)tt * NB + b] = run;   // becomes this slice's write cursor in bucket b
+                            run += c;
+                        }
+                    }
+                    bucket_start[NB] = run;
+                }
+            }   // implicit barrier
+            if (!bad) {
+                for (int64_t e = e0; e < e1; ++e) {
+                    const int32_t y = edge_dst[e];
+                    const int64_t pos = h[y >> shift]++;
+                    tmp_src[pos] = edge_src[e];
+                    tmp_dst[pos] = y;
+                }
+            }
+#pragma omp barrier
+            if (!bad) {
+                std::vector<int32_t> cnt((size_t)rows_per_bucket + 1);
+#pragma omp for schedule(dynamic, 8)
+                for (int b = 0; b < NB; ++b) {
+                    const int64_t r0 = (int64_t)b * rows_per_bucket;
+                    const int64_t r1 = std::min(N, r0 + rows_per_bucket);
+                    if (r0 >= r1) continue;
+                    const int64_t s0 = bucket_start[b], s1 = bucket_start[b + 1];
+                    std::fill(cnt.begin(), cnt.begin() + (r1 - r0) + 1, 0);
+                    for (int64_t p = s0; p < s1; ++p) cnt[tmp_dst[p] - r0 + 1]++;
+                    int32_t run = (int32_t)s0;
+                    for (int64_t r = r0; r < r1; ++r) {
+                        const int32_t c = cnt[r - r0 + 1];
+                        row_ptr[r] = run;
+                        cnt[r - r0 + 1] = run;   // write cursor of row r
+                        run += c;
+                    }
+                    for (int64_t p = s0; p < s1; ++p) col_idx[cnt[tmp_dst[p] - r0 + 1]++] = tmp_src[p];
+                }
+            }
+        }
+        if (bad) return S2V_ERR_BAD_CSR;
+        row_ptr[N] = (int32_t)E;
     }
-    for (int64_t i = 0; i < num_nodes; ++i) fill[i + 1] += fill[i];
-    std::memcpy(row_ptr, fill.data(), sizeof(int32_t) * ((size_t)num_nodes + 1));
-    for (int64_t e = 0; e < num_edges; ++e) col_idx[fill[edge_dst[e]]++] = edge_src[e];
     if (val) {
-        for (int64_t i = 0; i < num_nodes; ++i) {
+#pragma omp parallel for num_threads(T) schedule(static) if (E >= (1 << 16))
+        for (int64_t i = 0; i < N; ++i) {
             const int32_t deg = row_ptr[i + 1] - row_ptr[i];
             const float v = average ? (float)(1.0 / deg) : 1.0f;
             for (int32_t t = row_ptr[i]; t < row_ptr[i + 1]; ++t) val[t] = v;
