@@ -61,6 +61,7 @@ def load_library():
         "s2v_level_f32": (i32, [vp, vp, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp]),
         "s2v_level_rp64_f32": (i32, [vp, vp, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp]),
         "s2v_level_lookup_f32": (i32, [vp, vp, i64, i64, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp]),
+        "s2v_level_first_f32": (i32, [vp, vp, i64, i32, vp, vp, vp, vp, vp, i32, vp, vp]),
         "s2v_spmm_csr_f32": (i32, [vp, vp, i64, i64, i32, vp, vp, vp, vp, f32, f32, vp]),
         "s2v_gemm_f32": (i32, [vp, vp, i32, i32, i64, i64, i64, f32, vp, i64, vp, i64, f32, vp, i64]),
         "s2v_axpy_f32": (i32, [vp, vp, i64, f32, vp, vp]),
@@ -68,6 +69,12 @@ def load_library():
         "s2v_relu_f32": (i32, [vp, vp, i64, vp, vp]),
         "s2v_softmax_f32": (i32, [vp, vp, i64, i32, vp, vp]),
         "s2v_argmax_f32": (i32, [vp, vp, i64, i32, vp, vp]),
+        "s2v_cross_entropy_f32": (i32, [vp, vp, i64, i32, vp, i32, vp, vp, vp, vp]),
+        "s2v_argmax_csr_f32": (i32, [vp, vp, i64, vp, vp, vp, vp]),
+        "s2v_in_top_k_f32": (i32, [vp, vp, i64, i32, vp, vp, i32, vp]),
+        "s2v_cast_i32_f32": (i32, [vp, vp, i64, vp, vp]),
+        "s2v_mean_f32": (i32, [vp, vp, i64, vp, vp]),
+        "s2v_loss_acc_f32": (i32, [vp, vp, i64, i32, vp, vp, vp, vp, i32, vp, vp, vp]),
         "s2v_segment_sum_f32": (i32, [vp, vp, i64, i32, vp, vp, vp]),
         "s2v_readout_f32": (i32, [vp, vp, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp]),
         "s2v_input_proj_onehot_f32": (i32, [vp, vp, i64, i32, i32, vp, vp, vp, vp]),
@@ -183,6 +190,12 @@ class Context:
                   _ptr(H), _ptr(W), _ptr(table), table.shape[0], _ptr(x_index), _ptr(out))
         return out
 
+    def level_first(self, row_ptr, col_idx, val, W, table, tags, out, stream=None):
+        n, d = out.shape
+        self.call("s2v_level_first_f32", stream, n, d, _ptr(row_ptr), _ptr(col_idx), _ptr(val), _ptr(W), _ptr(table),
+                  table.shape[0], _ptr(tags), _ptr(out))
+        return out
+
     def spmm(self, m, k, row_ptr, col_idx, val, B, C_out, alpha=1.0, beta=0.0, stream=None):
         self.call("s2v_spmm_csr_f32", stream, m, k, B.shape[1], _ptr(row_ptr), _ptr(col_idx), _ptr(val), _ptr(B),
                   alpha, beta, _ptr(C_out))
@@ -215,6 +228,10 @@ class Context:
     def argmax(self, x, out, stream=None):
         self.call("s2v_argmax_f32", stream, x.shape[0], x.shape[1], _ptr(x), _ptr(out))
         return out
+
+    def loss_acc(self, logits, label_rp, label_ci, label_val, loss, acc, per_graph=None, topk=1, stream=None):
+        self.call("s2v_loss_acc_f32", stream, logits.shape[0], logits.shape[1], _ptr(logits), _ptr(label_rp), _ptr(label_ci),
+                  _ptr(label_val), topk, _ptr(loss), _ptr(acc), _ptr(per_graph))
 
     def segment_sum(self, seg_ptr, H, Y, stream=None):
         self.call("s2v_segment_sum_f32", stream, Y.shape[0], H.shape[1], _ptr(seg_ptr), _ptr(H), _ptr(Y))

@@ -207,6 +207,23 @@ int s2v_level_lookup_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_
                             nullptr, table, x_index, out);
 }
 
+int s2v_level_first_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n, int d, const int32_t* row_ptr, const int32_t* col_idx,
+                        const float* val, const float* W, const float* table, int n_table, const int32_t* tags, float* out)
+{
+    S2V_ENTER(ctx);
+    if (n < 0 || d <= 0 || n_table <= 0) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level_first: bad shape");
+    if (n == 0) return S2V_OK;
+    if (!row_ptr || !W || !table || !tags || !out) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level_first: NULL pointer");
+    if (!s2v_aligned16(W) || !s2v_aligned16(table) || !s2v_aligned16(out))
+        return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level_first: W, table, out must be 16-byte aligned");
+    if (d != 128 || ctx->tc_mode == 0 || (ctx->tc_mode == 1 && n < S2V_TC_MIN_ROWS))
+        return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "level_first: only the d = 128 tcgen05 kernel has this form; materialise H0 instead");
+    const int rc = s2v_launch_level_tc(ctx, s2v_pick_stream(ctx, stream), n, d, row_ptr, col_idx, val, nullptr, W, nullptr, table,
+                                       tags, out);
+    if (rc == S2V_ERR_UNSUPPORTED) return s2v_fail(ctx, rc, "level_first: shape not supported by the tcgen05 kernel");
+    return rc;
+}
+
 // ---------------------------------------------------------------- whole model, device buffers
 size_t s2v_forward_workspace_bytes(int64_t num_nodes, int64_t num_graphs, int d)
 {
@@ -246,7 +263,18 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
     // With one-hot tags the X term of every level is a lookup in W_in, so `msg` is
     // never materialised; a dense X needs it.
     const bool onehot = batch->tags != nullptr && d % 4 == 0;
-    if (onehot)
+    // first level straight from the tags (no H0 in memory) when the tcgen05 kernel takes this shape
+    bool first_fused = false;
+    if (onehot && L >= 1 && d == 128 && (ctx->tc_mode == 2 || (ctx->tc_mode == 1 && N >= S2V_TC_MIN_ROWS))) {
+        float* dst = (L == 1 && embed_out) ? embed_out : ha;
+        rc = s2v_level_first_f32(ctx, st, N, d, batch->n2n_row_ptr, batch->n2n_col_idx, batch->n2n_val, model->p_node_conv,
+                                 model->w_n2l, model->num_feat, batch->tags, dst);
+        if (rc == S2V_OK) first_fused = true;
+        else if (rc != S2V_ERR_UNSUPPORTED) return rc;
+    }
+    if (first_fused)
+        rc = S2V_OK;
+    else if (onehot)
         rc = s2v_input_proj_onehot_f32(ctx, st, N, model->num_feat, d, batch->tags, model->w_n2l, nullptr, ha);
     else if (batch->tags)
         return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "forward: one-hot input needs d % 4 == 0");
@@ -254,9 +282,9 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
         rc = s2v_input_proj_dense_f32(ctx, st, N, model->num_feat, d, batch->x_dense, model->w_n2l, msg, ha);
     if (rc != S2V_OK) return rc;
 
-    float* cur = ha;
+    float* cur = (first_fused && L == 1 && embed_out) ? embed_out : ha;
     float* nxt = hb;
-    for (int lv = 0; lv < L; ++lv) {
+    for (int lv = first_fused ? 1 : 0; lv < L; ++lv) {
         float* dst = (lv == L - 1 && embed_out) ? embed_out : nxt;
         if (onehot)
             rc = s2v_level_lookup_f32(ctx, st, N, N, d, batch->n2n_row_ptr, batch->n2n_col_idx, batch->n2n_val, cur,

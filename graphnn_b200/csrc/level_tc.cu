@@ -9,10 +9,11 @@
 // above the HBM time.  tcgen05 runs the same 3xTF32 product about four times faster and
 // needs no registers for the operands, so the kernel goes back to being memory-bound.
 //
-// One persistent CTA per SM, 128-row tiles, three warp roles connected by mbarriers:
+// One persistent 768-thread CTA per SM, 128-row tiles, three warp roles connected by mbarriers:
 //
-//   gather warps (8)  : the tile's CSR slice -> shared memory, neighbour rows summed in
-//                       CSR order as one flat stream (8 loads in flight per lane) into a
+//   gather warps (16) : the tile's CSR slice -> shared memory, neighbour rows summed in
+//                       CSR order as one flat software-pipelined stream (4..8 loads in flight per
+//                       lane, indices prefetched a tile ahead) into a
 //                       fp32 staging tile [128 x 128];
 //   operand warps (4) : read the staging tile "transposed" (thread = row), split every
 //                       value into a TF32 head and tail and store both into tensor memory
@@ -34,13 +35,13 @@ namespace
 
 constexpr int TC_D = 128;
 constexpr int TC_TILE = 128;           // rows per tile = MMA M
-constexpr int TC_GW = 8;               // gather warps
+constexpr int TC_GW = 16;              // gather warps (measured: 16 x 4 loads per chunk beats 8 x 8)
 constexpr int TC_AW = 4;               // operand warps (one per tensor-memory lane quarter)
 constexpr int TC_EW = 4;               // epilogue warps
 constexpr int TC_THREADS = (TC_GW + TC_AW + TC_EW) * 32;
 constexpr int TC_ROWS_PER_GW = TC_TILE / TC_GW;   // 16
-constexpr int TC_U = 8;
-constexpr int TC_IDX_CAP = 128;
+constexpr int TC_U = 4;
+constexpr int TC_IDX_CAP = 64;
 constexpr int TC_STAGE_STRIDE = TC_D + 4;         // floats; 33 float4 per row: thread-per-row float4 reads are conflict-free
 constexpr int TC_OUT_STRIDE = 36;                 // floats; 9 float4 per row
 constexpr int TC_WAIT_LIMIT = 1 << 22;
@@ -144,7 +145,7 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_tmem, uint64_
 #define TC_TRACE_PRINT(role) do {} while (0)
 #endif
 
-template <bool HAS_VAL, int XMODE>
+template <bool HAS_VAL, int XMODE, bool HSRC_TABLE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict__ row_ptr,
                     const int32_t* __restrict__ col_idx, const float* __restrict__ val, const float* __restrict__ H,
@@ -254,7 +255,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             for (int j = 0; j < IPL; ++j)
                 idx_pref[j] = (nnz1 <= TC_IDX_CAP && lane + 32 * j < nnz1) ? col_idx[base1 + lane + 32 * j] : 0;
             TC_TRACE(0);
-            // Flat stream over the 16 rows' non-zeros, software-pipelined: the loads of chunk
+            // Flat stream over this warp's rows' non-zeros, software-pipelined: the loads of chunk
             // k+1 are in flight while chunk k is summed, and the first chunk is issued before
             // waiting for the staging tile, so the wait costs no memory latency.
             int row = 0;
@@ -264,9 +265,19 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             float* srow = stage + (size_t)(warp * TC_ROWS_PER_GW) * TC_STAGE_STRIDE + lane * 4;
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             float4 va[TC_U], vb[TC_U];
+// HSRC_TABLE: the gather source is not a matrix but ReLU(table[x_index[col], :]) -- the first level of
+// the classifier with one-hot inputs, where H0 = ReLU(W_in[tag]) need not be materialised
 #define TC_LOAD(v, t0)                                                                             \
     _Pragma("unroll") for (int u = 0; u < TC_U; ++u)                                               \
-        if ((t0) + u < ee) v[u] = ld_nc_f4(H4 + (int64_t)ip[(t0) + u] * LPR + lane);
+        if ((t0) + u < ee) {                                                                       \
+            if (HSRC_TABLE) {                                                                      \
+                const int tg = __ldg(x_index + ip[(t0) + u]);                                      \
+                const float4 w = ld_nc_f4(reinterpret_cast<const float4*>(X) + (int64_t)tg * LPR + lane); \
+                v[u] = make_float4(relu_ref(w.x), relu_ref(w.y), relu_ref(w.z), relu_ref(w.w));    \
+            } else {                                                                               \
+                v[u] = ld_nc_f4(H4 + (int64_t)ip[(t0) + u] * LPR + lane);                          \
+            }                                                                                      \
+        }
 #define TC_CONSUME(v, t0)                                                                          \
     _Pragma("unroll") for (int u = 0; u < TC_U; ++u) {                                             \
         if ((t0) + u < ee) {                                                                       \
@@ -482,11 +493,11 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
 }
 
-template <bool HAS_VAL, int XMODE>
+template <bool HAS_VAL, int XMODE, bool HSRC_TABLE = false>
 int tc_launch(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const int32_t* rp, const int32_t* ci, const float* val,
               const float* H, const float* W, const float* X, const int32_t* x_index, float* out)
 {
-    auto kern = s2v_level_tc_kernel<HAS_VAL, XMODE>;
+    auto kern = s2v_level_tc_kernel<HAS_VAL, XMODE, HSRC_TABLE>;
     S2V_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
     const int64_t num_tiles = (n_rows + TC_TILE - 1) / TC_TILE;
     int64_t blocks = num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count;
@@ -500,12 +511,18 @@ int tc_launch(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const int32_t* rp, 
 }  // namespace
 
 // d = 128, 32-bit row offsets.  Returns S2V_ERR_UNSUPPORTED for anything else (the caller falls back).
+// H == NULL with a table: the gather source is ReLU(table[x_index[col], :]) (square matrices only).
 int s2v_launch_level_tc(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int d, const int32_t* row_ptr,
                         const int32_t* col_idx, const float* val, const float* H, const float* W, const float* X,
                         const float* table, const int32_t* x_index, float* out)
 {
     if (d != TC_D) return S2V_ERR_UNSUPPORTED;
     if (TC_SMEM_BYTES > ctx->smem_optin) return S2V_ERR_UNSUPPORTED;
+    if (!H) {
+        if (!table || !x_index) return S2V_ERR_UNSUPPORTED;
+        return val ? tc_launch<true, 2, true>(ctx, st, n_rows, row_ptr, col_idx, val, nullptr, W, table, x_index, out)
+                   : tc_launch<false, 2, true>(ctx, st, n_rows, row_ptr, col_idx, val, nullptr, W, table, x_index, out);
+    }
     const int xmode = table ? 2 : (X ? 1 : 0);
     const float* xa = table ? table : X;
 #define TC_GO(HV, XM) return tc_launch<HV, XM>(ctx, st, n_rows, row_ptr, col_idx, val, H, W, xa, x_index, out)

@@ -174,6 +174,88 @@ __global__ void __launch_bounds__(256) readout_kernel(int64_t G, int d, int hidd
     }
 }
 
+// Register-tiled form for d % 4 == 0 and hidden % 4 == 0 (the configurations of the path):
+// a CTA takes 32 graphs; a thread owns 4 consecutive hidden units x 8 graphs, walks k in steps of
+// 4 with one 16-byte load of W1 per k (L1-resident after the first tile: W1 is at most 128 KB)
+// and one 16-byte shared load of Y per graph, 128 FMAs per 12 loads; k ascending per output.
+constexpr int TG4 = 32;
+__global__ void __launch_bounds__(256) readout_v4_kernel(int64_t G, int d, int hidden, int C, const float* __restrict__ Y,
+                                                         const float* __restrict__ W1, const float* __restrict__ W2,
+                                                         float* __restrict__ logits, float* __restrict__ probs,
+                                                         int32_t* __restrict__ pred)
+{
+    extern __shared__ __align__(16) float sm4[];
+    const int ys = d + 4, hs = hidden + 4;
+    float* Ys = sm4;                  // [TG4][d + 4]
+    float* Hs = Ys + TG4 * ys;        // [TG4][hidden + 4]
+    float* Ls = Hs + TG4 * hs;        // [TG4][C]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int d4 = d >> 2, hq = hidden >> 2;
+    for (int64_t g0 = (int64_t)blockIdx.x * TG4; g0 < G; g0 += (int64_t)gridDim.x * TG4) {
+        const int ng = (int)((G - g0) < TG4 ? (G - g0) : TG4);
+        for (int e = threadIdx.x; e < TG4 * d4; e += blockDim.x) {
+            const int g = e / d4, c = e - g * d4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (g < ng) v = __ldcs(reinterpret_cast<const float4*>(Y + (g0 + g) * d) + c);
+            *reinterpret_cast<float4*>(Ys + g * ys + 4 * c) = v;
+        }
+        __syncthreads();
+        for (int item = threadIdx.x; item < hq * 4; item += blockDim.x) {
+            const int h4 = (item % hq) * 4, gb = (item / hq) * 8;
+            float acc[8][4];
+#pragma unroll
+            for (int g = 0; g < 8; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+            for (int k = 0; k < d; k += 4) {
+                float4 w[4];
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) w[kk] = __ldg(reinterpret_cast<const float4*>(W1 + (int64_t)(k + kk) * hidden + h4));
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const float4 y = *reinterpret_cast<const float4*>(Ys + (gb + g) * ys + k);
+                    const float yy[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        acc[g][0] = fmaf(yy[kk], w[kk].x, acc[g][0]);
+                        acc[g][1] = fmaf(yy[kk], w[kk].y, acc[g][1]);
+                        acc[g][2] = fmaf(yy[kk], w[kk].z, acc[g][2]);
+                        acc[g][3] = fmaf(yy[kk], w[kk].w, acc[g][3]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+                *reinterpret_cast<float4*>(Hs + (gb + g) * hs + h4) =
+                    make_float4(relu_ref(acc[g][0]), relu_ref(acc[g][1]), relu_ref(acc[g][2]), relu_ref(acc[g][3]));
+        }
+        __syncthreads();
+        for (int g = warp; g < ng; g += (blockDim.x >> 5)) {
+            for (int c = 0; c < C; ++c) {
+                float acc = 0.f;
+                for (int h = lane; h < hidden; h += 32) acc = fmaf(Hs[g * hs + h], __ldg(W2 + (int64_t)h * C + c), acc);
+#pragma unroll
+                for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (lane == 0) Ls[g * C + c] = acc;
+            }
+            __syncwarp();
+            if (lane == 0) {
+                const float* l = Ls + g * C;
+                float mx = l[0];
+                int best = 0;
+                for (int c = 1; c < C; ++c)
+                    if (l[c] > mx) { mx = l[c]; best = c; }
+                float s = 0.f;
+                for (int c = 0; c < C; ++c) s += expf(l[c] - mx);
+                for (int c = 0; c < C; ++c) {
+                    logits[(g0 + g) * C + c] = l[c];
+                    if (probs) probs[(g0 + g) * C + c] = expf(l[c] - mx) / s;
+                }
+                if (pred) pred[g0 + g] = best;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 inline unsigned grid_cap(s2v_ctx* ctx, int64_t blocks, int per_sm)
 {
     const int64_t cap = (int64_t)ctx->sm_count * per_sm;
@@ -250,6 +332,14 @@ int s2v_readout_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int d, 
         return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "readout: bad shape");
     if (num_graphs == 0) return S2V_OK;
     if (!Y || !W1 || !W2 || !logits) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "readout: NULL pointer");
+    const size_t smem4 = sizeof(float) * (size_t)TG4 * ((size_t)d + 4 + hidden + 4 + num_class);
+    if (d % 4 == 0 && hidden % 4 == 0 && smem4 <= 96 * 1024 && s2v_aligned16(Y) && s2v_aligned16(W1)) {
+        S2V_CUDA_OK(ctx, cudaFuncSetAttribute(readout_v4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4));
+        readout_v4_kernel<<<grid_cap(ctx, (num_graphs + TG4 - 1) / TG4, 2), 256, smem4, s2v_pick_stream(ctx, stream)>>>(
+            num_graphs, d, hidden, num_class, Y, W1, W2, logits, probs, pred);
+        S2V_CHECK_LAUNCH(ctx, "readout_v4_kernel");
+        return S2V_OK;
+    }
     const size_t smem = sizeof(float) * (size_t)TG * ((size_t)d + hidden + num_class);
     if (smem > 200 * 1024) return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "readout: d + hidden + classes too large for shared memory");
     S2V_CUDA_OK(ctx, cudaFuncSetAttribute(readout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -87,6 +87,15 @@ int s2v_level_lookup_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_
                          const int32_t* row_ptr, const int32_t* col_idx, const float* val, const float* H,
                          const float* W, const float* table, int n_table, const int32_t* x_index, float* out);
 
+/* First level of the classifier with one-hot inputs, without materialising H0:
+ * out = ReLU((A * ReLU(table[tags,:])) * W + table[tags,:]), A square [n x n]; i.e. MatMul(data, w_n2l),
+ * ReLU and the first level (kernel_mean_field.cpp:31-41) in one kernel.  Only the d = 128 tcgen05
+ * kernel has this form (n >= 16,384 unless forced); otherwise S2V_ERR_UNSUPPORTED: run
+ * s2v_input_proj_onehot_f32 + s2v_level_lookup_f32 instead. */
+int s2v_level_first_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n, int d, const int32_t* row_ptr,
+                        const int32_t* col_idx, const float* val, const float* W, const float* table, int n_table,
+                        const int32_t* tags, float* out);
+
 /* ---- unfused tensor operations, one kernel each (the reference's DTensor<GPU,float>
  *      surface used by MatMul / ElewiseAdd / ReLU / Softmax / ArgMax factors) ---- */
 
@@ -112,6 +121,29 @@ int s2v_softmax_f32(s2v_ctx* ctx, s2v_stream stream, int64_t rows, int cols, con
 /* Per-row index of the maximum, first index wins ties: DTensor<GPU>::ArgMax
  * (src/tensor/gpu_dense_tensor.cu:184-190, include/tensor/gpu_reduce_kernel.h:12-33). */
 int s2v_argmax_f32(s2v_ctx* ctx, s2v_stream stream, int64_t rows, int cols, const float* in, int32_t* out);
+
+/* ---- loss / metric tail of the driver's TEST loop (targets = {loss, acc}, nn_common.h:127-146) ----
+ * Labels are a CSR matrix [rows x cols] as GetBatch builds them (one entry per graph, nn_common.h:92-99). */
+/* out[i] = -sum_k log(p[i, col_k]) * val_k, p = softmax(pred row) when need_softmax, |p| < 1e-8 clamped
+ * to 1e-8: CrossEntropy factor (src/nn/cross_entropy.cpp:9-50).  label_val may be NULL (ones). */
+int s2v_cross_entropy_f32(s2v_ctx* ctx, s2v_stream stream, int64_t rows, int cols, const float* pred, int need_softmax,
+                          const int32_t* label_row_ptr, const int32_t* label_col_idx, const float* label_val, float* out);
+/* Column of the largest value of every CSR row, first maximum wins: SpTensor::ArgMax
+ * (src/tensor/gpu_sparse_tensor.cu:82-122, CPU form cpu_sparse_tensor.cpp:86-103). */
+int s2v_argmax_csr_f32(s2v_ctx* ctx, s2v_stream stream, int64_t rows, const int32_t* row_ptr, const int32_t* col_idx,
+                       const float* val, int32_t* out);
+/* out[i] = 1 if fewer than k classes score strictly higher than target[i]: InTopK (src/nn/in_top_k.cpp:6-23). */
+int s2v_in_top_k_f32(s2v_ctx* ctx, s2v_stream stream, int64_t rows, int cols, const float* pred, const int32_t* target,
+                     int k, int32_t* out);
+/* int32 -> float: TypeCast factor (src/nn/type_cast.cpp:14-30). */
+int s2v_cast_i32_f32(s2v_ctx* ctx, s2v_stream stream, int64_t count, const int32_t* in, float* out);
+/* out[0] = sum(in) / count, deterministic: DTensor::Mean / ReduceMean (src/nn/reduce_mean.cpp:14-42). */
+int s2v_mean_f32(s2v_ctx* ctx, s2v_stream stream, int64_t count, const float* in, float* out);
+/* All of the above in one launch: mean cross entropy (with softmax) and mean top-k accuracy of
+ * logits [G x C] against CSR labels; per_graph_loss [G] may be NULL; loss_mean or acc_mean may be NULL. */
+int s2v_loss_acc_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int num_class, const float* logits,
+                     const int32_t* label_row_ptr, const int32_t* label_col_idx, const float* label_val, int topk,
+                     float* loss_mean, float* acc_mean, float* per_graph_loss);
 
 /* ---- graph pooling: Y[g,:] = sum of H[n,:] over n in [seg_ptr[g], seg_ptr[g+1]).
  * Replaces MatMul(SubgraphMsgPass CSR, H) (kernel_mean_field.cpp:44,

@@ -122,3 +122,27 @@ def level(prob, impl: str = "oracle", iters: int = 1, rows: int | None = None):
     if rc != 0:
         raise RuntimeError(f"reference level failed with status {rc}")
     return out, secs
+
+
+def loss_acc(logits: np.ndarray, labels: np.ndarray, impl: str = "oracle", topk: int = 1):
+    """Mean cross entropy (with softmax) and top-k accuracy of logits [G x C] against integer labels [G],
+    presented as the one-entry-per-row CSR the reference's batcher builds.  Returns (loss, acc, per_graph)."""
+    lib = _lib(impl)
+    G, K = logits.shape
+    lg = np.ascontiguousarray(logits, np.float32)
+    rp = np.arange(G + 1, dtype=np.int32)
+    ci = np.ascontiguousarray(labels, np.int32)
+    val = np.ones(G, np.float32)
+    loss, acc = C.c_float(), C.c_float()
+    per = np.zeros(G, np.float32)
+    if impl == "oracle":
+        lib.oracle_loss_acc.restype = None
+        lib.oracle_loss_acc(C.c_int64(G), C.c_int64(K), _p(lg, _f32p), _p(rp, _i32p), _p(ci, _i32p), _p(val, _f32p),
+                            C.c_int(topk), C.byref(loss), C.byref(acc), _p(per, _f32p))
+    else:
+        assert topk == 1
+        rc = lib.ref_loss_acc(C.c_int(G), C.c_int(K), _p(lg, _f32p), _p(rp, _i32p), _p(ci, _i32p), _p(val, _f32p),
+                              C.byref(loss), C.byref(acc), _p(per, _f32p))
+        if rc != 0:
+            raise RuntimeError(f"reference loss/acc failed with status {rc}")
+    return float(loss.value), float(acc.value), per

@@ -172,6 +172,47 @@ int ref_s2v_forward(int G, const int* nodes_per_graph, int E, const int* edge_sr
 }
 
 /*
+ * Loss / metric tail exactly as the driver wires it (kernel_mean_field.cpp:49-56): CrossEntropy(output,
+ * label, need_softmax) -> ReduceMean; ArgMax(label) -> InTopK(output, truth) -> TypeCast -> ReduceMean.
+ * logits [G x C]; labels as the CSR tensor GetBatch builds (nn_common.h:92-99).
+ */
+int ref_loss_acc(int G, int C, const float* logits, const int* label_rp, const int* label_ci, const float* label_val,
+                 float* loss_mean, float* acc_mean, float* per_graph_loss)
+{
+    if (G <= 0 || C <= 0) return -1;
+    DTensor<mode, Dtype> out_t;
+    out_t.Reshape({(size_t)G, (size_t)C});
+    std::memcpy(out_t.data->ptr, logits, sizeof(float) * (size_t)G * C);
+    SpTensor<mode, Dtype> y;
+    y.Reshape({(size_t)G, (size_t)C});
+    y.ResizeSp(label_rp[G], G + 1);
+    std::memcpy(y.data->row_ptr, label_rp, sizeof(int) * (G + 1));
+    std::memcpy(y.data->col_idx, label_ci, sizeof(int) * label_rp[G]);
+    for (int i = 0; i < label_rp[G]; ++i) y.data->val[i] = label_val ? label_val[i] : 1.0f;
+
+    FactorGraph fg;
+    auto output = add_const<DTensorVar<mode, Dtype>>(fg, "output", true);
+    auto label = add_const<SpTensorVar<mode, Dtype>>(fg, "label", true);
+    auto ce = af<CrossEntropy>(fg, {output, label}, true);
+    auto loss = af<ReduceMean>(fg, {ce});
+    auto truth = af<ArgMax>(fg, {label});
+    auto cmp = af<InTopK<mode, Dtype>>(fg, std::make_pair(output, truth));
+    auto real_cmp = af<TypeCast<mode, Dtype>>(fg, {cmp});
+    auto acc = af<ReduceMean>(fg, {real_cmp});
+    std::map<std::string, void*> feed;
+    feed["output"] = &out_t;
+    feed["label"] = &y;
+    std::vector<std::shared_ptr<Variable>> targets;
+    targets.push_back(loss);
+    targets.push_back(acc);
+    fg.FeedForward(targets, feed, Phase::TEST);
+    *loss_mean = loss->AsScalar();
+    *acc_mean = acc->AsScalar();
+    copy_out(per_graph_loss, ce->value);
+    return 0;
+}
+
+/*
  * One level on caller-supplied CSR A [n_rows x n_src] (int32, 3-array), H [n_src x d],
  * W [d x d], X [n_rows x d] (may be NULL: then the ElewiseAdd factor is left out).
  * out [n_rows x d] = ReLU((A*H)*W + X), through the reference's factors.

@@ -259,3 +259,42 @@ int oracle_s2v_forward(int G, const int32_t* nodes_per_graph, int E, const int32
     free(scratch); free(y); free(hid); free(logits); free(probs);
     return rc;
 }
+
+/*
+ * Loss / metric tail of the driver's TEST loop: loss = mean cross entropy with softmax against CSR
+ * labels (src/nn/cross_entropy.cpp:9-50: probabilities with |p| < 1e-8 are clamped to 1e-8), acc =
+ * mean of "fewer than topk classes score strictly higher than the label's argmax"
+ * (ArgMax of the CSR label row, src/tensor/cpu_sparse_tensor.cpp:86-103; InTopK,
+ * src/nn/in_top_k.cpp:6-23; TypeCast; ReduceMean = sequential sum / count,
+ * src/tensor/cpu_dense_tensor.cpp:283-293).  per_graph_loss may be NULL.
+ */
+void oracle_loss_acc(int64_t G, int64_t C, const float* logits, const int32_t* label_rp, const int32_t* label_ci,
+                     const float* label_val, int topk, float* loss_mean, float* acc_mean, float* per_graph_loss)
+{
+    float* probs = (float*)malloc(sizeof(float) * (size_t)G * (size_t)C);
+    oracle_softmax(G, C, logits, probs);
+    float loss_sum = 0.0f, acc_sum = 0.0f;
+    for (int64_t i = 0; i < G; ++i) {
+        float loss = 0.0f;
+        for (int32_t k = label_rp[i]; k < label_rp[i + 1]; ++k) {
+            float t = probs[C * i + label_ci[k]];
+            if (fabs(t) < 1e-8) t = 1e-8f;
+            loss -= logf(t) * (label_val ? label_val[k] : 1.0f);
+        }
+        if (per_graph_loss) per_graph_loss[i] = loss;
+        loss_sum += loss;
+        int32_t target = 0;
+        float cur = 0.0f;
+        for (int32_t j = label_rp[i]; j < label_rp[i + 1]; ++j) {
+            float v = label_val ? label_val[j] : 1.0f;
+            if (j == label_rp[i] || v > cur) { cur = v; target = label_ci[j]; }
+        }
+        int t = 0;
+        for (int64_t j = 0; j < C; ++j)
+            if (j != target && logits[C * i + j] > logits[C * i + target]) t++;
+        acc_sum += (float)(t < topk);
+    }
+    *loss_mean = loss_sum / (float)G;
+    *acc_mean = acc_sum / (float)G;
+    free(probs);
+}

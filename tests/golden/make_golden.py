@@ -35,6 +35,11 @@ def main():
     np.savez_compressed(os.path.join(HERE, "mutag_like_seed3.npz"), digest=b2.digest(),
                         n2n_row_ptr=r2["n2n_row_ptr"], n2n_col_idx=r2["n2n_col_idx"], pooled=r2["pooled"],
                         logits=r2["logits"], probs=r2["probs"], argmax=r2["argmax"])
+    # 2b. loss / accuracy tail of the driver's TEST loop on those logits, labels drawn from seed 7
+    labels = np.random.default_rng(7).integers(0, 2, size=b2.num_graphs).astype(np.int32)
+    loss, acc, per_graph = ob.loss_acc(r2["logits"], labels, "reference")
+    np.savez_compressed(os.path.join(HERE, "loss_acc_seed3.npz"), labels=labels, loss=np.float32(loss), acc=np.float32(acc),
+                        per_graph=per_graph)
     # 3. one fused level on a small directed Erdos-Renyi graph (duplicates, empty rows, unsorted rows)
     p = synth.erdos_renyi_level(n=1000, nnz=6000, d=64, seed=1)
     out, _ = ob.level(p, "reference")

@@ -123,3 +123,47 @@ def test_full_size_properties():
     eng.ctx.synchronize()
     assert np.array_equal(l2.cpu().numpy(), logits[lo:])   # block-diagonal independence, bit-exact
     assert np.isfinite(logits).all()
+
+
+def test_loss_accuracy_tail_on_device(gpu_ctx, oracle_lib, golden):
+    """Fused loss/accuracy launch and the per-factor kernels against the reference's golden tail."""
+    g = golden("mutag_like_seed3.npz")
+    t = golden("loss_acc_seed3.npz")
+    G, C = g["logits"].shape
+    logits = torch.from_numpy(g["logits"]).cuda()
+    rp = torch.arange(G + 1, dtype=torch.int32, device="cuda")
+    ci = torch.from_numpy(t["labels"]).cuda()
+    val = torch.ones(G, device="cuda")
+    loss = torch.zeros(1, device="cuda")
+    acc = torch.zeros(1, device="cuda")
+    per = torch.zeros(G, device="cuda")
+    gpu_ctx.loss_acc(logits, rp, ci, val, loss, acc, per)
+    gpu_ctx.synchronize()
+    assert abs(loss.item() - float(t["loss"])) <= 1e-5 * max(1.0, abs(float(t["loss"])))
+    assert acc.item() == float(t["acc"])
+    assert_close(per.cpu().numpy(), t["per_graph"], "per-graph loss")
+    # the same through the one-kernel-per-factor entry points
+    ce = torch.zeros(G, device="cuda")
+    truth = torch.zeros(G, dtype=torch.int32, device="cuda")
+    hit = torch.zeros(G, dtype=torch.int32, device="cuda")
+    hitf = torch.zeros(G, device="cuda")
+    m = torch.zeros(2, device="cuda")
+    gpu_ctx.call("s2v_cross_entropy_f32", None, G, C, logits.data_ptr(), 1, rp.data_ptr(), ci.data_ptr(), val.data_ptr(), ce.data_ptr())
+    gpu_ctx.call("s2v_argmax_csr_f32", None, G, rp.data_ptr(), ci.data_ptr(), val.data_ptr(), truth.data_ptr())
+    gpu_ctx.call("s2v_in_top_k_f32", None, G, C, logits.data_ptr(), truth.data_ptr(), 1, hit.data_ptr())
+    gpu_ctx.call("s2v_cast_i32_f32", None, G, hit.data_ptr(), hitf.data_ptr())
+    gpu_ctx.call("s2v_mean_f32", None, G, ce.data_ptr(), m.data_ptr())
+    gpu_ctx.call("s2v_mean_f32", None, G, hitf.data_ptr(), m.data_ptr() + 4)
+    gpu_ctx.synchronize()
+    assert torch.equal(truth.cpu(), ci.cpu()) and torch.equal(ce, per)
+    assert abs(m[0].item() - float(t["loss"])) <= 1e-5 * max(1.0, abs(float(t["loss"]))) and m[1].item() == float(t["acc"])
+    # large random case against the oracle
+    rng = np.random.default_rng(1)
+    lg = (rng.standard_normal((5000, 6)) * 8).astype(np.float32)
+    lab = rng.integers(0, 6, 5000).astype(np.int32)
+    want = oracle_lib.loss_acc(lg, lab, "oracle", topk=2)
+    l2, a2 = torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda")
+    gpu_ctx.loss_acc(torch.from_numpy(lg).cuda(), torch.arange(5001, dtype=torch.int32, device="cuda"), torch.from_numpy(lab).cuda(),
+                     None, l2, a2, None, topk=2)
+    gpu_ctx.synchronize()
+    assert abs(l2.item() - want[0]) <= 2e-5 * abs(want[0]) and abs(a2.item() - want[1]) <= 1e-6

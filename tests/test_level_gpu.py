@@ -95,6 +95,30 @@ def test_level_block_diagonal_batch(gpu_ctx, oracle_lib):
     assert_close(out.cpu().numpy(), o["levels"][2], "lookup form")
 
 
+def test_first_level_straight_from_tags(gpu_ctx, oracle_lib):
+    """s2v_level_first_f32 (H0 never materialised) against input projection + level, and the oracle."""
+    from graphnn_b200.capi import S2VError
+    b = synth.molecules_16k(seed=4, num_graphs=700)          # ~21k nodes: the tcgen05 kernel takes it
+    o = oracle_lib.forward(b, "oracle")
+    rp, ci, tags = dev(o["n2n_row_ptr"]), dev(o["n2n_col_idx"]), dev(b.tags.astype(np.int32))
+    W, table = dev(b.weights["p_node_conv"]), dev(b.weights["w_n2l"])
+    fused = torch.full((b.num_nodes, b.d), float("nan"), device="cuda")
+    gpu_ctx.level_first(rp, ci, None, W, table, tags, fused)
+    h0 = torch.empty_like(fused)
+    two_step = torch.empty_like(fused)
+    gpu_ctx.input_proj_onehot(tags, table, None, h0)
+    gpu_ctx.level_lookup(rp, ci, None, h0, W, table, tags, two_step)
+    gpu_ctx.synchronize()
+    assert torch.equal(fused, two_step)                       # same arithmetic in the same order
+    assert_close(fused.cpu().numpy(), o["levels"][1], "first level from tags")
+    small = synth.mutag_like(seed=0)                          # d = 64: no such kernel, the caller must fall back
+    with pytest.raises(S2VError) as e:
+        gpu_ctx.level_first(dev(np.zeros(small.num_nodes + 1, np.int32)), None, None, dev(small.weights["p_node_conv"]),
+                            dev(small.weights["w_n2l"]), dev(small.tags.astype(np.int32)),
+                            torch.empty((small.num_nodes, 64), device="cuda"))
+    assert e.value.status == -2
+
+
 def test_level_relu_keeps_negative_zero_and_nan(gpu_ctx):
     d = 64
     H = np.zeros((16, d), np.float32)

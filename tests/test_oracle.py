@@ -120,3 +120,23 @@ def test_shard_bounds_cover_and_balance():
         shards = [b.shard(r, world) for r in range(world)]
         assert sum(s.num_edges for s in shards) == b.num_edges
         assert sum(s.num_nodes for s in shards) == b.num_nodes
+
+
+def test_loss_accuracy_tail(oracle_lib, golden):
+    g = golden("mutag_like_seed3.npz")
+    t = golden("loss_acc_seed3.npz")
+    loss, acc, per = oracle_lib.loss_acc(g["logits"], t["labels"], "oracle")
+    assert abs(loss - float(t["loss"])) <= 1e-5 * max(1.0, abs(float(t["loss"]))) and acc == float(t["acc"])
+    assert_close(per, t["per_graph"], "per-graph cross entropy")
+    # clamp: a probability that underflows to 0 is treated as 1e-8
+    lg = np.array([[100.0, -100.0], [0.0, 0.0]], np.float32)
+    loss2, acc2, per2 = oracle_lib.loss_acc(lg, np.array([1, 0], np.int32), "oracle")
+    assert abs(per2[0] - (-np.log(np.float32(1e-8)))) < 1e-4 and abs(per2[1] - np.log(2.0)) < 1e-6 and acc2 == 0.5
+    if oracle_lib.have_reference():
+        rng = np.random.default_rng(5)
+        lgs = (rng.standard_normal((300, 5)) * 10).astype(np.float32)
+        lab = rng.integers(0, 5, 300).astype(np.int32)
+        a = oracle_lib.loss_acc(lgs, lab, "oracle")
+        b = oracle_lib.loss_acc(lgs, lab, "reference")
+        assert abs(a[0] - b[0]) <= 1e-5 * abs(b[0]) and a[1] == b[1]
+        assert_close(a[2], b[2], "per-graph loss vs reference")
