@@ -5,7 +5,11 @@
 // examples/graph_classification/src/kernel_mean_field.cpp:28-47 and the batch is assembled the
 // way its GetBatch does (include/nn_common.h:36-105).
 //
-//   s2v_mean_field <batch.bin> <out.bin> [--fused 0|1] [--iters K]
+//   s2v_mean_field <batch.bin> <out.bin> [--fused 0|1] [--iters K] [--labels labels.bin]
+//
+// --labels  : int32 class of every graph; the driver then also evaluates the reference's targets
+//             {loss, acc} (CrossEntropy -> ReduceMean, ArgMax -> InTopK -> TypeCast -> ReduceMean,
+//             kernel_mean_field.cpp:49-56) and prints them on stdout as "loss <v> acc <v>".
 //
 // --fused 0 : the reference's wiring, one factor per tensor operation
 //             (MatMul, ReLU, MatMul(sparse), MatMul, ElewiseAdd, ReLU, ...)
@@ -83,9 +87,11 @@ int main(int argc, const char** argv)
         return 2;
     }
     int fused = 1, iters = 1;
+    const char* labels_path = nullptr;
     for (int i = 3; i + 1 < argc; i += 2) {
         if (!strcmp(argv[i], "--fused")) fused = atoi(argv[i + 1]);
         if (!strcmp(argv[i], "--iters")) iters = atoi(argv[i + 1]);
+        if (!strcmp(argv[i], "--labels")) labels_path = argv[i + 1];
     }
     Batch b = load_batch(argv[1]);
     GpuHandle::Init(0, 1);
@@ -164,6 +170,37 @@ int main(int argc, const char** argv)
     targets.push_back(pred);
     targets.push_back(cur_message_layer);
 
+    // ---- optional loss / accuracy targets, labels as the CSR tensor GetBatch builds (nn_common.h:92-99)
+    SpTensor<CPU, Dtype> y_cpu;
+    SpTensor<mode, Dtype> label;
+    std::shared_ptr<DTensorVar<mode, Dtype>> loss, acc;
+    if (labels_path) {
+        std::vector<int> lab;
+        FILE* lf = fopen(labels_path, "rb");
+        ASSERT(lf, "cannot open " << labels_path);
+        read_vec(lf, lab, b.G);
+        fclose(lf);
+        y_cpu.Reshape({(size_t)b.G, (size_t)cfg::num_class});
+        y_cpu.ResizeSp(b.G, b.G + 1);
+        for (int i = 0; i < b.G; ++i) {
+            y_cpu.data->row_ptr[i] = i;
+            y_cpu.data->val[i] = 1.0;
+            y_cpu.data->col_idx[i] = lab[i];
+        }
+        y_cpu.data->row_ptr[b.G] = b.G;
+        label.CopyFrom(y_cpu);
+        auto label_var = add_const<SpTensorVar<mode, Dtype>>(fg, "label", true);
+        auto ce = af<CrossEntropy>(fg, {output, label_var}, true);
+        loss = af<ReduceMean>(fg, {ce});
+        auto truth = af<ArgMax>(fg, {label_var});
+        auto cmp = af<InTopK<mode, Dtype>>(fg, std::make_pair(output, truth));
+        auto real_cmp = af<TypeCast<mode, Dtype>>(fg, {cmp});
+        acc = af<ReduceMean>(fg, {real_cmp});
+        inputs["label"] = &label;
+        targets.push_back(loss);
+        targets.push_back(acc);
+    }
+
     double best = 1e30;
     for (int it = 0; it < iters; ++it) {
         auto t0 = std::chrono::steady_clock::now();
@@ -174,6 +211,8 @@ int main(int argc, const char** argv)
     }
     fprintf(stderr, "s2v_mean_field: %d graphs, %d nodes, %d edges, fused=%d, %zu factors, %llu kernel launches, best FeedForward %.3f ms\n",
             b.G, b.N, b.E, fused, fg.NumFactors(), (unsigned long long)s2v_launch_count(GpuHandle::ctx()), best * 1e3);
+
+    if (labels_path) printf("loss %.9g acc %.9g\n", (double)loss->AsScalar(), (double)acc->AsScalar());
 
     // ---- results back to the host
     DTensor<CPU, Dtype> logits_cpu, probs_cpu, embed_cpu;

@@ -186,6 +186,15 @@ typename FacType::OutType af(FactorGraph& g, std::initializer_list<VarPtrT> op, 
 {
     return af<FacType>(g, std::vector<VarPtrT>(op), std::forward<Args>(args)...);
 }
+// af<InTopK<mode, Dtype>>(graph, std::make_pair(pred, labels)): operands of two different types
+template <typename FacType, typename VarPtr1, typename VarPtr2, typename... Args>
+typename FacType::OutType af(FactorGraph& g, std::pair<VarPtr1, VarPtr2> op, Args&&... args)
+{
+    std::vector<std::shared_ptr<Variable>> ops(2);
+    ops[0] = op.first;
+    ops[1] = op.second;
+    return af<FacType>(g, ops, std::forward<Args>(args)...);
+}
 // af<MatMul>(graph, {a, b}): mode and element type deduced from the operands
 template <template <typename, typename> class FacType, typename... Args>
 typename FacType<GPU, float>::OutType af(FactorGraph& g, std::vector<std::shared_ptr<TensorVar<GPU, float>>> op, Args&&... args)

@@ -143,9 +143,105 @@ public:
         ASSERT(outputs.size() == 1, "unexpected output size for " << StrType());
         auto* out = dynamic_cast<DTensorVar<mode, int>*>(outputs[0].get());
         ASSERT(out, "wrong output type for " << StrType());
-        detail::dense<mode, Dtype>(operands[0]).ArgMax(out->value);
+        auto* in = dynamic_cast<TensorVar<mode, Dtype>*>(operands[0].get());
+        ASSERT(in, "wrong operand type for " << StrType());
+        if (in->GetMatType() == MatType::dense) {
+            in->template Derived<DENSE>().value.ArgMax(out->value);
+        } else {   // label matrices are CSR: column of the largest value per row
+            auto& sp = in->template Derived<CSR_SPARSE>().value;
+            out->value.Reshape({sp.rows()});
+            S2V_ASSERT_OK(s2v_argmax_csr_f32(GpuHandle::ctx(), nullptr, (int64_t)sp.rows(), sp.data->row_ptr, sp.data->col_idx,
+                                             sp.data->val, out->value.data->ptr));
+        }
     }
     uint axis;
+};
+
+// ---- loss / metric tail of the driver (kernel_mean_field.cpp:49-56) ---------------------------
+// per-row cross entropy of dense predictions against CSR labels (src/nn/cross_entropy.cpp:33-50)
+template <typename mode, typename Dtype>
+class CrossEntropy : public Factor
+{
+public:
+    S2V_DENSE_OUT("CrossEntropy")
+    CrossEntropy(std::string _name, bool _need_softmax, PropErr _properr = PropErr::T)
+        : Factor(_name, _properr), need_softmax(_need_softmax) {}
+    void Forward(std::vector<std::shared_ptr<Variable>>& operands, std::vector<std::shared_ptr<Variable>>& outputs, Phase) override
+    {
+        ASSERT(operands.size() == 2, "unexpected input size for " << StrType());
+        auto& pred = detail::dense<mode, Dtype>(operands[0]);
+        auto& label = detail::sparse<mode, Dtype>(operands[1]);
+        ASSERT(pred.cols() == label.cols() && pred.rows() == label.rows(), "# class doesn't match");
+        auto& out = detail::dense<mode, Dtype>(outputs[0]);
+        out.Reshape({pred.rows(), 1});
+        S2V_ASSERT_OK(s2v_cross_entropy_f32(GpuHandle::ctx(), nullptr, (int64_t)pred.rows(), (int)pred.cols(), pred.data->ptr,
+                                            need_softmax ? 1 : 0, label.data->row_ptr, label.data->col_idx, label.data->val,
+                                            out.data->ptr));
+    }
+    bool need_softmax;
+};
+
+// global mean -> tensor of one element (src/nn/reduce_mean.cpp:14-42)
+template <typename mode, typename Dtype>
+class ReduceMean : public Factor
+{
+public:
+    S2V_DENSE_OUT("ReduceMean")
+    ReduceMean(std::string _name, int _axis = -1, bool _keep_dim = false, PropErr _properr = PropErr::T)
+        : Factor(_name, _properr), axis(_axis), keep_dim(_keep_dim) {}
+    void Forward(std::vector<std::shared_ptr<Variable>>& operands, std::vector<std::shared_ptr<Variable>>& outputs, Phase) override
+    {
+        ASSERT(operands.size() == 1, "unexpected input size for " << StrType());
+        ASSERT(axis == -1 && keep_dim == false, "currently only support axis=-1 and keep_dim=false in " << StrType());
+        auto& in = detail::dense<mode, Dtype>(operands[0]);
+        auto& out = detail::dense<mode, Dtype>(outputs[0]);
+        out.Reshape({1});
+        S2V_ASSERT_OK(s2v_mean_f32(GpuHandle::ctx(), nullptr, (int64_t)in.shape.Count(), in.data->ptr, out.data->ptr));
+    }
+    int axis;
+    bool keep_dim;
+};
+
+// operands {predictions (dense), labels (int)}: 1 where the label is among the top k (src/nn/in_top_k.cpp:6-49)
+template <typename mode, typename Dtype>
+class InTopK : public Factor
+{
+public:
+    static std::string StrType() { return "InTopK"; }
+    using OutType = std::shared_ptr<DTensorVar<mode, int>>;
+    OutType CreateOutVar() { return std::make_shared<DTensorVar<mode, int>>(this->name + ":out_0"); }
+    InTopK(std::string _name, int _topK = 1) : Factor(_name, PropErr::N), topK(_topK) {}
+    void Forward(std::vector<std::shared_ptr<Variable>>& operands, std::vector<std::shared_ptr<Variable>>& outputs, Phase) override
+    {
+        ASSERT(operands.size() == 2, "unexpected input size for " << StrType());
+        auto& pred = detail::dense<mode, Dtype>(operands[0]);
+        auto* lab = dynamic_cast<DTensorVar<mode, int>*>(operands[1].get());
+        auto* out = dynamic_cast<DTensorVar<mode, int>*>(outputs[0].get());
+        ASSERT(lab && out, "wrong operand types for " << StrType());
+        ASSERT(pred.rows() == lab->value.shape.Count(), "# instances doesn't match");
+        out->value.Reshape(lab->value.shape.dims);
+        S2V_ASSERT_OK(s2v_in_top_k_f32(GpuHandle::ctx(), nullptr, (int64_t)pred.rows(), (int)pred.cols(), pred.data->ptr,
+                                       lab->value.data->ptr, topK, out->value.data->ptr));
+    }
+    int topK;
+};
+
+// int tensor -> Dtype tensor (src/nn/type_cast.cpp:14-30)
+template <typename mode, typename Dtype>
+class TypeCast : public Factor
+{
+public:
+    S2V_DENSE_OUT("TypeCast")
+    TypeCast(std::string _name, PropErr _properr = PropErr::T) : Factor(_name, _properr) {}
+    void Forward(std::vector<std::shared_ptr<Variable>>& operands, std::vector<std::shared_ptr<Variable>>& outputs, Phase) override
+    {
+        ASSERT(operands.size() == 1, "unexpected input size for " << StrType());
+        auto* in = dynamic_cast<DTensorVar<mode, int>*>(operands[0].get());
+        ASSERT(in, StrType() << " is implemented for int -> float");
+        auto& out = detail::dense<mode, Dtype>(outputs[0]);
+        out.Reshape(in->value.shape.dims);
+        S2V_ASSERT_OK(s2v_cast_i32_f32(GpuHandle::ctx(), nullptr, (int64_t)in->value.shape.Count(), in->value.data->ptr, out.data->ptr));
+    }
 };
 
 // ---- message-passing matrices (src/nn/msg_pass.cpp:25-67,156-177): built on the host from the

@@ -85,3 +85,21 @@ def test_driver_on_a_larger_batch(cxx_bins, oracle_lib, tmp_path):
         assert_close(got["embed"], o["levels"][-1], f"embeddings fused={fused}")
         assert_close(got["logits"], o["logits"], f"logits fused={fused}", scale=max(1.0, float(np.abs(o["logits"]).max())))
         assert np.array_equal(got["pred"], o["argmax"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fused", [0, 1])
+def test_driver_loss_and_accuracy_targets(cxx_bins, golden, tmp_path, fused):
+    """The reference's TEST-loop targets {loss, acc} through the mirrored factors
+    (CrossEntropy, ReduceMean, ArgMax on the CSR labels, InTopK, TypeCast)."""
+    t = golden("loss_acc_seed3.npz")
+    b = synth.mutag_like(seed=3)
+    write_batch(tmp_path / "batch.bin", b)
+    np.ascontiguousarray(t["labels"], np.int32).tofile(tmp_path / "labels.bin")
+    r = subprocess.run([cxx_bins["s2v_mean_field"], str(tmp_path / "batch.bin"), str(tmp_path / "out.bin"), "--fused", str(fused),
+                        "--labels", str(tmp_path / "labels.bin")], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    words = r.stdout.split()
+    loss, acc = float(words[1]), float(words[3])
+    assert abs(loss - float(t["loss"])) <= 1e-5 * max(1.0, abs(float(t["loss"])))
+    assert acc == float(t["acc"])
