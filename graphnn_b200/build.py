@@ -67,8 +67,10 @@ def build_cxx(force: bool = False) -> dict:
     os.makedirs(CXX_BIN, exist_ok=True)
     headers = [h for h in glob.glob(os.path.join(CXX_DIR, "include", "**", "*.h"), recursive=True)]
     headers.append(os.path.join(REPO, "include", "s2v_b200.h"))
+    headers.append(os.path.join(CXX_DIR, "examples", "dataset.h"))
     out = {}
     for name, src in (("s2v_mean_field", os.path.join(CXX_DIR, "examples", "s2v_mean_field.cpp")),
+                      ("s2v_classify", os.path.join(CXX_DIR, "examples", "s2v_classify.cpp")),
                       ("host_interface_test", os.path.join(CXX_DIR, "tests", "host_interface_test.cpp"))):
         exe = os.path.join(CXX_BIN, name)
         if force or _stale(exe, [src, LIB] + headers):

@@ -2,6 +2,7 @@
 #ifndef S2V_PARAM_SET_H
 #define S2V_PARAM_SET_H
 
+#include <cstdio>
 #include <map>
 #include <memory>
 #include <string>
@@ -19,6 +20,22 @@ public:
     {
         ASSERT(params.count(param->name) == 0, "duplicated parameter " << param->name);
         params[param->name] = param;
+    }
+    // Checkpoint = the tensors' records one after another in name order, as the reference writes
+    // them (src/nn/param_set.cpp:28-54); a file saved by the reference loads here and vice versa.
+    void Save(std::string filename)
+    {
+        FILE* fid = fopen(filename.c_str(), "wb");
+        ASSERT(fid, "file " + filename + " cannot be written");
+        for (auto& p : params) p.second->value.Serialize(fid);
+        fclose(fid);
+    }
+    void Load(std::string filename)
+    {
+        FILE* fid = fopen(filename.c_str(), "rb");
+        ASSERT(fid, "file " + filename + " is not found");
+        for (auto& p : params) p.second->value.Deserialize(fid);
+        fclose(fid);
     }
     std::map<std::string, std::shared_ptr<DTensorVar<mode, Dtype>>> params;
 };

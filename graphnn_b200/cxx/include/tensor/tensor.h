@@ -12,6 +12,7 @@
 
 #include <cuda_runtime_api.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <memory>
@@ -298,6 +299,33 @@ public:
         Dtype v;
         detail::copy_bytes<CPU, mode>(&v, data->ptr, sizeof(Dtype));
         return v;
+    }
+
+    // Byte layout of the reference's checkpoints (src/tensor/tensor.cpp:15-29,
+    // src/tensor/cpu_dense_tensor.cpp:72-88, src/tensor/gpu_dense_tensor.cu:71-95):
+    // [rank : size_t][dims : size_t x rank][mem_size : size_t][mem_size elements]
+    void Serialize(FILE* fid)
+    {
+        const size_t len = shape.dims.size(), n = shape.Count();
+        ASSERT(fwrite(&len, sizeof(size_t), 1, fid) == 1, "write failed");
+        ASSERT(fwrite(shape.dims.data(), sizeof(size_t), len, fid) == len, "write failed");
+        std::vector<Dtype> host(n);
+        detail::copy_bytes<CPU, mode>(host.data(), data->ptr, sizeof(Dtype) * n);
+        ASSERT(fwrite(&n, sizeof(size_t), 1, fid) == 1, "write failed");
+        ASSERT(fwrite(host.data(), sizeof(Dtype), n, fid) == n, "write failed");
+    }
+    void Deserialize(FILE* fid)
+    {
+        size_t len = 0, mem = 0;
+        ASSERT(fread(&len, sizeof(size_t), 1, fid) == 1 && len <= 8, "not a tensor record");
+        std::vector<size_t> dims(len);
+        ASSERT(fread(dims.data(), sizeof(size_t), len, fid) == len, "truncated tensor record");
+        ASSERT(fread(&mem, sizeof(size_t), 1, fid) == 1, "truncated tensor record");
+        Reshape(dims);
+        ASSERT(mem >= shape.Count(), "tensor record holds fewer elements than its shape");
+        std::vector<Dtype> host(mem);   // the reference stores its whole (grow-only) buffer
+        ASSERT(fread(host.data(), sizeof(Dtype), mem, fid) == mem, "truncated tensor record");
+        detail::copy_bytes<mode, CPU>(data->ptr, host.data(), sizeof(Dtype) * shape.Count());
     }
 
     // ---- arithmetic (GPU float): one library kernel each

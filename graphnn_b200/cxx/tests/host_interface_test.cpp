@@ -138,7 +138,25 @@ static int test_cpu_tensors()
     return 0;
 }
 
-int main()
+// argv[1]: a checkpoint written by the reference's ParamSet::Save (F=3, d=4, hidden=5, C=2);
+// argv[2]: where to write it back with this library's Save.  The caller compares the bytes.
+static int test_checkpoint(const char* in_path, const char* out_path)
 {
+    ParamSet<CPU, float> model;
+    auto a = add_diff<DTensorVar>(model, "input-node-to-latent", {3u, 4u});
+    auto b = add_diff<DTensorVar>(model, "linear-node-conv", {4u, 4u});
+    auto c = add_diff<DTensorVar>(model, "h1_weight", {4u, 5u});
+    auto e = add_diff<DTensorVar>(model, "h2_weight", {5u, 2u});
+    model.Load(in_path);
+    CHECK(a->value.rows() == 3 && a->value.cols() == 4 && c->value.cols() == 5 && e->value.shape.Count() == 10);
+    printf("first %.9g %.9g %.9g %.9g\n", a->value.data->ptr[0], b->value.data->ptr[0], c->value.data->ptr[0], e->value.data->ptr[9]);
+    model.Save(out_path);
+    puts("ok checkpoint");
+    return 0;
+}
+
+int main(int argc, const char** argv)
+{
+    if (argc == 3) return test_checkpoint(argv[1], argv[2]);
     return test_schedule() || test_msg_pass_matrices() || test_cpu_tensors();
 }

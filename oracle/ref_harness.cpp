@@ -172,6 +172,26 @@ int ref_s2v_forward(int G, const int* nodes_per_graph, int E, const int* edge_sr
 }
 
 /*
+ * Writes a checkpoint with the reference's own ParamSet::Save (src/nn/param_set.cpp:28-41) holding the four
+ * parameters of the classifier under the names the driver gives them (kernel_mean_field.cpp:14-17).
+ */
+int ref_save_model(const char* path, int F, int d, int hidden, int C, const float* w_n2l, const float* p_node_conv,
+                   const float* h1_weight, const float* h2_weight)
+{
+    ParamSet<mode, Dtype> model;
+    auto a = add_diff<DTensorVar>(model, "input-node-to-latent", {(uint)F, (uint)d});
+    auto b = add_diff<DTensorVar>(model, "linear-node-conv", {(uint)d, (uint)d});
+    auto c = add_diff<DTensorVar>(model, "h1_weight", {(uint)d, (uint)hidden});
+    auto e = add_diff<DTensorVar>(model, "h2_weight", {(uint)hidden, (uint)C});
+    fill_param(a, w_n2l);
+    fill_param(b, p_node_conv);
+    fill_param(c, h1_weight);
+    fill_param(e, h2_weight);
+    model.Save(path);
+    return 0;
+}
+
+/*
  * Loss / metric tail exactly as the driver wires it (kernel_mean_field.cpp:49-56): CrossEntropy(output,
  * label, need_softmax) -> ReduceMean; ArgMax(label) -> InTopK(output, truth) -> TypeCast -> ReduceMean.
  * logits [G x C]; labels as the CSR tensor GetBatch builds (nn_common.h:92-99).

@@ -45,6 +45,16 @@ def main():
     out, _ = ob.level(p, "reference")
     np.savez_compressed(os.path.join(HERE, "er_level_n1000_d64_seed1.npz"), row_ptr=p.row_ptr, col_idx=p.col_idx,
                         out=out)
+    # 4. a checkpoint written by the reference's own ParamSet::Save (byte-format fixture) and its weights
+    import ctypes as C
+    rng = np.random.default_rng(0)
+    F, d, h, K = 3, 4, 5, 2
+    w = {"w_n2l": rng.standard_normal((F, d)).astype(np.float32), "p_node_conv": rng.standard_normal((d, d)).astype(np.float32),
+         "h1_weight": rng.standard_normal((d, h)).astype(np.float32), "h2_weight": rng.standard_normal((h, K)).astype(np.float32)}
+    f32p = C.POINTER(C.c_float)
+    ob._lib("reference").ref_save_model(os.path.join(HERE, "tiny_reference_saved.model").encode(), F, d, h, K,
+                                        *[w[k].ctypes.data_as(f32p) for k in ("w_n2l", "p_node_conv", "h1_weight", "h2_weight")])
+    np.savez(os.path.join(HERE, "tiny_reference_saved_weights.npz"), **w)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")

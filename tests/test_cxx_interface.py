@@ -103,3 +103,64 @@ def test_driver_loss_and_accuracy_targets(cxx_bins, golden, tmp_path, fused):
     loss, acc = float(words[1]), float(words[3])
     assert abs(loss - float(t["loss"])) <= 1e-5 * max(1.0, abs(float(t["loss"])))
     assert acc == float(t["acc"])
+
+
+def test_checkpoint_format_against_reference_written_file(cxx_bins, golden, tmp_path):
+    """tests/golden/tiny_reference_saved.model was written by the reference's ParamSet::Save."""
+    from conftest import GOLDEN
+    from graphnn_b200 import io
+    src = os.path.join(GOLDEN, "tiny_reference_saved.model")
+    w = golden("tiny_reference_saved_weights.npz")
+    got = io.read_model(src)
+    for k in ("w_n2l", "p_node_conv", "h1_weight", "h2_weight"):
+        assert np.array_equal(got[k], w[k]), k
+    io.write_model(str(tmp_path / "py.model"), {k: w[k] for k in w.files})
+    assert open(src, "rb").read() == open(tmp_path / "py.model", "rb").read()
+    # the C++ mirror: Load the reference's file, Save it again, same bytes
+    r = subprocess.run([cxx_bins["host_interface_test"], src, str(tmp_path / "cxx.model")], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "ok checkpoint" in r.stdout, r.stdout + r.stderr
+    first = [float(x) for x in r.stdout.splitlines()[0].split()[1:]]
+    assert np.allclose(first, [w["w_n2l"][0, 0], w["p_node_conv"][0, 0], w["h1_weight"][0, 0], w["h2_weight"][4, 1]], rtol=1e-7)
+    assert open(src, "rb").read() == open(tmp_path / "cxx.model", "rb").read()
+
+
+def test_txt_dataset_round_trip(tmp_path):
+    from graphnn_b200 import io
+    b = synth.mutag_like(seed=2, num_graphs=9)
+    graphs = io.graphs_of_batch(b)
+    labels = np.arange(9) % 2
+    io.write_txt_dataset(str(tmp_path / "d.txt"), graphs, labels)
+    g2, l2 = io.read_txt_dataset(str(tmp_path / "d.txt"))
+    assert np.array_equal(l2, labels) and len(g2) == 9
+    for (t1, a1), (t2, a2) in zip(graphs, g2):
+        assert np.array_equal(t1, t2) and all(np.array_equal(x, y) for x, y in zip(a1, a2))
+    ref_file = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference",
+                            "examples", "graph_classification", "data", "MUTAG", "MUTAG.txt")
+    if os.path.exists(ref_file):     # the reference's own file, when a checkout is next to this repository
+        g, l = io.read_txt_dataset(ref_file)
+        assert len(g) == len(l) > 100 and len(set(l.tolist())) == 2
+        for tags, adj in g[:20]:          # undirected graphs: every neighbour list is mirrored
+            pairs = {(i, int(j)) for i, nb in enumerate(adj) for j in nb}
+            assert all((j, i) in pairs for i, j in pairs) and all(0 <= j < len(tags) for _, j in pairs)
+
+
+@pytest.mark.gpu
+def test_serving_driver_on_text_dataset_and_checkpoint(cxx_bins, oracle_lib, tmp_path):
+    """s2v_classify: text data set + ParamSet checkpoint -> batched inference, loss and accuracy."""
+    from graphnn_b200 import io
+    b = synth.mutag_like(seed=3, num_graphs=40)
+    labels = np.random.default_rng(1).integers(0, 2, 40).astype(np.int32)
+    io.write_txt_dataset(str(tmp_path / "d.txt"), io.graphs_of_batch(b), labels)
+    io.write_model(str(tmp_path / "w.model"), b.weights)
+    idx = np.arange(39, -1, -1)                 # reversed order: batches differ from the file order
+    np.savetxt(tmp_path / "idx.txt", idx, fmt="%d")
+    r = subprocess.run([cxx_bins["s2v_classify"], "-graph", str(tmp_path / "d.txt"), "-model", str(tmp_path / "w.model"),
+                        "-test_idx", str(tmp_path / "idx.txt"), "-conv", "64", "-hidden", "128", "-lv", "3", "-b", "16",
+                        "-node_dim", "7", "-out", str(tmp_path / "pred.txt")], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    o = oracle_lib.forward(b, "oracle", want_levels=False)
+    pred = np.loadtxt(tmp_path / "pred.txt", dtype=int)
+    assert np.array_equal(pred[:, 0], idx) and np.array_equal(pred[:, 1], o["argmax"][idx]) and np.array_equal(pred[:, 2], labels[idx])
+    want_loss, want_acc, _ = oracle_lib.loss_acc(o["logits"], labels, "oracle")
+    words = r.stdout.split()
+    assert abs(float(words[2]) - want_loss) <= 1e-5 * max(1.0, want_loss) and abs(float(words[4]) - want_acc) < 1e-6
