@@ -6,7 +6,6 @@
 #include <cstdlib>
 #include <cstring>
 #include <new>
-#include <thread>
 #include <vector>
 
 #include "common.cuh"
@@ -107,8 +106,6 @@ int s2v_ctx_create(int device, s2v_ctx** out)
     ctx->sm_count = prop.multiProcessorCount;
     ctx->smem_optin = prop.sharedMemPerBlockOptin;
     bool ok = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) == cudaSuccess &&
-              cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking) == cudaSuccess &&
-              cudaEventCreateWithFlags(&ctx->ev_upload, cudaEventDisableTiming) == cudaSuccess &&
               cudaHostAlloc((void**)&ctx->dstatus_host, sizeof(s2v_device_status), cudaHostAllocMapped) == cudaSuccess &&
               cudaHostGetDevicePointer((void**)&ctx->dstatus_dev, ctx->dstatus_host, 0) == cudaSuccess;
     if (!ok) {
@@ -129,8 +126,6 @@ int s2v_ctx_destroy(s2v_ctx* ctx)
     {
         s2v_device_guard guard(ctx->device);
         if (ctx->stream) { cudaStreamSynchronize(ctx->stream); cudaStreamDestroy(ctx->stream); }
-        if (ctx->copy_stream) { cudaStreamSynchronize(ctx->copy_stream); cudaStreamDestroy(ctx->copy_stream); }
-        if (ctx->ev_upload) cudaEventDestroy(ctx->ev_upload);
         if (ctx->dstatus_host) cudaFreeHost(ctx->dstatus_host);
         if (ctx->staging.dev) cudaFree(ctx->staging.dev);
         if (ctx->staging.pinned) cudaFreeHost(ctx->staging.pinned);

@@ -31,8 +31,6 @@ struct s2v_ctx {
     int sm_count = 0;
     size_t smem_optin = 0;
     cudaStream_t stream = nullptr;       // the context's own non-blocking stream
-    cudaStream_t copy_stream = nullptr;  // uploads of the host-buffer entry point
-    cudaEvent_t ev_upload = nullptr;
     s2v_device_status* dstatus_host = nullptr;  // pinned + mapped
     s2v_device_status* dstatus_dev = nullptr;
     std::atomic<uint64_t> launches{0};

@@ -184,21 +184,17 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
         const int rp_rel = (int)(rp_abs - base);
         const int tile_nnz = __shfl_sync(0xffffffffu, rp_rel, TILE_R);
         if (lane <= TILE_R) rp_s[lane] = rp_rel;
-        const bool fits = tile_nnz <= IDX_CAP;
-        const int* ip;
-        const float* vp;
+        const bool fits = tile_nnz <= IDX_CAP;   // warp-uniform; almost always true
         if (fits) {
             for (int t = lane; t < tile_nnz; t += 32) {
                 idx_s[t] = col_idx[base + t];
                 if (HAS_VAL) val_s[t] = val[base + t];
             }
-            ip = idx_s;
-            vp = val_s;
-        } else {
-            ip = col_idx + base;
-            vp = HAS_VAL ? val + base : nullptr;
         }
         __syncwarp();
+        // index / value of the tile's t-th non-zero: shared memory when the tile fits, else global
+#define S2V_IDX(t) (fits ? idx_s[(t)] : __ldg(col_idx + base + (t)))
+#define S2V_VAL(t) (fits ? val_s[(t)] : __ldg(val + base + (t)))
 
         // ---- 2. gather + sum in CSR order.
         //   FLAT (low-degree, wide rows): each group of LPR lanes walks the non-zeros of its
@@ -223,7 +219,7 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
     }
 #define S2V_ACCUM(u)                                                         \
     if (HAS_VAL) {                                                           \
-        const float a = vp[t + (u)];                                         \
+        const float a = S2V_VAL(t + (u));                                         \
         acc.x = fmaf(a, v[u].x, acc.x); acc.y = fmaf(a, v[u].y, acc.y);      \
         acc.z = fmaf(a, v[u].z, acc.z); acc.w = fmaf(a, v[u].w, acc.w);      \
     } else {                                                                 \
@@ -232,7 +228,7 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
             for (; t + U <= ee; t += U) {
                 float4 v[U];
 #pragma unroll
-                for (int u = 0; u < U; ++u) v[u] = ld_nc_f4(H4 + (int64_t)ip[t + u] * LPR + sl);
+                for (int u = 0; u < U; ++u) v[u] = ld_nc_f4(H4 + (int64_t)S2V_IDX(t + u) * LPR + sl);
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     S2V_FLUSH_ROWS(t + u)
@@ -243,7 +239,7 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
                 float4 v[U];
 #pragma unroll
                 for (int u = 0; u < U; ++u)
-                    if (t + u < ee) v[u] = ld_nc_f4(H4 + (int64_t)ip[t + u] * LPR + sl);
+                    if (t + u < ee) v[u] = ld_nc_f4(H4 + (int64_t)S2V_IDX(t + u) * LPR + sl);
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     if (t + u < ee) {
@@ -271,11 +267,11 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
             for (; t + U <= end; t += U) {
                 float4 v[U];
 #pragma unroll
-                for (int u = 0; u < U; ++u) v[u] = ld_nc_f4(H4 + (int64_t)ip[t + u] * LPR + sl);
+                for (int u = 0; u < U; ++u) v[u] = ld_nc_f4(H4 + (int64_t)S2V_IDX(t + u) * LPR + sl);
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     if (HAS_VAL) {
-                        const float a = vp[t + u];
+                        const float a = S2V_VAL(t + u);
                         acc.x = fmaf(a, v[u].x, acc.x); acc.y = fmaf(a, v[u].y, acc.y);
                         acc.z = fmaf(a, v[u].z, acc.z); acc.w = fmaf(a, v[u].w, acc.w);
                     } else {
@@ -287,12 +283,12 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
                 float4 v[U];
 #pragma unroll
                 for (int u = 0; u < U; ++u)
-                    v[u] = (t + u < end) ? ld_nc_f4(H4 + (int64_t)ip[t + u] * LPR + sl) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    v[u] = (t + u < end) ? ld_nc_f4(H4 + (int64_t)S2V_IDX(t + u) * LPR + sl) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     if (t + u < end) {
                         if (HAS_VAL) {
-                            const float a = vp[t + u];
+                            const float a = S2V_VAL(t + u);
                             acc.x = fmaf(a, v[u].x, acc.x); acc.y = fmaf(a, v[u].y, acc.y);
                             acc.z = fmaf(a, v[u].z, acc.z); acc.w = fmaf(a, v[u].w, acc.w);
                         } else {
@@ -306,6 +302,8 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
         }
         __syncwarp();
 
+#undef S2V_IDX
+#undef S2V_VAL
         // ---- 3. [16 x D] * W[D x D] on the tensor cores, 3xTF32
         float c[NT][4];
 #pragma unroll

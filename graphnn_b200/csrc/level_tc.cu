@@ -243,8 +243,9 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
         for (int64_t it = 0; it < my_tiles; ++it) {
             int* idx_s = idx_buf[it & 1];
             const int* rp_s = idx_s + TC_IDX_CAP;
-            const int* ip = (nnz <= TC_IDX_CAP) ? idx_s : col_idx + base;
+            const bool fits = nnz <= TC_IDX_CAP;   // warp-uniform; almost always true
             const float* vp = HAS_VAL ? val + base : nullptr;
+#define TC_IDX(t) (fits ? idx_s[(t)] : __ldg(col_idx + base + (t)))
             // prefetch (registers): offsets of tile it+2, indices of tile it+1
             rp_next2 = load_rp(it + 2);
             const int32_t base1 = __shfl_sync(0xffffffffu, rp_next, 0);
@@ -271,11 +272,11 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
     _Pragma("unroll") for (int u = 0; u < TC_U; ++u)                                               \
         if ((t0) + u < ee) {                                                                       \
             if (HSRC_TABLE) {                                                                      \
-                const int tg = __ldg(x_index + ip[(t0) + u]);                                      \
+                const int tg = __ldg(x_index + TC_IDX((t0) + u));                                      \
                 const float4 w = ld_nc_f4(reinterpret_cast<const float4*>(X) + (int64_t)tg * LPR + lane); \
                 v[u] = make_float4(relu_ref(w.x), relu_ref(w.y), relu_ref(w.z), relu_ref(w.w));    \
             } else {                                                                               \
-                v[u] = ld_nc_f4(H4 + (int64_t)ip[(t0) + u] * LPR + lane);                          \
+                v[u] = ld_nc_f4(H4 + (int64_t)TC_IDX((t0) + u) * LPR + lane);                          \
             }                                                                                      \
         }
 #define TC_CONSUME(v, t0)                                                                          \
@@ -312,6 +313,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             }
 #undef TC_LOAD
 #undef TC_CONSUME
+#undef TC_IDX
             while (row < TC_ROWS_PER_GW) {
                 *reinterpret_cast<float4*>(srow) = acc;
                 acc = make_float4(0.f, 0.f, 0.f, 0.f);
