@@ -286,8 +286,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     st = stream.cuda_stream
     level_events = []
 
-    # d = 128: the first level reads ReLU(W_in[tag]) directly (H0 is never written), as s2v_forward_f32 does
-    first_fused = d == 128 and N >= 16384
+    # d = 64 / 128: the first level reads ReLU(W_in[tag]) directly (H0 is never written), as s2v_forward_f32 does
+    first_fused = d in (64, 128) and N >= 16384
 
     def step(timed: bool):
         cur, nxt = ha, hbuf
@@ -386,7 +386,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     "from_edge_list": {"value": world * G * e2e_steps / (e2e_build_ms * 1e-3), "ms_per_step": e2e_build_ms / e2e_steps,
                                        "includes": "the same plus s2v_build_n2n_csr_host (stable sort of the raw edge list)"}},
             "gpu_launches": int(launches),
-            "roofline": {"kernel": ("s2v_level_tc_kernel (tcgen05, d=128, X looked up from W_in by tag)" if d == 128 else
+            "roofline": {"kernel": (f"s2v_level_tc_kernel (tcgen05, d={d}, X looked up from W_in by tag)" if d in (64, 128) else
                                     f"s2v_level_kernel<{d}> (X looked up from W_in by tag)"), "bound": "hbm", "achieved": ach,
                          "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs, "peak_kind": peak_kind,
                          # dram__bytes_read + dram__bytes_write of one launch on this very input

@@ -211,8 +211,8 @@ int s2v_level_first_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n, int d, const
     if (!row_ptr || !W || !table || !tags || !out) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level_first: NULL pointer");
     if (!s2v_aligned16(W) || !s2v_aligned16(table) || !s2v_aligned16(out))
         return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level_first: W, table, out must be 16-byte aligned");
-    if (d != 128 || ctx->tc_mode == 0 || (ctx->tc_mode == 1 && n < S2V_TC_MIN_ROWS))
-        return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "level_first: only the d = 128 tcgen05 kernel has this form; materialise H0 instead");
+    if (!s2v_use_tc(ctx, d, n))
+        return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "level_first: only the tcgen05 kernel (d = 64 or 128, large batch) has this form; materialise H0 instead");
     const int rc = s2v_launch_level_tc(ctx, s2v_pick_stream(ctx, stream), n, d, row_ptr, col_idx, val, nullptr, W, nullptr, table,
                                        tags, out);
     if (rc == S2V_ERR_UNSUPPORTED) return s2v_fail(ctx, rc, "level_first: shape not supported by the tcgen05 kernel");
@@ -260,7 +260,7 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
     const bool onehot = batch->tags != nullptr && d % 4 == 0;
     // first level straight from the tags (no H0 in memory) when the tcgen05 kernel takes this shape
     bool first_fused = false;
-    if (onehot && L >= 1 && d == 128 && (ctx->tc_mode == 2 || (ctx->tc_mode == 1 && N >= S2V_TC_MIN_ROWS))) {
+    if (onehot && L >= 1 && s2v_use_tc(ctx, d, N)) {
         float* dst = (L == 1 && embed_out) ? embed_out : ha;
         rc = s2v_level_first_f32(ctx, st, N, d, batch->n2n_row_ptr, batch->n2n_col_idx, batch->n2n_val, model->p_node_conv,
                                  model->w_n2l, model->num_feat, batch->tags, dst);

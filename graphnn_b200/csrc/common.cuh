@@ -124,8 +124,13 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p)
 
 #endif  // __CUDACC__
 
-// Rows from which the d = 128 level goes to the tcgen05 kernel (128-row tiles, one CTA per SM).
+// Rows from which the d = 64 / d = 128 level goes to the tcgen05 kernel (128-row tiles, one CTA per SM).
 constexpr int64_t S2V_TC_MIN_ROWS = 16384;
+inline bool s2v_use_tc(const s2v_ctx* ctx, int d, int64_t n_rows)
+{
+    if (d != 128 && d != 64) return false;
+    return ctx->tc_mode == 2 || (ctx->tc_mode == 1 && n_rows >= S2V_TC_MIN_ROWS);
+}
 
 // launchers implemented in the .cu files (host side)
 int s2v_launch_level_tc(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int d, const int32_t* row_ptr,

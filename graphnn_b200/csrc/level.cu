@@ -406,7 +406,7 @@ int s2v_launch_level(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int64_t n_sr
 {
     (void)n_src;
     if (n_rows == 0) return S2V_OK;
-    if (d == 128 && !rp64 && (ctx->tc_mode == 2 || (ctx->tc_mode == 1 && n_rows >= S2V_TC_MIN_ROWS))) {
+    if (!rp64 && s2v_use_tc(ctx, d, n_rows)) {
         const int rc = s2v_launch_level_tc(ctx, st, n_rows, d, (const int32_t*)row_ptr, col_idx, val, H, W, X, table,
                                            x_index, out);
         if (rc != S2V_ERR_UNSUPPORTED) return rc;

@@ -1,4 +1,4 @@
-// Fused structure2vec level for d = 128 with the dense stage on the 5th-generation
+// Fused structure2vec level for d = 64 and d = 128 with the dense stage on the 5th-generation
 // tensor cores (tcgen05.mma, accumulators and the A operand in tensor memory).
 //
 //     out[i,:] = ReLU( (sum_{t in row i} val[t] * H[col_idx[t],:]) * W + X[i,:] )
@@ -8,19 +8,21 @@
 // warp-level mma.sync path (level.cu) is bounded by the legacy tensor rate there, well
 // above the HBM time.  tcgen05 runs the same 3xTF32 product about four times faster and
 // needs no registers for the operands, so the kernel goes back to being memory-bound.
+// At d = 64 the gain is the warp specialisation: dedicated gather warps keep a software-
+// pipelined stream of neighbour loads in flight instead of alternating with the product.
 //
 // One persistent 768-thread CTA per SM, 128-row tiles, three warp roles connected by mbarriers:
 //
 //   gather warps (16) : the tile's CSR slice -> shared memory, neighbour rows summed in
-//                       CSR order as one flat software-pipelined stream (4..8 loads in flight per
-//                       lane, indices prefetched a tile ahead) into a
-//                       fp32 staging tile [128 x 128];
+//                       CSR order as one flat software-pipelined stream per group of d/4
+//                       lanes (8 loads in flight per lane, indices prefetched a tile ahead)
+//                       into a fp32 staging tile [128 x d] (two of them at d = 64);
 //   operand warps (4) : read the staging tile "transposed" (thread = row), split every
 //                       value into a TF32 head and tail and store both into tensor memory
-//                       (tcgen05.st); one elected thread then issues the 48 MMAs
-//                       (lo*hi, hi*lo, hi*hi over K = 128 in steps of 8) against W^T, which
-//                       sits in shared memory split the same way in the K-major
-//                       128-byte-swizzle layout, and commits them to an mbarrier;
+//                       (tcgen05.st; double-buffered at d = 64); one elected thread then
+//                       issues the 3 * d/8 MMAs (lo*hi, hi*lo, hi*hi over K = d in steps
+//                       of 8) against W^T, which sits in shared memory split the same way
+//                       in the K-major 128-byte-swizzle layout, and commits them to an mbarrier;
 //   epilogue warps (4): tcgen05.ld the fp32 accumulator (double-buffered in tensor
 //                       memory), transpose 32x32 blocks through shared memory, add X,
 //                       apply ReLU and store whole 128-byte row segments.
@@ -33,36 +35,49 @@
 namespace
 {
 
-constexpr int TC_D = 128;
 constexpr int TC_TILE = 128;           // rows per tile = MMA M
 constexpr int TC_GW = 16;              // gather warps (measured: 16 x 4 loads per chunk beats 8 x 8)
 constexpr int TC_AW = 4;               // operand warps (one per tensor-memory lane quarter)
 constexpr int TC_EW = 4;               // epilogue warps
 constexpr int TC_THREADS = (TC_GW + TC_AW + TC_EW) * 32;
-constexpr int TC_ROWS_PER_GW = TC_TILE / TC_GW;   // 16
+constexpr int TC_ROWS_PER_GW = TC_TILE / TC_GW;   // 8
 constexpr int TC_U = 4;
-constexpr int TC_IDX_CAP = 64;
-constexpr int TC_STAGE_STRIDE = TC_D + 4;         // floats; 33 float4 per row: thread-per-row float4 reads are conflict-free
 constexpr int TC_OUT_STRIDE = 36;                 // floats; 9 float4 per row
 constexpr int TC_WAIT_LIMIT = 1 << 22;
+constexpr int TC_MAX_STAGES = 2;
 
-// shared memory map (offsets from a 1024-byte aligned base)
-constexpr size_t TC_OFF_BHI = 0;
-constexpr size_t TC_OFF_BLO = TC_OFF_BHI + sizeof(float) * TC_D * TC_D;
-constexpr size_t TC_OFF_STAGE = TC_OFF_BLO + sizeof(float) * TC_D * TC_D;
-constexpr size_t TC_OFF_OUT = TC_OFF_STAGE + sizeof(float) * TC_TILE * TC_STAGE_STRIDE;
-constexpr size_t TC_OFF_GW = TC_OFF_OUT + sizeof(float) * TC_EW * 32 * TC_OUT_STRIDE;
-constexpr size_t TC_GW_BYTES = 2 * (sizeof(int) * TC_IDX_CAP + sizeof(int) * 32);   // double-buffered indices + row offsets
-constexpr size_t TC_OFF_BAR = TC_OFF_GW + TC_GW_BYTES * TC_GW;
-constexpr size_t TC_SMEM_BYTES = TC_OFF_BAR + 128 + 1024;   // + barriers/flags + alignment slack
+// Per-width configuration and shared memory map (offsets from a 1024-byte aligned base).
+template <int D>
+struct TcCfg {
+    static constexpr int NSTAGE = (D == 64) ? 2 : 1;   // fp32 staging tiles (shared memory allows two at d = 64)
+    static constexpr int NABUF = (D == 64) ? 2 : 1;    // A-operand buffers in tensor memory (512 columns allow two at d = 64)
+    static constexpr int IDX_CAP = (D == 64) ? 128 : 64;   // column indices of one gather warp's 8 rows kept in shared memory
+    static constexpr int STAGE_STRIDE = D + 4;         // floats; an odd number of float4 per row: thread-per-row float4 reads are conflict-free
+    static constexpr size_t OFF_BHI = 0;
+    static constexpr size_t OFF_BLO = OFF_BHI + sizeof(float) * D * D;
+    static constexpr size_t OFF_STAGE = OFF_BLO + sizeof(float) * D * D;
+    static constexpr size_t STAGE_BYTES = sizeof(float) * TC_TILE * STAGE_STRIDE;
+    static constexpr size_t OFF_OUT = OFF_STAGE + STAGE_BYTES * NSTAGE;
+    static constexpr size_t OFF_GW = OFF_OUT + sizeof(float) * TC_EW * 32 * TC_OUT_STRIDE;
+    static constexpr size_t GW_BYTES = 2 * (sizeof(int) * IDX_CAP + sizeof(int) * 32);   // double-buffered indices + row offsets
+    static constexpr size_t OFF_BAR = OFF_GW + GW_BYTES * TC_GW;
+    static constexpr size_t SMEM_BYTES = OFF_BAR + 256 + 1024;   // + barriers/flags + alignment slack
+    // tensor memory columns: A head/tail per buffer, then two accumulators
+    static constexpr uint32_t TM_A = 0;                 // + ab*2D : head, + ab*2D + D : tail
+    static constexpr uint32_t TM_ACC = 2 * D * NABUF;   // + b*D
+    static_assert(2 * D * NABUF + 2 * D <= 512, "tensor memory has 512 columns");
+    // instruction descriptor: D = f32, A = B = tf32, both K-major, M = 128, N = D
+    static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(TC_TILE >> 4) << 24);
+};
 
-// mbarriers.  FULL/SFREE exist per tensor-memory lane quarter (32 rows = two gather warps, one operand warp).
+// mbarriers.  FULL/SFREE exist per staging tile and tensor-memory lane quarter (32 rows = four gather
+// warps, one operand warp).
 enum {
-    BAR_FULL0 = 0,                   // +q : the quarter's 32 rows of the staging tile are written
-    BAR_SFREE0 = 4,                  // +q : the quarter's rows have been read back and may be overwritten
-    BAR_AREADY = 8,                  // all four quarters of the A operand are in tensor memory
-    BAR_MMA0, BAR_MMA1,              // the MMAs into accumulator buffer 0 / 1 are complete
-    BAR_DFREE0, BAR_DFREE1,          // accumulator buffer 0 / 1 has been read by the epilogue
+    BAR_FULL0 = 0,                                 // +4*s+q : the quarter's 32 rows of staging tile s are written
+    BAR_SFREE0 = BAR_FULL0 + 4 * TC_MAX_STAGES,    // +4*s+q : the quarter's rows have been read back and may be overwritten
+    BAR_AREADY0 = BAR_SFREE0 + 4 * TC_MAX_STAGES,  // +ab : all four quarters of A-operand buffer ab are in tensor memory
+    BAR_MMA0 = BAR_AREADY0 + 2, BAR_MMA1,          // the MMAs into accumulator buffer 0 / 1 are complete
+    BAR_DFREE0, BAR_DFREE1,                        // accumulator buffer 0 / 1 has been read by the epilogue
     BAR_COUNT
 };
 
@@ -119,17 +134,14 @@ __device__ __forceinline__ uint64_t tc_b_desc(uint32_t smem_addr)
     d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
     return d;
 }
-// instruction descriptor: D = f32, A = B = tf32, both K-major, M = 128, N = 128
-constexpr uint32_t TC_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TC_D >> 3) << 17) | ((uint32_t)(TC_TILE >> 4) << 24);
-
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t accumulate)
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
 {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
         :
-        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(TC_IDESC), "r"(accumulate)
+        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
@@ -145,7 +157,7 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_tmem, uint64_
 #define TC_TRACE_PRINT(role) do {} while (0)
 #endif
 
-template <bool HAS_VAL, int XMODE, bool HSRC_TABLE>
+template <int D, bool HAS_VAL, int XMODE, bool HSRC_TABLE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict__ row_ptr,
                     const int32_t* __restrict__ col_idx, const float* __restrict__ val, const float* __restrict__ H,
@@ -154,12 +166,14 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
 {
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
-    float* Bhi = reinterpret_cast<float*>(smem + TC_OFF_BHI);
-    float* Blo = reinterpret_cast<float*>(smem + TC_OFF_BLO);
-    float* stage = reinterpret_cast<float*>(smem + TC_OFF_STAGE);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TC_OFF_BAR);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + TC_OFF_BAR + 8 * BAR_COUNT);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TC_OFF_BAR + 8 * BAR_COUNT + 8);
+    using Cfg = TcCfg<D>;
+    constexpr int NSTAGE = Cfg::NSTAGE, NABUF = Cfg::NABUF, IDX_CAP = Cfg::IDX_CAP, STAGE_STRIDE = Cfg::STAGE_STRIDE;
+    float* Bhi = reinterpret_cast<float*>(smem + Cfg::OFF_BHI);
+    float* Blo = reinterpret_cast<float*>(smem + Cfg::OFF_BLO);
+    float* stage0 = reinterpret_cast<float*>(smem + Cfg::OFF_STAGE);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 8 * BAR_COUNT);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 8 * BAR_COUNT + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar0 = smem_u32(bars);
@@ -167,11 +181,11 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
 
     // ---- set-up: barriers, tensor memory, W^T split into TF32 head/tail in the MMA layout
     if (threadIdx.x == 0) {
-        for (int qq = 0; qq < 4; ++qq) {
+        for (int qq = 0; qq < 4 * NSTAGE; ++qq) {
             tc_mbar_init(bar(BAR_FULL0 + qq), TC_GW / 4);
             tc_mbar_init(bar(BAR_SFREE0 + qq), 1);
         }
-        tc_mbar_init(bar(BAR_AREADY), TC_AW);
+        for (int ab = 0; ab < NABUF; ++ab) tc_mbar_init(bar(BAR_AREADY0 + ab), TC_AW);
         tc_mbar_init(bar(BAR_MMA0), 1);
         tc_mbar_init(bar(BAR_MMA1), 1);
         tc_mbar_init(bar(BAR_DFREE0), TC_EW);
@@ -184,13 +198,13 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // B[n][k] = W[k][n]; element (n, k) lives at  kb*16384 + n*128 + ((kk/4) ^ (n&7))*16 + (kk%4)*4,
+    // B[n][k] = W[k][n]; element (n, k) lives at  kb*(D*128) + n*128 + ((kk/4) ^ (n&7))*16 + (kk%4)*4,
     // kb = k/32, kk = k%32.  Each task converts 4 consecutive k of one n: one 16-byte store per matrix.
-    for (int e = threadIdx.x; e < TC_D * TC_D / 4; e += TC_THREADS) {
-        const int n = e % TC_D, kq = e / TC_D;   // k = 4*kq .. 4*kq+3
+    for (int e = threadIdx.x; e < D * D / 4; e += TC_THREADS) {
+        const int n = e % D, kq = e / D;   // k = 4*kq .. 4*kq+3
         float w[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) w[j] = __ldg(W + (int64_t)(4 * kq + j) * TC_D + n);
+        for (int j = 0; j < 4; ++j) w[j] = __ldg(W + (int64_t)(4 * kq + j) * D + n);
         uint32_t hi[4], lo[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -198,7 +212,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             lo[j] = tf32_rn(w[j] - __uint_as_float(hi[j]));
         }
         const int kb = kq >> 3, chunk = kq & 7;
-        const size_t off = (size_t)kb * 16384 + (size_t)n * 128 + (size_t)((chunk ^ (n & 7)) * 16);
+        const size_t off = (size_t)kb * (D * 128) + (size_t)n * 128 + (size_t)((chunk ^ (n & 7)) * 16);
         *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(Bhi) + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
         *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(Blo) + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
@@ -207,17 +221,20 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t TM_AHI = tmem_base, TM_ALO = tmem_base + 128, TM_D = tmem_base + 256;
+    const uint32_t TM_A = tmem_base + Cfg::TM_A, TM_ACC = tmem_base + Cfg::TM_ACC;
 
     const int64_t my_tiles = (num_tiles > (int64_t)blockIdx.x) ? (num_tiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
 
     if (warp < TC_GW) {
         // =========================== gather warps ===========================
-        unsigned char* gbase = smem + TC_OFF_GW + TC_GW_BYTES * warp;
-        int* idx_buf[2] = {reinterpret_cast<int*>(gbase), reinterpret_cast<int*>(gbase) + TC_IDX_CAP + 32};
+        unsigned char* gbase = smem + Cfg::OFF_GW + Cfg::GW_BYTES * warp;
+        int* idx_buf[2] = {reinterpret_cast<int*>(gbase), reinterpret_cast<int*>(gbase) + IDX_CAP + 32};
         const float4* __restrict__ H4 = reinterpret_cast<const float4*>(H);
-        constexpr int LPR = TC_D / 4;   // 32: one lane group = the whole warp
-        constexpr int IPL = TC_IDX_CAP / 32;   // prefetched indices per lane
+        constexpr int LPR = D / 4;                       // lanes that cover one row with float4
+        constexpr int RPG = TC_ROWS_PER_GW / (32 / LPR); // consecutive rows one lane group streams through
+        constexpr int IPL = IDX_CAP / 32;                // prefetched indices per lane
+        const int sub = lane / LPR, sl = lane % LPR;
+        const int q = warp / (TC_GW / 4);                // tensor-memory lane quarter my rows belong to
         // Row offsets are fetched two tiles ahead and column indices one tile ahead, into
         // registers while the current tile is gathered, so no tile waits on that chain.
         auto load_rp = [&](int64_t it) -> int32_t {
@@ -233,8 +250,8 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             base = __shfl_sync(0xffffffffu, rp_next, 0);
             const int rel = rp_next - base;
             nnz = __shfl_sync(0xffffffffu, rel, TC_ROWS_PER_GW);
-            if (lane <= TC_ROWS_PER_GW) idx_buf[0][TC_IDX_CAP + lane] = rel;
-            if (nnz <= TC_IDX_CAP)
+            if (lane <= TC_ROWS_PER_GW) idx_buf[0][IDX_CAP + lane] = rel;
+            if (nnz <= IDX_CAP)
                 for (int t = lane; t < nnz; t += 32) idx_buf[0][t] = col_idx[base + t];
             rp_next = rp_next2;
         }
@@ -242,8 +259,9 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
         TC_TRACE_DECL();
         for (int64_t it = 0; it < my_tiles; ++it) {
             int* idx_s = idx_buf[it & 1];
-            const int* rp_s = idx_s + TC_IDX_CAP;
-            const bool fits = nnz <= TC_IDX_CAP;   // warp-uniform; almost always true
+            const int* rp_s = idx_s + IDX_CAP;
+            const bool fits = nnz <= IDX_CAP;   // warp-uniform; almost always true
+            const int s = (int)(it % NSTAGE);
             const float* vp = HAS_VAL ? val + base : nullptr;
 #define TC_IDX(t) (fits ? idx_s[(t)] : __ldg(col_idx + base + (t)))
             // prefetch (registers): offsets of tile it+2, indices of tile it+1
@@ -254,39 +272,42 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             int idx_pref[IPL];
 #pragma unroll
             for (int j = 0; j < IPL; ++j)
-                idx_pref[j] = (nnz1 <= TC_IDX_CAP && lane + 32 * j < nnz1) ? col_idx[base1 + lane + 32 * j] : 0;
+                idx_pref[j] = (nnz1 <= IDX_CAP && lane + 32 * j < nnz1) ? col_idx[base1 + lane + 32 * j] : 0;
             TC_TRACE(0);
-            // Flat stream over this warp's rows' non-zeros, software-pipelined: the loads of chunk
-            // k+1 are in flight while chunk k is summed, and the first chunk is issued before
-            // waiting for the staging tile, so the wait costs no memory latency.
-            int row = 0;
-            int t = 0;
-            const int ee = nnz;
-            int row_end = rp_s[1];
-            float* srow = stage + (size_t)(warp * TC_ROWS_PER_GW) * TC_STAGE_STRIDE + lane * 4;
+            // Flat stream over the non-zeros of my lane group's RPG rows, software-pipelined: the
+            // loads of chunk k+1 are in flight while chunk k is summed, and the first chunk is
+            // issued before waiting for the staging tile, so the wait costs no memory latency.
+            int row = sub * RPG;
+            const int row_stop = row + RPG;
+            int t = rp_s[row];
+            const int ee = rp_s[row_stop];
+            int row_end = rp_s[row + 1];
+            float* srow = stage0 + (size_t)s * (TC_TILE * STAGE_STRIDE) + (size_t)(warp * TC_ROWS_PER_GW + row) * STAGE_STRIDE + sl * 4;
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             float4 va[TC_U], vb[TC_U];
 // HSRC_TABLE: the gather source is not a matrix but ReLU(table[x_index[col], :]) -- the first level of
 // the classifier with one-hot inputs, where H0 = ReLU(W_in[tag]) need not be materialised
-#define TC_LOAD(v, t0)                                                                             \
-    _Pragma("unroll") for (int u = 0; u < TC_U; ++u)                                               \
+#define TC_LOAD(v, t0) TC_LOADN(v, t0, TC_U)
+#define TC_LOADN(v, t0, NN)                                                                        \
+    _Pragma("unroll") for (int u = 0; u < NN; ++u)                                                 \
         if ((t0) + u < ee) {                                                                       \
             if (HSRC_TABLE) {                                                                      \
                 const int tg = __ldg(x_index + TC_IDX((t0) + u));                                      \
-                const float4 w = ld_nc_f4(reinterpret_cast<const float4*>(X) + (int64_t)tg * LPR + lane); \
+                const float4 w = ld_nc_f4(reinterpret_cast<const float4*>(X) + (int64_t)tg * LPR + sl); \
                 v[u] = make_float4(relu_ref(w.x), relu_ref(w.y), relu_ref(w.z), relu_ref(w.w));    \
             } else {                                                                               \
-                v[u] = ld_nc_f4(H4 + (int64_t)TC_IDX((t0) + u) * LPR + lane);                          \
+                v[u] = ld_nc_f4(H4 + (int64_t)TC_IDX((t0) + u) * LPR + sl);                            \
             }                                                                                      \
         }
-#define TC_CONSUME(v, t0)                                                                          \
-    _Pragma("unroll") for (int u = 0; u < TC_U; ++u) {                                             \
+#define TC_CONSUME(v, t0) TC_CONSUMEN(v, t0, TC_U)
+#define TC_CONSUMEN(v, t0, NN)                                                                     \
+    _Pragma("unroll") for (int u = 0; u < NN; ++u) {                                               \
         if ((t0) + u < ee) {                                                                       \
             while ((t0) + u == row_end) {                                                          \
                 *reinterpret_cast<float4*>(srow) = acc;                                            \
                 acc = make_float4(0.f, 0.f, 0.f, 0.f);                                             \
                 ++row;                                                                             \
-                srow += TC_STAGE_STRIDE;                                                           \
+                srow += STAGE_STRIDE;                                                              \
                 row_end = rp_s[row + 1];                                                           \
             }                                                                                      \
             if (HAS_VAL) {                                                                         \
@@ -298,60 +319,80 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             }                                                                                      \
         }                                                                                          \
     }
-            TC_LOAD(va, 0)
-            // my quarter of the staging tile is free once its operand warp has read tile it-1
-            if (it > 0 && !tc_wait(bar(BAR_SFREE0 + warp / (TC_GW / 4)), (uint32_t)((it - 1) & 1), abort_flag, status, 10)) break;
+            TC_LOAD(va, t)
+            // Pull the neighbour rows of the NEXT tile into L2 now, a whole tile ahead of their use:
+            // a prefetch holds no register, so the rows in flight are not bounded by the register file.
+            if (!HSRC_TABLE) {
+#pragma unroll
+                for (int j = 0; j < IPL; ++j)
+                    if (nnz1 <= IDX_CAP && lane + 32 * j < nnz1) {
+                        const char* rowp = reinterpret_cast<const char*>(H4 + (int64_t)idx_pref[j] * LPR);
+#pragma unroll
+                        for (int l = 0; l < D * 4 / 128; ++l) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + 128 * l));
+                    }
+            }
+            // my quarter of staging tile s is free once its operand warp has read tile it-NSTAGE
+            if (it >= NSTAGE && !tc_wait(bar(BAR_SFREE0 + 4 * s + q), (uint32_t)(((it - NSTAGE) / NSTAGE) & 1), abort_flag, status, 10)) break;
             TC_TRACE(1);
             while (t < ee) {
                 TC_LOAD(vb, t + TC_U)
+                TC_TRACE(2);
                 TC_CONSUME(va, t)
+                TC_TRACE(3);
                 t += TC_U;
                 if (t >= ee) break;
                 TC_LOAD(va, t + TC_U)
+                TC_TRACE(2);
                 TC_CONSUME(vb, t)
+                TC_TRACE(3);
                 t += TC_U;
             }
 #undef TC_LOAD
 #undef TC_CONSUME
+#undef TC_LOADN
+#undef TC_CONSUMEN
 #undef TC_IDX
-            while (row < TC_ROWS_PER_GW) {
+            while (row < row_stop) {
                 *reinterpret_cast<float4*>(srow) = acc;
                 acc = make_float4(0.f, 0.f, 0.f, 0.f);
                 ++row;
-                srow += TC_STAGE_STRIDE;
+                srow += STAGE_STRIDE;
             }
             __syncwarp();
-            if (lane == 0) tc_mbar_arrive(bar(BAR_FULL0 + warp / (TC_GW / 4)));
+            if (lane == 0) tc_mbar_arrive(bar(BAR_FULL0 + 4 * s + q));
             {   // publish the prefetched slice of tile it+1 in the other buffer
                 int* nb = idx_buf[(it + 1) & 1];
-                if (lane <= TC_ROWS_PER_GW) nb[TC_IDX_CAP + lane] = rel1;
+                if (lane <= TC_ROWS_PER_GW) nb[IDX_CAP + lane] = rel1;
 #pragma unroll
                 for (int j = 0; j < IPL; ++j)
-                    if (lane + 32 * j < nnz1 && nnz1 <= TC_IDX_CAP) nb[lane + 32 * j] = idx_pref[j];
+                    if (lane + 32 * j < nnz1 && nnz1 <= IDX_CAP) nb[lane + 32 * j] = idx_pref[j];
                 base = base1;
                 nnz = nnz1;
                 rp_next = rp_next2;
             }
             __syncwarp();
-            TC_TRACE(2);
+            TC_TRACE(4);
         }
         TC_TRACE_PRINT("gather");
     } else if (warp < TC_GW + TC_AW) {
         // =========================== operand warps ===========================
         const int q = warp & 3;   // tensor-memory lane quarter this warp may access
         const uint32_t lane_base = (uint32_t)(32 * q) << 16;
-        const float* my_row = stage + (size_t)(32 * q + lane) * TC_STAGE_STRIDE;
         TC_TRACE_DECL();
         for (int64_t it = 0; it < my_tiles; ++it) {
             const int b = (int)(it & 1);
-            if (!tc_wait(bar(BAR_FULL0 + q), (uint32_t)(it & 1), abort_flag, status, 20)) break;
+            const int s = (int)(it % NSTAGE);
+            const int ab = (int)(it % NABUF);
+            const float* my_row = stage0 + (size_t)s * (TC_TILE * STAGE_STRIDE) + (size_t)(32 * q + lane) * STAGE_STRIDE;
+            const uint32_t TM_AHI = TM_A + (uint32_t)(2 * D * ab), TM_ALO = TM_AHI + D;
+            if (!tc_wait(bar(BAR_FULL0 + 4 * s + q), (uint32_t)((it / NSTAGE) & 1), abort_flag, status, 20)) break;
             TC_TRACE(0);
-            // the previous tile's MMAs must be done reading the A operand in tensor memory
-            if (it > 0 && !tc_wait(bar(BAR_MMA0 + (int)((it - 1) & 1)), (uint32_t)(((it - 1) >> 1) & 1), abort_flag, status, 21)) break;
+            // the MMAs of the tile that used this A-operand buffer before must be done reading it
+            if (it >= NABUF && !tc_wait(bar(BAR_MMA0 + (int)((it - NABUF) & 1)), (uint32_t)(((it - NABUF) >> 1) & 1), abort_flag, status, 21)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             TC_TRACE(1);
 #pragma unroll 1
-            for (int kc = 0; kc < TC_D / 32; ++kc) {
+            for (int kc = 0; kc < D / 32; ++kc) {
                 uint32_t hi[32], lo[32];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -376,19 +417,19 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             __syncwarp();
-            if (lane == 0) tc_mbar_arrive(bar(BAR_SFREE0 + q));   // my 32 rows of the staging tile are consumed
+            if (lane == 0) tc_mbar_arrive(bar(BAR_SFREE0 + 4 * s + q));   // my 32 rows of the staging tile are consumed
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            if (lane == 0) tc_mbar_arrive(bar(BAR_AREADY));   // my quarter of the A operand is in tensor memory
+            if (lane == 0) tc_mbar_arrive(bar(BAR_AREADY0 + ab));   // my quarter of the A operand is in tensor memory
             TC_TRACE(2);
             if (q == 0) {
                 // one elected thread issues the tile's MMAs
-                bool ok = tc_wait(bar(BAR_AREADY), (uint32_t)(it & 1), abort_flag, status, 22);
+                bool ok = tc_wait(bar(BAR_AREADY0 + ab), (uint32_t)((it / NABUF) & 1), abort_flag, status, 22);
                 if (ok && it >= 2) ok = tc_wait(bar(BAR_DFREE0 + b), (uint32_t)(((it - 2) >> 1) & 1), abort_flag, status, 23);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 TC_TRACE(3);
                 if (lane == 0) {
-                    const uint32_t d_tmem = TM_D + 128u * (uint32_t)b;
+                    const uint32_t d_tmem = TM_ACC + (uint32_t)(D * b);
                     const uint32_t bhi = smem_u32(Bhi), blo = smem_u32(Blo);
                     uint32_t accumulate = 0;
 #pragma unroll 1
@@ -396,9 +437,9 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                         const uint32_t a_base = (pass == 0) ? TM_ALO : TM_AHI;
                         const uint32_t b_base = (pass == 1) ? blo : bhi;
 #pragma unroll 1
-                        for (int ks = 0; ks < TC_D / 8; ++ks) {
-                            const uint32_t b_addr = b_base + (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
-                            tc_mma(d_tmem, a_base + 8u * (uint32_t)ks, tc_b_desc(b_addr), accumulate);
+                        for (int ks = 0; ks < D / 8; ++ks) {
+                            const uint32_t b_addr = b_base + (uint32_t)(ks >> 2) * (uint32_t)(D * 128) + (uint32_t)(ks & 3) * 32u;
+                            tc_mma(d_tmem, a_base + 8u * (uint32_t)ks, tc_b_desc(b_addr), Cfg::IDESC, accumulate);
                             accumulate = 1;
                         }
                     }
@@ -415,7 +456,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
         // =========================== epilogue warps ===========================
         const int q = warp & 3;
         const uint32_t lane_base = (uint32_t)(32 * q) << 16;
-        float* ostage = reinterpret_cast<float*>(smem + TC_OFF_OUT) + (size_t)q * 32 * TC_OUT_STRIDE;
+        float* ostage = reinterpret_cast<float*>(smem + Cfg::OFF_OUT) + (size_t)q * 32 * TC_OUT_STRIDE;
         const int rsub = lane >> 3, c4 = lane & 7;
         TC_TRACE_DECL();
         for (int64_t it = 0; it < my_tiles; ++it) {
@@ -432,7 +473,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             TC_TRACE(0);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-            for (int cc = 0; cc < TC_D / 32; ++cc) {
+            for (int cc = 0; cc < D / 32; ++cc) {
                 uint32_t v[32];
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -441,10 +482,10 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                       "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
                       "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
                       "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                    : "r"(TM_D + 128u * (uint32_t)b + lane_base + 32u * (uint32_t)cc)
+                    : "r"(TM_ACC + (uint32_t)(D * b) + lane_base + 32u * (uint32_t)cc)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (cc == TC_D / 32 - 1) {   // the accumulator buffer is fully read: hand it back early
+                if (cc == D / 32 - 1) {   // the accumulator buffer is fully read: hand it back early
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     if (lane == 0) tc_mbar_arrive(bar(BAR_DFREE0 + b));
                 }
@@ -463,10 +504,10 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                     const int64_t row = tile * TC_TILE + 32 * q + rl;
                     o[rr] = *reinterpret_cast<const float4*>(ostage + rl * TC_OUT_STRIDE + 4 * c4);
                     x[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (XMODE == 1 && row < n_rows) x[rr] = ld_stream_f4(reinterpret_cast<const float4*>(X) + row * (TC_D / 4) + col4);
+                    if (XMODE == 1 && row < n_rows) x[rr] = ld_stream_f4(reinterpret_cast<const float4*>(X) + row * (D / 4) + col4);
                     if (XMODE == 2) {
                         const int xi = __shfl_sync(0xffffffffu, my_xi, rl);
-                        if (row < n_rows) x[rr] = ld_nc_f4(reinterpret_cast<const float4*>(X) + (int64_t)xi * (TC_D / 4) + col4);
+                        if (row < n_rows) x[rr] = ld_nc_f4(reinterpret_cast<const float4*>(X) + (int64_t)xi * (D / 4) + col4);
                     }
                 }
 #pragma unroll
@@ -478,7 +519,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                         r.y = relu_ref(o[rr].y + x[rr].y);
                         r.z = relu_ref(o[rr].z + x[rr].z);
                         r.w = relu_ref(o[rr].w + x[rr].w);
-                        reinterpret_cast<float4*>(out)[row * (TC_D / 4) + col4] = r;
+                        reinterpret_cast<float4*>(out)[row * (D / 4) + col4] = r;
                     }
                 }
                 __syncwarp();
@@ -495,16 +536,18 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
 }
 
-template <bool HAS_VAL, int XMODE, bool HSRC_TABLE = false>
+template <int D, bool HAS_VAL, int XMODE, bool HSRC_TABLE = false>
 int tc_launch(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const int32_t* rp, const int32_t* ci, const float* val,
               const float* H, const float* W, const float* X, const int32_t* x_index, float* out)
 {
-    auto kern = s2v_level_tc_kernel<HAS_VAL, XMODE, HSRC_TABLE>;
-    S2V_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
+    auto kern = s2v_level_tc_kernel<D, HAS_VAL, XMODE, HSRC_TABLE>;
+    constexpr size_t SMEM = TcCfg<D>::SMEM_BYTES;
+    if (SMEM > ctx->smem_optin) return S2V_ERR_UNSUPPORTED;
+    S2V_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
     const int64_t num_tiles = (n_rows + TC_TILE - 1) / TC_TILE;
     int64_t blocks = num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count;
     if (blocks < 1) blocks = 1;
-    kern<<<(unsigned)blocks, TC_THREADS, TC_SMEM_BYTES, st>>>(n_rows, num_tiles, rp, ci, val, H, W, X, x_index, out,
+    kern<<<(unsigned)blocks, TC_THREADS, SMEM, st>>>(n_rows, num_tiles, rp, ci, val, H, W, X, x_index, out,
                                                                ctx->dstatus_dev);
     S2V_CHECK_LAUNCH(ctx, "s2v_level_tc_kernel");
     return S2V_OK;
@@ -512,22 +555,21 @@ int tc_launch(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const int32_t* rp, 
 
 }  // namespace
 
-// d = 128, 32-bit row offsets.  Returns S2V_ERR_UNSUPPORTED for anything else (the caller falls back).
+// d = 64 or 128, 32-bit row offsets.  Returns S2V_ERR_UNSUPPORTED for anything else (the caller falls back).
 // H == NULL with a table: the gather source is ReLU(table[x_index[col], :]) (square matrices only).
-int s2v_launch_level_tc(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int d, const int32_t* row_ptr,
-                        const int32_t* col_idx, const float* val, const float* H, const float* W, const float* X,
-                        const float* table, const int32_t* x_index, float* out)
+template <int D>
+static int tc_dispatch(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const int32_t* row_ptr, const int32_t* col_idx,
+                       const float* val, const float* H, const float* W, const float* X, const float* table,
+                       const int32_t* x_index, float* out)
 {
-    if (d != TC_D) return S2V_ERR_UNSUPPORTED;
-    if (TC_SMEM_BYTES > ctx->smem_optin) return S2V_ERR_UNSUPPORTED;
     if (!H) {
         if (!table || !x_index) return S2V_ERR_UNSUPPORTED;
-        return val ? tc_launch<true, 2, true>(ctx, st, n_rows, row_ptr, col_idx, val, nullptr, W, table, x_index, out)
-                   : tc_launch<false, 2, true>(ctx, st, n_rows, row_ptr, col_idx, val, nullptr, W, table, x_index, out);
+        return val ? tc_launch<D, true, 2, true>(ctx, st, n_rows, row_ptr, col_idx, val, nullptr, W, table, x_index, out)
+                   : tc_launch<D, false, 2, true>(ctx, st, n_rows, row_ptr, col_idx, val, nullptr, W, table, x_index, out);
     }
     const int xmode = table ? 2 : (X ? 1 : 0);
     const float* xa = table ? table : X;
-#define TC_GO(HV, XM) return tc_launch<HV, XM>(ctx, st, n_rows, row_ptr, col_idx, val, H, W, xa, x_index, out)
+#define TC_GO(HV, XM) return tc_launch<D, HV, XM>(ctx, st, n_rows, row_ptr, col_idx, val, H, W, xa, x_index, out)
     if (val) {
         if (xmode == 0) TC_GO(true, 0);
         if (xmode == 1) TC_GO(true, 1);
@@ -537,4 +579,13 @@ int s2v_launch_level_tc(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int d, co
     if (xmode == 1) TC_GO(false, 1);
     TC_GO(false, 2);
 #undef TC_GO
+}
+
+int s2v_launch_level_tc(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int d, const int32_t* row_ptr,
+                        const int32_t* col_idx, const float* val, const float* H, const float* W, const float* X,
+                        const float* table, const int32_t* x_index, float* out)
+{
+    if (d == 128) return tc_dispatch<128>(ctx, st, n_rows, row_ptr, col_idx, val, H, W, X, table, x_index, out);
+    if (d == 64) return tc_dispatch<64>(ctx, st, n_rows, row_ptr, col_idx, val, H, W, X, table, x_index, out);
+    return S2V_ERR_UNSUPPORTED;
 }

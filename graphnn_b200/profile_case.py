@@ -41,7 +41,7 @@ def main():
         launch = lambda: ctx.level(rp, ci, None, H, W, X, out, stream=st)
         desc = f"{p.name}: n={p.n_rows} nnz={p.nnz}"
     else:
-        b = synth.molecules_16k(seed=0) if args.case == "mol_d128" else synth.proteins_4k(seed=0, num_graphs=1024)
+        b = synth.molecules_16k(seed=0) if args.case == "mol_d128" else synth.proteins_4k(seed=0, num_graphs=2048)
         rp_h, ci_h, _ = capi.build_n2n_csr_host(b.num_nodes, b.edge_src, b.edge_dst, with_val=False)
         rp, ci, tags = up(rp_h), up(ci_h), up(b.tags.astype(np.int32))
         W, table = up(b.weights["p_node_conv"]), up(b.weights["w_n2l"])

@@ -111,7 +111,7 @@ def test_first_level_straight_from_tags(gpu_ctx, oracle_lib):
     gpu_ctx.synchronize()
     assert torch.equal(fused, two_step)                       # same arithmetic in the same order
     assert_close(fused.cpu().numpy(), o["levels"][1], "first level from tags")
-    small = synth.mutag_like(seed=0)                          # d = 64: no such kernel, the caller must fall back
+    small = synth.mutag_like(seed=0)                          # small batch: not taken by the tcgen05 kernel, the caller must fall back
     with pytest.raises(S2VError) as e:
         gpu_ctx.level_first(dev(np.zeros(small.num_nodes + 1, np.int32)), None, None, dev(small.weights["p_node_conv"]),
                             dev(small.weights["w_n2l"]), dev(small.tags.astype(np.int32)),
