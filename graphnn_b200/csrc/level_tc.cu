@@ -6,29 +6,31 @@
 // Why a second form of the kernel: at d = 128 the product [rows x 128] * [128 x 128] in
 // 3xTF32 costs 3 * 2 * 128^2 flop per row against 1.5 KB of compulsory traffic; the
 // warp-level mma.sync path (level.cu) is bounded by the legacy tensor rate there, well
-// above the HBM time.  tcgen05 runs the same 3xTF32 product about four times faster and
+// above the HBM time.  tcgen05 runs the same 3xTF32 product several times faster and
 // needs no registers for the operands, so the kernel goes back to being memory-bound.
-// At d = 64 the gain is the warp specialisation: dedicated gather warps keep a software-
-// pipelined stream of neighbour loads in flight instead of alternating with the product.
 //
-// One persistent 768-thread CTA per SM, 128-row tiles, three warp roles connected by mbarriers:
+// One persistent 544-thread CTA per SM, 128-row tiles.  Sixteen symmetric worker warps and
+// one MMA-issue warp, connected by mbarriers:
 //
-//   gather warps (16) : the tile's CSR slice -> shared memory, neighbour rows summed in
-//                       CSR order as one flat software-pipelined stream per group of d/4
-//                       lanes (8 loads in flight per lane, indices prefetched a tile ahead)
-//                       into a fp32 staging tile [128 x d] (two of them at d = 64);
-//   operand warps (4) : read the staging tile "transposed" (thread = row), split every
-//                       value into a TF32 head and tail and store both into tensor memory
-//                       (tcgen05.st; double-buffered at d = 64); one elected thread then
-//                       issues the 3 * d/8 MMAs (lo*hi, hi*lo, hi*hi over K = d in steps
-//                       of 8) against W^T, which sits in shared memory split the same way
-//                       in the K-major 128-byte-swizzle layout, and commits them to an mbarrier;
-//   epilogue warps (4): tcgen05.ld the fp32 accumulator (double-buffered in tensor
-//                       memory), transpose 32x32 blocks through shared memory, add X,
-//                       apply ReLU and store whole 128-byte row segments.
+//   worker w (quarter q = w % 4 of the tensor-memory lanes, slot j = w / 4), per tile:
+//     gather   : rows 32q + 8j .. +7 of the tile: the CSR slice comes through shared memory
+//                (indices prefetched a tile ahead, their rows prefetched into L2), neighbour
+//                rows are summed in CSR order as one flat software-pipelined stream per group
+//                of d/4 lanes (8 loads in flight per lane, no branch per non-zero: row ends come from a
+//                bit mask built with warp votes) into a fp32 staging tile [128 x d];
+//     operand  : once the quarter's four warps are done: thread = row, columns [d/4*j, d/4*(j+1)):
+//                split every value into a TF32 head and tail and store both into tensor
+//                memory (tcgen05.st);
+//     epilogue : the PREVIOUS tile's accumulator, same rows and columns: tcgen05.ld, transpose
+//                through the warp's own (now idle) slab of the staging tile, add X, apply ReLU
+//                and store whole row segments;
+//   MMA warp  : when all sixteen operand blocks are in tensor memory, one thread issues the
+//                3 * d/8 MMAs (lo*hi, hi*lo, hi*hi over K = d in steps of 8) against W^T, which
+//                sits in shared memory split the same way in the K-major 128-byte-swizzle
+//                layout, into one of two accumulators, and commits them to an mbarrier.
 //
-// The gather of tile i+1 overlaps the operand/MMA/epilogue work of tile i.  Every wait is
-// bounded: on a time-out the kernel records S2V_ERR_DEVICE_TIMEOUT, raises a CTA-wide
+// The MMAs of tile i overlap the epilogue of tile i-1 and the gather of tile i+1.  Every wait
+// is bounded: on a time-out the kernel records S2V_ERR_DEVICE_TIMEOUT, raises a CTA-wide
 // abort flag, drains, frees its tensor memory and returns.
 #include "common.cuh"
 
@@ -36,48 +38,43 @@ namespace
 {
 
 constexpr int TC_TILE = 128;           // rows per tile = MMA M
-constexpr int TC_GW = 16;              // gather warps (measured: 16 x 4 loads per chunk beats 8 x 8)
-constexpr int TC_AW = 4;               // operand warps (one per tensor-memory lane quarter)
-constexpr int TC_EW = 4;               // epilogue warps
-constexpr int TC_THREADS = (TC_GW + TC_AW + TC_EW) * 32;
+constexpr int TC_GW = 16;              // worker warps, four per tensor-memory lane quarter
+constexpr int TC_MW = 1;               // MMA-issue warp (one elected lane)
+constexpr int TC_THREADS = (TC_GW + TC_MW) * 32;
 constexpr int TC_ROWS_PER_GW = TC_TILE / TC_GW;   // 8
 constexpr int TC_U = 4;
-constexpr int TC_OUT_STRIDE = 36;                 // floats; 9 float4 per row
-constexpr int TC_WAIT_LIMIT = 1 << 22;
-constexpr int TC_MAX_STAGES = 2;
+constexpr int TC_WAIT_LIMIT = 1 << 17;        // polls before a wait gives up (each may sleep up to TC_SUSPEND_NS)
+constexpr uint32_t TC_SUSPEND_NS = 10000;    // a waiting thread sleeps in the barrier unit instead of spinning through the issue port
 
 // Per-width configuration and shared memory map (offsets from a 1024-byte aligned base).
 template <int D>
 struct TcCfg {
-    static constexpr int NSTAGE = (D == 64) ? 2 : 1;   // fp32 staging tiles (shared memory allows two at d = 64)
-    static constexpr int NABUF = (D == 64) ? 2 : 1;    // A-operand buffers in tensor memory (512 columns allow two at d = 64)
-    static constexpr int IDX_CAP = (D == 64) ? 128 : 64;   // column indices of one gather warp's 8 rows kept in shared memory
+    static constexpr int IDX_CAP = (D == 64) ? 128 : 64;   // column indices of one worker's 8 rows kept in shared memory
     static constexpr int STAGE_STRIDE = D + 4;         // floats; an odd number of float4 per row: thread-per-row float4 reads are conflict-free
     static constexpr size_t OFF_BHI = 0;
     static constexpr size_t OFF_BLO = OFF_BHI + sizeof(float) * D * D;
     static constexpr size_t OFF_STAGE = OFF_BLO + sizeof(float) * D * D;
     static constexpr size_t STAGE_BYTES = sizeof(float) * TC_TILE * STAGE_STRIDE;
-    static constexpr size_t OFF_OUT = OFF_STAGE + STAGE_BYTES * NSTAGE;
-    static constexpr size_t OFF_GW = OFF_OUT + sizeof(float) * TC_EW * 32 * TC_OUT_STRIDE;
+    static constexpr size_t OFF_GW = OFF_STAGE + STAGE_BYTES;
     static constexpr size_t GW_BYTES = 2 * (sizeof(int) * IDX_CAP + sizeof(int) * 32);   // double-buffered indices + row offsets
     static constexpr size_t OFF_BAR = OFF_GW + GW_BYTES * TC_GW;
     static constexpr size_t SMEM_BYTES = OFF_BAR + 256 + 1024;   // + barriers/flags + alignment slack
-    // tensor memory columns: A head/tail per buffer, then two accumulators
-    static constexpr uint32_t TM_A = 0;                 // + ab*2D : head, + ab*2D + D : tail
-    static constexpr uint32_t TM_ACC = 2 * D * NABUF;   // + b*D
-    static_assert(2 * D * NABUF + 2 * D <= 512, "tensor memory has 512 columns");
+    // tensor memory columns: A head, A tail, two accumulators
+    static constexpr uint32_t TM_AHI = 0, TM_ACC = 2 * D;   // A tail at TM_AHI + D, accumulator b at TM_ACC + b*D
+    static_assert(4 * D <= 512, "tensor memory has 512 columns");
+    // a worker's slab of the staging tile (8 rows) doubles as its 32 x d/4 transposition buffer
+    static_assert(TC_ROWS_PER_GW * STAGE_STRIDE >= 32 * (D / 4), "transposition buffer does not fit the slab");
     // instruction descriptor: D = f32, A = B = tf32, both K-major, M = 128, N = D
     static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(TC_TILE >> 4) << 24);
 };
 
-// mbarriers.  FULL/SFREE exist per staging tile and tensor-memory lane quarter (32 rows = four gather
-// warps, one operand warp).
+// mbarriers.  FULL/SFREE exist per tensor-memory lane quarter (32 rows = four workers).
 enum {
-    BAR_FULL0 = 0,                                 // +4*s+q : the quarter's 32 rows of staging tile s are written
-    BAR_SFREE0 = BAR_FULL0 + 4 * TC_MAX_STAGES,    // +4*s+q : the quarter's rows have been read back and may be overwritten
-    BAR_AREADY0 = BAR_SFREE0 + 4 * TC_MAX_STAGES,  // +ab : all four quarters of A-operand buffer ab are in tensor memory
-    BAR_MMA0 = BAR_AREADY0 + 2, BAR_MMA1,          // the MMAs into accumulator buffer 0 / 1 are complete
-    BAR_DFREE0, BAR_DFREE1,                        // accumulator buffer 0 / 1 has been read by the epilogue
+    BAR_FULL0 = 0,                   // +q : the quarter's 32 rows of the staging tile are written
+    BAR_SFREE0 = 4,                  // +q : the quarter's rows have been read back by all four workers
+    BAR_AREADY = 8,                  // all sixteen blocks of the A operand are in tensor memory
+    BAR_MMA0, BAR_MMA1,              // the MMAs into accumulator buffer 0 / 1 are complete
+    BAR_DFREE0, BAR_DFREE1,          // accumulator buffer 0 / 1 has been read by all sixteen workers
     BAR_COUNT
 };
 
@@ -94,10 +91,10 @@ __device__ __forceinline__ bool tc_mbar_try(uint32_t bar, uint32_t parity)
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(TC_SUSPEND_NS)
         : "memory");
     return ok != 0;
 }
@@ -116,6 +113,21 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
         }
     }
     return true;
+}
+// TF32 head by truncation (the subtraction is then exact) and the tail cut to TF32 the same way:
+// integer-pipe work only, no conversion-unit instruction.  head + tail differs from v by < 2^-21 |v|.
+__device__ __forceinline__ void tc_split(float v, uint32_t& head, uint32_t& tail)
+{
+    head = __float_as_uint(v) & 0xffffe000u;
+    tail = __float_as_uint(v - __uint_as_float(head)) & 0xffffe000u;
+}
+// A 32-bit load that stays where it is written: the values fetched a tile ahead (row offsets, X row
+// indices) must be issued early, and a plain load may be moved down to its first use.
+__device__ __forceinline__ int32_t tc_ld_early(const int32_t* p)
+{
+    int32_t v;
+    asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
 }
 __device__ __forceinline__ uint32_t tf32_rn(float v)
 {
@@ -144,13 +156,29 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_tmem, uint64_
         : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// tcgen05.st / tcgen05.ld of this thread's tensor-memory lane, 8 or 16 consecutive 32-bit columns
+__device__ __forceinline__ void tc_st_cols8(uint32_t addr, const uint32_t* r)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(addr), "r"(r[0]), "r"(r[1]),
+                 "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tc_ld_cols16(uint32_t addr, uint32_t* v)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(addr)
+        : "memory");
+}
 
 // Optional cycle accounting per warp role (compile with -DS2V_TC_TRACE): block 0 prints, per
 // role, the cycles spent in each numbered section.  Compiled out by default.
 #ifdef S2V_TC_TRACE
-#define TC_TRACE_DECL() long long tr__[6] = {0, 0, 0, 0, 0, 0}; long long t0__ = clock64()
+#define TC_TRACE_DECL() long long tr__[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long t0__ = clock64()
 #define TC_TRACE(slot) do { const long long t1__ = clock64(); tr__[slot] += t1__ - t0__; t0__ = t1__; } while (0)
-#define TC_TRACE_PRINT(role) do { if (blockIdx.x == 0 && lane == 0) printf("%s warp %d tiles %lld: %lld %lld %lld %lld %lld %lld\n", role, warp, (long long)my_tiles, tr__[0], tr__[1], tr__[2], tr__[3], tr__[4], tr__[5]); } while (0)
+#define TC_TRACE_PRINT(role) do { if (blockIdx.x == 0 && lane == 0) printf("%s warp %d tiles %d: %lld %lld %lld %lld %lld %lld %lld %lld\n", role, warp, my_tiles, tr__[0], tr__[1], tr__[2], tr__[3], tr__[4], tr__[5], tr__[6], tr__[7]); } while (0)
 #else
 #define TC_TRACE_DECL() do {} while (0)
 #define TC_TRACE(slot) do {} while (0)
@@ -165,12 +193,14 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                     float* __restrict__ out, s2v_device_status* status)
 {
     extern __shared__ unsigned char tc_smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    // 1024-byte alignment as an OFFSET from the shared array: a pointer rebuilt from an integer would lose
+    // its address space and every access through it would become a generic load/store
+    unsigned char* smem = tc_smem_raw + ((1024u - (smem_u32(tc_smem_raw) & 1023u)) & 1023u);
     using Cfg = TcCfg<D>;
-    constexpr int NSTAGE = Cfg::NSTAGE, NABUF = Cfg::NABUF, IDX_CAP = Cfg::IDX_CAP, STAGE_STRIDE = Cfg::STAGE_STRIDE;
+    constexpr int IDX_CAP = Cfg::IDX_CAP, STAGE_STRIDE = Cfg::STAGE_STRIDE;
     float* Bhi = reinterpret_cast<float*>(smem + Cfg::OFF_BHI);
     float* Blo = reinterpret_cast<float*>(smem + Cfg::OFF_BLO);
-    float* stage0 = reinterpret_cast<float*>(smem + Cfg::OFF_STAGE);
+    float* stage = reinterpret_cast<float*>(smem + Cfg::OFF_STAGE);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 8 * BAR_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 8 * BAR_COUNT + 8);
@@ -181,15 +211,15 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
 
     // ---- set-up: barriers, tensor memory, W^T split into TF32 head/tail in the MMA layout
     if (threadIdx.x == 0) {
-        for (int qq = 0; qq < 4 * NSTAGE; ++qq) {
+        for (int qq = 0; qq < 4; ++qq) {
             tc_mbar_init(bar(BAR_FULL0 + qq), TC_GW / 4);
-            tc_mbar_init(bar(BAR_SFREE0 + qq), 1);
+            tc_mbar_init(bar(BAR_SFREE0 + qq), TC_GW / 4);
         }
-        for (int ab = 0; ab < NABUF; ++ab) tc_mbar_init(bar(BAR_AREADY0 + ab), TC_AW);
+        tc_mbar_init(bar(BAR_AREADY), TC_GW);
         tc_mbar_init(bar(BAR_MMA0), 1);
         tc_mbar_init(bar(BAR_MMA1), 1);
-        tc_mbar_init(bar(BAR_DFREE0), TC_EW);
-        tc_mbar_init(bar(BAR_DFREE1), TC_EW);
+        tc_mbar_init(bar(BAR_DFREE0), TC_GW);
+        tc_mbar_init(bar(BAR_DFREE1), TC_GW);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -221,26 +251,41 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t TM_A = tmem_base + Cfg::TM_A, TM_ACC = tmem_base + Cfg::TM_ACC;
+    const uint32_t TM_AHI = tmem_base + Cfg::TM_AHI, TM_ACC = tmem_base + Cfg::TM_ACC;
 
-    const int64_t my_tiles = (num_tiles > (int64_t)blockIdx.x) ? (num_tiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+    const int my_tiles = (int)((num_tiles > (int64_t)blockIdx.x) ? (num_tiles - 1 - blockIdx.x) / gridDim.x + 1 : 0);
 
     if (warp < TC_GW) {
-        // =========================== gather warps ===========================
+        // =========================== worker warps ===========================
+        constexpr int CW = D / 4;                        // operand / accumulator columns handled per worker
+        constexpr int C4 = CW / 4;                       // float4 per row of my column block: 8 (d = 128) or 4 (d = 64)
+        constexpr int RPI = 32 / C4;                     // rows per store instruction in the epilogue: 4 or 8
+        constexpr int NRR = 32 / RPI;                    // store instructions per column block: 8 or 4
+        const int q = warp & 3, j = warp >> 2;
+        const int row0 = 32 * q + TC_ROWS_PER_GW * j;    // my first row within the tile
+        const uint32_t lane_base = (uint32_t)(32 * q) << 16;
         unsigned char* gbase = smem + Cfg::OFF_GW + Cfg::GW_BYTES * warp;
-        int* idx_buf[2] = {reinterpret_cast<int*>(gbase), reinterpret_cast<int*>(gbase) + IDX_CAP + 32};
+        int* const idx_base = reinterpret_cast<int*>(gbase);   // two buffers of IDX_CAP indices + 32 row offsets
+        constexpr int IDX_BUF = IDX_CAP + 32;
         const float4* __restrict__ H4 = reinterpret_cast<const float4*>(H);
+        const float4* __restrict__ X4 = reinterpret_cast<const float4*>(X);
         constexpr int LPR = D / 4;                       // lanes that cover one row with float4
         constexpr int RPG = TC_ROWS_PER_GW / (32 / LPR); // consecutive rows one lane group streams through
         constexpr int IPL = IDX_CAP / 32;                // prefetched indices per lane
         const int sub = lane / LPR, sl = lane % LPR;
-        const int q = warp / (TC_GW / 4);                // tensor-memory lane quarter my rows belong to
+        float* const slab = stage + (size_t)row0 * STAGE_STRIDE;   // my 8 rows; also my transposition buffer
+        const int ersub = lane / C4, ec4 = lane % C4;    // epilogue: row within a store instruction, float4 column
         // Row offsets are fetched two tiles ahead and column indices one tile ahead, into
         // registers while the current tile is gathered, so no tile waits on that chain.
-        auto load_rp = [&](int64_t it) -> int32_t {
-            int64_t rpi = (blockIdx.x + it * gridDim.x) * TC_TILE + (int64_t)warp * TC_ROWS_PER_GW + lane;
+        auto load_rp = [&](int it) -> int32_t {
+            int64_t rpi = ((int64_t)blockIdx.x + (int64_t)it * gridDim.x) * TC_TILE + row0 + lane;
             if (rpi > n_rows) rpi = n_rows;
-            return lane <= TC_ROWS_PER_GW ? row_ptr[rpi] : 0;
+            return lane <= TC_ROWS_PER_GW ? tc_ld_early(row_ptr + rpi) : 0;
+        };
+        // X row index of "my" epilogue row (lane = row within the quarter)
+        auto load_xi = [&](int it) -> int {
+            const int64_t mr = ((int64_t)blockIdx.x + (int64_t)it * gridDim.x) * TC_TILE + 32 * q + lane;
+            return (XMODE == 2 && it < my_tiles && mr < n_rows) ? tc_ld_early(x_index + mr) : 0;
         };
         int32_t rp_next = load_rp(0);      // row offsets of the tile whose indices are fetched next
         int32_t rp_next2 = load_rp(1);
@@ -250,58 +295,60 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             base = __shfl_sync(0xffffffffu, rp_next, 0);
             const int rel = rp_next - base;
             nnz = __shfl_sync(0xffffffffu, rel, TC_ROWS_PER_GW);
-            if (lane <= TC_ROWS_PER_GW) idx_buf[0][IDX_CAP + lane] = rel;
+            if (lane <= TC_ROWS_PER_GW) idx_base[IDX_CAP + lane] = rel;
             if (nnz <= IDX_CAP)
-                for (int t = lane; t < nnz; t += 32) idx_buf[0][t] = col_idx[base + t];
+                for (int t = lane; t < nnz; t += 32) idx_base[t] = col_idx[base + t];
             rp_next = rp_next2;
         }
+        int xi_prev = 0;                   // X row index of my row in tile it-1 (the tile whose epilogue runs in iteration it)
         __syncwarp();
         TC_TRACE_DECL();
-        for (int64_t it = 0; it < my_tiles; ++it) {
-            int* idx_s = idx_buf[it & 1];
-            const int* rp_s = idx_s + IDX_CAP;
-            const bool fits = nnz <= IDX_CAP;   // warp-uniform; almost always true
-            const int s = (int)(it % NSTAGE);
-            const float* vp = HAS_VAL ? val + base : nullptr;
+        // iteration `it`: gather + operand of tile it (it < my_tiles), epilogue of tile it-1 (it >= 1)
+        for (int it = 0; it <= my_tiles; ++it) {
+            const bool have_tile = it < my_tiles;
+            const int xi_this = load_xi(it);   // used one iteration later: a whole tile to arrive
+            if (have_tile) {
+                // -------------------------------- gather --------------------------------
+                int* idx_s = idx_base + (it & 1) * IDX_BUF;
+                const int* rp_s = idx_s + IDX_CAP;
+                const bool fits = nnz <= IDX_CAP;   // warp-uniform; almost always true
+                const float* vp = HAS_VAL ? val + base : nullptr;
 #define TC_IDX(t) (fits ? idx_s[(t)] : __ldg(col_idx + base + (t)))
-            // prefetch (registers): offsets of tile it+2, indices of tile it+1
-            rp_next2 = load_rp(it + 2);
-            const int32_t base1 = __shfl_sync(0xffffffffu, rp_next, 0);
-            const int rel1 = rp_next - base1;
-            const int nnz1 = __shfl_sync(0xffffffffu, rel1, TC_ROWS_PER_GW);
-            int idx_pref[IPL];
+                // prefetch (registers): offsets of tile it+2, indices of tile it+1
+                rp_next2 = load_rp(it + 2);
+                const int32_t base1 = __shfl_sync(0xffffffffu, rp_next, 0);
+                const int rel1 = rp_next - base1;
+                const int nnz1 = __shfl_sync(0xffffffffu, rel1, TC_ROWS_PER_GW);
+                int idx_pref[IPL];
 #pragma unroll
-            for (int j = 0; j < IPL; ++j)
-                idx_pref[j] = (nnz1 <= IDX_CAP && lane + 32 * j < nnz1) ? col_idx[base1 + lane + 32 * j] : 0;
-            TC_TRACE(0);
-            // Flat stream over the non-zeros of my lane group's RPG rows, software-pipelined: the
-            // loads of chunk k+1 are in flight while chunk k is summed, and the first chunk is
-            // issued before waiting for the staging tile, so the wait costs no memory latency.
-            int row = sub * RPG;
-            const int row_stop = row + RPG;
-            int t = rp_s[row];
-            const int ee = rp_s[row_stop];
-            int row_end = rp_s[row + 1];
-            float* srow = stage0 + (size_t)s * (TC_TILE * STAGE_STRIDE) + (size_t)(warp * TC_ROWS_PER_GW + row) * STAGE_STRIDE + sl * 4;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            float4 va[TC_U], vb[TC_U];
+                for (int jj = 0; jj < IPL; ++jj)
+                    idx_pref[jj] = (nnz1 <= IDX_CAP && lane + 32 * jj < nnz1) ? tc_ld_early(col_idx + base1 + lane + 32 * jj) : 0;
+                // Flat stream over the non-zeros of my lane group's RPG rows, software-pipelined: the
+                // loads of chunk k+1 are in flight while chunk k is summed.  My slab of the staging
+                // tile is free: the quarter finished reading it before my last epilogue used it.
+                int row = sub * RPG;
+                const int row_stop = row + RPG;
+                int t = rp_s[row];
+                const int ee = rp_s[row_stop];
+                int row_end = rp_s[row + 1];
+                float* srow = slab + (size_t)row * STAGE_STRIDE + sl * 4;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 va[TC_U], vb[TC_U];
 // HSRC_TABLE: the gather source is not a matrix but ReLU(table[x_index[col], :]) -- the first level of
 // the classifier with one-hot inputs, where H0 = ReLU(W_in[tag]) need not be materialised
-#define TC_LOAD(v, t0) TC_LOADN(v, t0, TC_U)
-#define TC_LOADN(v, t0, NN)                                                                        \
-    _Pragma("unroll") for (int u = 0; u < NN; ++u)                                                 \
+#define TC_LOAD(v, t0)                                                                             \
+    _Pragma("unroll") for (int u = 0; u < TC_U; ++u)                                               \
         if ((t0) + u < ee) {                                                                       \
             if (HSRC_TABLE) {                                                                      \
-                const int tg = __ldg(x_index + TC_IDX((t0) + u));                                      \
-                const float4 w = ld_nc_f4(reinterpret_cast<const float4*>(X) + (int64_t)tg * LPR + sl); \
+                const int tg = __ldg(x_index + TC_IDX((t0) + u));                                  \
+                const float4 w = ld_nc_f4(X4 + (int64_t)tg * LPR + sl);                            \
                 v[u] = make_float4(relu_ref(w.x), relu_ref(w.y), relu_ref(w.z), relu_ref(w.w));    \
             } else {                                                                               \
-                v[u] = ld_nc_f4(H4 + (int64_t)TC_IDX((t0) + u) * LPR + sl);                            \
+                v[u] = ld_nc_f4(H4 + (int64_t)TC_IDX((t0) + u) * LPR + sl);                    \
             }                                                                                      \
         }
-#define TC_CONSUME(v, t0) TC_CONSUMEN(v, t0, TC_U)
-#define TC_CONSUMEN(v, t0, NN)                                                                     \
-    _Pragma("unroll") for (int u = 0; u < NN; ++u) {                                               \
+#define TC_CONSUME(v, t0)                                                                          \
+    _Pragma("unroll") for (int u = 0; u < TC_U; ++u) {                                             \
         if ((t0) + u < ee) {                                                                       \
             while ((t0) + u == row_end) {                                                          \
                 *reinterpret_cast<float4*>(srow) = acc;                                            \
@@ -319,214 +366,284 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             }                                                                                      \
         }                                                                                          \
     }
-            TC_LOAD(va, t)
-            // Pull the neighbour rows of the NEXT tile into L2 now, a whole tile ahead of their use:
-            // a prefetch holds no register, so the rows in flight are not bounded by the register file.
-            if (!HSRC_TABLE) {
+                // Fast path (warp-uniform test): the tile's indices are in shared memory and every lane
+                // group has at most 64 non-zeros, so that "element p ends a row" fits a 64-bit mask.
+                // The masks are built by the warp together: lane r+1 speaks for row r.
+                constexpr int G = 32 / LPR;   // lane groups per warp
+                const int rel = lane <= TC_ROWS_PER_GW ? rp_s[lane] : 0;
+                const int relp = __shfl_up_sync(0xffffffffu, rel, 1);
+                const int rr_ = lane - 1;                                 // my row as a speaker
+                const bool isrow = lane >= 1 && lane <= TC_ROWS_PER_GW;
+                const int rg = isrow ? rr_ / RPG : 0;                     // my row's lane group
+                const int gbeg = __shfl_sync(0xffffffffu, rel, rg * RPG); // first non-zero of that group
+                const bool ne_row = isrow && rel > relp;
+                const int pos = rel - 1 - gbeg;                           // my row's last non-zero, counted within its group
+                const uint32_t ne_bits = __ballot_sync(0xffffffffu, ne_row) >> 1;        // bit r: row r is not empty
+                const bool big = __ballot_sync(0xffffffffu, isrow && pos >= 64) != 0;    // some group has more than 64 non-zeros
+                const bool fast = fits && !big;
+                if (fast) {
+                    // Branch-free form of the stream.  Per lane group: endmask bit p = 1 if the p-th
+                    // non-zero of the group is the last of its row; nxtmap holds, 4 bits per row, the next
+                    // non-empty row; empty rows are zero-filled up front.  Sums run in CSR order.
+                    const int r_lo = sub * RPG;
+                    uint32_t em_lo = 0, em_hi = 0, nxtmap = 0;
+                    const uint32_t ne_g_mine = (ne_bits >> (rg * RPG)) & ((1u << RPG) - 1u);   // speaker view: my row's group
+                    const int rin = rr_ - rg * RPG;                                          // my row within its group
+                    const uint32_t above = isrow ? (ne_g_mine >> (rin + 1)) : 0u;
+                    const uint32_t nxt_r = above ? (uint32_t)(rin + 1 + __ffs(above) - 1) : 15u;
 #pragma unroll
-                for (int j = 0; j < IPL; ++j)
-                    if (nnz1 <= IDX_CAP && lane + 32 * j < nnz1) {
-                        const char* rowp = reinterpret_cast<const char*>(H4 + (int64_t)idx_pref[j] * LPR);
-#pragma unroll
-                        for (int l = 0; l < D * 4 / 128; ++l) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + 128 * l));
+                    for (int gg = 0; gg < G; ++gg) {
+                        const bool mine = ne_row && rg == gg;
+                        const uint32_t lo = __reduce_or_sync(0xffffffffu, (mine && pos < 32) ? (1u << pos) : 0u);
+                        const uint32_t hi = __reduce_or_sync(0xffffffffu, (mine && pos >= 32) ? (1u << (pos - 32)) : 0u);
+                        const uint32_t nm = __reduce_or_sync(0xffffffffu, (isrow && rg == gg) ? (nxt_r << (4 * rin)) : 0u);
+                        if (gg == sub) { em_lo = lo; em_hi = hi; nxtmap = nm; }
                     }
-            }
-            // my quarter of staging tile s is free once its operand warp has read tile it-NSTAGE
-            if (it >= NSTAGE && !tc_wait(bar(BAR_SFREE0 + 4 * s + q), (uint32_t)(((it - NSTAGE) / NSTAGE) & 1), abort_flag, status, 10)) break;
-            TC_TRACE(1);
-            while (t < ee) {
-                TC_LOAD(vb, t + TC_U)
-                TC_TRACE(2);
-                TC_CONSUME(va, t)
-                TC_TRACE(3);
-                t += TC_U;
-                if (t >= ee) break;
-                TC_LOAD(va, t + TC_U)
-                TC_TRACE(2);
-                TC_CONSUME(vb, t)
-                TC_TRACE(3);
-                t += TC_U;
-            }
+                    unsigned long long em = ((unsigned long long)em_hi << 32) | em_lo;
+                    const uint32_t ne_g = (ne_bits >> r_lo) & ((1u << RPG) - 1u);            // worker view: my lane group
+#pragma unroll
+                    for (int r = 0; r < RPG; ++r)
+                        if (!((ne_g >> r) & 1u))
+                            *reinterpret_cast<float4*>(slab + (size_t)(r_lo + r) * STAGE_STRIDE + sl * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+                    const int nxt = ne_g ? (__ffs(ne_g) - 1) : 15;
+                    int frow = nxt;   // first non-empty row of my group (15: none)
+                    const bool any = t < ee;                  // my group has non-zeros at all
+                    const int cz = any ? idx_s[t] : 0;        // a safe column for the slots past the end: the group's first neighbour
+                    float wa[TC_U], wb[TC_U];
+#define TC_LOADF(v, wt, t0)                                                                         \
+    _Pragma("unroll") for (int u = 0; u < TC_U; ++u) {                                             \
+        const bool pv = (t0) + u < ee;                                                             \
+        const int c = pv ? idx_s[(t0) + u] : cz;                                                   \
+        if (HAS_VAL) wt[u] = pv ? __ldg(vp + (t0) + u) : 0.f;                                       \
+        if (HSRC_TABLE) {                                                                          \
+            const int tg = __ldg(x_index + c);                                                     \
+            const float4 xw = ld_nc_f4(X4 + (int64_t)tg * LPR + sl);                               \
+            v[u] = make_float4(relu_ref(xw.x), relu_ref(xw.y), relu_ref(xw.z), relu_ref(xw.w));    \
+        } else {                                                                                   \
+            v[u] = ld_nc_f4(H4 + (int64_t)c * LPR + sl);                                       \
+        }                                                                                          \
+    }
+// Slots past the group's end load the group's first neighbour again (a valid row, an L1 hit) and carry no
+// end bit: whatever they add to acc comes after the group's last row was stored and is never stored itself.
+#define TC_CONSF(v, wt)                                                                             \
+    {                                                                                              \
+        const uint32_t m4 = (uint32_t)em & 15u;                                                    \
+        em >>= 4;                                                                                  \
+        _Pragma("unroll") for (int u = 0; u < TC_U; ++u) {                                         \
+            if (HAS_VAL) {                                                                         \
+                acc.x = fmaf(wt[u], v[u].x, acc.x); acc.y = fmaf(wt[u], v[u].y, acc.y);            \
+                acc.z = fmaf(wt[u], v[u].z, acc.z); acc.w = fmaf(wt[u], v[u].w, acc.w);            \
+            } else {                                                                               \
+                acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;                \
+            }                                                                                      \
+            const bool last = (m4 >> u) & 1u;                                                      \
+            if (last) *reinterpret_cast<float4*>(slab + (size_t)(r_lo + frow) * STAGE_STRIDE + sl * 4) = acc; \
+            acc.x = last ? 0.f : acc.x; acc.y = last ? 0.f : acc.y;                                \
+            acc.z = last ? 0.f : acc.z; acc.w = last ? 0.f : acc.w;                                \
+            frow = last ? (int)((nxtmap >> (4 * frow)) & 15u) : frow;                              \
+        }                                                                                          \
+    }
+                    if (any) {
+                        TC_LOADF(va, wa, t)
+                        TC_LOADF(vb, wb, t + TC_U)
+                    }
+                    TC_TRACE(0);
+                    if (!HSRC_TABLE) {   // next tile's neighbour rows -> L2, a whole tile ahead of their use
+#pragma unroll
+                        for (int jj = 0; jj < IPL; ++jj)
+                            if (nnz1 <= IDX_CAP && lane + 32 * jj < nnz1) {
+                                const char* rowp = reinterpret_cast<const char*>(H4 + (int64_t)idx_pref[jj] * LPR);
+#pragma unroll
+                                for (int l = 0; l < D * 4 / 128; ++l) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + 128 * l));
+                            }
+                    }
+                    {   // publish the prefetched slice of tile it+1 in the other buffer (last read for tile it-1)
+                        int* nb = idx_base + ((it + 1) & 1) * IDX_BUF;
+                        if (lane <= TC_ROWS_PER_GW) nb[IDX_CAP + lane] = rel1;
+#pragma unroll
+                        for (int jj = 0; jj < IPL; ++jj)
+                            if (lane + 32 * jj < nnz1 && nnz1 <= IDX_CAP) nb[lane + 32 * jj] = idx_pref[jj];
+                    }
+                    TC_TRACE(1);
+                    while (t < ee) {
+                        TC_CONSF(va, wa)
+                        t += TC_U;
+                        if (t >= ee) break;
+                        TC_LOADF(va, wa, t + TC_U)
+                        TC_CONSF(vb, wb)
+                        t += TC_U;
+                        if (t >= ee) break;
+                        TC_LOADF(vb, wb, t + TC_U)
+                    }
+#undef TC_LOADF
+#undef TC_CONSF
+                } else {
+                TC_LOAD(va, t)
+                if (!HSRC_TABLE) {
+#pragma unroll
+                    for (int jj = 0; jj < IPL; ++jj)
+                        if (nnz1 <= IDX_CAP && lane + 32 * jj < nnz1) {
+                            const char* rowp = reinterpret_cast<const char*>(H4 + (int64_t)idx_pref[jj] * LPR);
+#pragma unroll
+                            for (int l = 0; l < D * 4 / 128; ++l) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + 128 * l));
+                        }
+                }
+                {
+                    int* nb = idx_base + ((it + 1) & 1) * IDX_BUF;
+                    if (lane <= TC_ROWS_PER_GW) nb[IDX_CAP + lane] = rel1;
+#pragma unroll
+                    for (int jj = 0; jj < IPL; ++jj)
+                        if (lane + 32 * jj < nnz1 && nnz1 <= IDX_CAP) nb[lane + 32 * jj] = idx_pref[jj];
+                }
+                while (t < ee) {
+                    TC_LOAD(vb, t + TC_U)
+                    TC_CONSUME(va, t)
+                    t += TC_U;
+                    if (t >= ee) break;
+                    TC_LOAD(va, t + TC_U)
+                    TC_CONSUME(vb, t)
+                    t += TC_U;
+                }
+                while (row < row_stop) {
+                    *reinterpret_cast<float4*>(srow) = acc;
+                    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    ++row;
+                    srow += STAGE_STRIDE;
+                }
+                }
 #undef TC_LOAD
 #undef TC_CONSUME
-#undef TC_LOADN
-#undef TC_CONSUMEN
 #undef TC_IDX
-            while (row < row_stop) {
-                *reinterpret_cast<float4*>(srow) = acc;
-                acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                ++row;
-                srow += STAGE_STRIDE;
-            }
-            __syncwarp();
-            if (lane == 0) tc_mbar_arrive(bar(BAR_FULL0 + 4 * s + q));
-            {   // publish the prefetched slice of tile it+1 in the other buffer
-                int* nb = idx_buf[(it + 1) & 1];
-                if (lane <= TC_ROWS_PER_GW) nb[IDX_CAP + lane] = rel1;
-#pragma unroll
-                for (int j = 0; j < IPL; ++j)
-                    if (lane + 32 * j < nnz1 && nnz1 <= IDX_CAP) nb[lane + 32 * j] = idx_pref[j];
                 base = base1;
                 nnz = nnz1;
                 rp_next = rp_next2;
-            }
-            __syncwarp();
-            TC_TRACE(4);
-        }
-        TC_TRACE_PRINT("gather");
-    } else if (warp < TC_GW + TC_AW) {
-        // =========================== operand warps ===========================
-        const int q = warp & 3;   // tensor-memory lane quarter this warp may access
-        const uint32_t lane_base = (uint32_t)(32 * q) << 16;
-        TC_TRACE_DECL();
-        for (int64_t it = 0; it < my_tiles; ++it) {
-            const int b = (int)(it & 1);
-            const int s = (int)(it % NSTAGE);
-            const int ab = (int)(it % NABUF);
-            const float* my_row = stage0 + (size_t)s * (TC_TILE * STAGE_STRIDE) + (size_t)(32 * q + lane) * STAGE_STRIDE;
-            const uint32_t TM_AHI = TM_A + (uint32_t)(2 * D * ab), TM_ALO = TM_AHI + D;
-            if (!tc_wait(bar(BAR_FULL0 + 4 * s + q), (uint32_t)((it / NSTAGE) & 1), abort_flag, status, 20)) break;
-            TC_TRACE(0);
-            // the MMAs of the tile that used this A-operand buffer before must be done reading it
-            if (it >= NABUF && !tc_wait(bar(BAR_MMA0 + (int)((it - NABUF) & 1)), (uint32_t)(((it - NABUF) >> 1) & 1), abort_flag, status, 21)) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            TC_TRACE(1);
-#pragma unroll 1
-            for (int kc = 0; kc < D / 32; ++kc) {
-                uint32_t hi[32], lo[32];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float4 v = *reinterpret_cast<const float4*>(my_row + 32 * kc + 4 * j);
-                    hi[4 * j + 0] = tf32_rn(v.x); lo[4 * j + 0] = tf32_rn(v.x - __uint_as_float(hi[4 * j + 0]));
-                    hi[4 * j + 1] = tf32_rn(v.y); lo[4 * j + 1] = tf32_rn(v.y - __uint_as_float(hi[4 * j + 1]));
-                    hi[4 * j + 2] = tf32_rn(v.z); lo[4 * j + 2] = tf32_rn(v.z - __uint_as_float(hi[4 * j + 2]));
-                    hi[4 * j + 3] = tf32_rn(v.w); lo[4 * j + 3] = tf32_rn(v.w - __uint_as_float(hi[4 * j + 3]));
-                }
-#define TC_ST32(addr, r)                                                                                             \
-    asm volatile(                                                                                                    \
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"        \
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(addr),                              \
-        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),  \
-        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),    \
-        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),    \
-        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])                                                                \
-        : "memory")
-                TC_ST32(TM_AHI + lane_base + 32 * kc, hi);
-                TC_ST32(TM_ALO + lane_base + 32 * kc, lo);
-#undef TC_ST32
-            }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) tc_mbar_arrive(bar(BAR_SFREE0 + 4 * s + q));   // my 32 rows of the staging tile are consumed
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            if (lane == 0) tc_mbar_arrive(bar(BAR_AREADY0 + ab));   // my quarter of the A operand is in tensor memory
-            TC_TRACE(2);
-            if (q == 0) {
-                // one elected thread issues the tile's MMAs
-                bool ok = tc_wait(bar(BAR_AREADY0 + ab), (uint32_t)((it / NABUF) & 1), abort_flag, status, 22);
-                if (ok && it >= 2) ok = tc_wait(bar(BAR_DFREE0 + b), (uint32_t)(((it - 2) >> 1) & 1), abort_flag, status, 23);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                TC_TRACE(3);
-                if (lane == 0) {
-                    const uint32_t d_tmem = TM_ACC + (uint32_t)(D * b);
-                    const uint32_t bhi = smem_u32(Bhi), blo = smem_u32(Blo);
-                    uint32_t accumulate = 0;
-#pragma unroll 1
-                    for (int pass = 0; pass < 3; ++pass) {   // lo*hi, hi*lo, hi*hi: small terms first
-                        const uint32_t a_base = (pass == 0) ? TM_ALO : TM_AHI;
-                        const uint32_t b_base = (pass == 1) ? blo : bhi;
-#pragma unroll 1
-                        for (int ks = 0; ks < D / 8; ++ks) {
-                            const uint32_t b_addr = b_base + (uint32_t)(ks >> 2) * (uint32_t)(D * 128) + (uint32_t)(ks & 3) * 32u;
-                            tc_mma(d_tmem, a_base + 8u * (uint32_t)ks, tc_b_desc(b_addr), Cfg::IDESC, accumulate);
-                            accumulate = 1;
-                        }
-                    }
-                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                                     bar(BAR_MMA0 + b))
-                                 : "memory");
-                }
                 __syncwarp();
+                if (lane == 0) tc_mbar_arrive(bar(BAR_FULL0 + q));
+                TC_TRACE(2);
+            }
+            // X term of tile it-1, my rows and columns: in flight across the waits below
+            const int64_t prow0 = (((int64_t)blockIdx.x + (int64_t)(it - 1) * gridDim.x) * TC_TILE) + 32 * q;
+            const int rows_left = it >= 1 ? (int)((n_rows - prow0) < 32 ? (n_rows - prow0) : 32) : 0;   // valid rows of my 32
+            float4 x[NRR];
+#pragma unroll
+            for (int rr = 0; rr < NRR; ++rr) {
+                const int rl = rr * RPI + ersub;
+                x[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (XMODE == 1 && rl < rows_left) x[rr] = ld_stream_f4(X4 + (prow0 + rl) * (D / 4) + C4 * j + ec4);
+                if (XMODE == 2) {
+                    const int xi = __shfl_sync(0xffffffffu, xi_prev, rl);
+                    if (rl < rows_left) x[rr] = ld_nc_f4(X4 + xi * (D / 4) + C4 * j + ec4);
+                }
+            }
+            // The MMAs of tile it-1 are complete: the A operand may be overwritten, the accumulator read.
+            if (it >= 1 && !tc_wait(bar(BAR_MMA0 + ((it - 1) & 1)), (uint32_t)(((it - 1) >> 1) & 1), abort_flag, status, 21)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            TC_TRACE(3);
+            if (have_tile) {
+                // -------------------------------- operand --------------------------------
+                // the quarter's 32 rows are complete; thread = row, my CW columns -> TF32 head and tail
+                if (!tc_wait(bar(BAR_FULL0 + q), (uint32_t)(it & 1), abort_flag, status, 20)) break;
                 TC_TRACE(4);
-            }
-        }
-        TC_TRACE_PRINT("operand");
-    } else {
-        // =========================== epilogue warps ===========================
-        const int q = warp & 3;
-        const uint32_t lane_base = (uint32_t)(32 * q) << 16;
-        float* ostage = reinterpret_cast<float*>(smem + Cfg::OFF_OUT) + (size_t)q * 32 * TC_OUT_STRIDE;
-        const int rsub = lane >> 3, c4 = lane & 7;
-        TC_TRACE_DECL();
-        for (int64_t it = 0; it < my_tiles; ++it) {
-            const int b = (int)(it & 1);
-            const int64_t tile = blockIdx.x + it * gridDim.x;
-            // X row index of "my" row (lane = row within this warp's 32 rows), fetched before the
-            // wait so that its latency hides behind the MMAs
-            int my_xi = 0;
-            if (XMODE == 2) {
-                const int64_t mr = tile * TC_TILE + 32 * q + lane;
-                if (mr < n_rows) my_xi = __ldg(x_index + mr);
-            }
-            if (!tc_wait(bar(BAR_MMA0 + b), (uint32_t)((it >> 1) & 1), abort_flag, status, 30)) break;
-            TC_TRACE(0);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-            for (int cc = 0; cc < D / 32; ++cc) {
-                uint32_t v[32];
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                    "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                      "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                      "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                    : "r"(TM_ACC + (uint32_t)(D * b) + lane_base + 32u * (uint32_t)cc)
-                    : "memory");
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (cc == D / 32 - 1) {   // the accumulator buffer is fully read: hand it back early
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    if (lane == 0) tc_mbar_arrive(bar(BAR_DFREE0 + b));
-                }
+                const float* my_row = stage + (size_t)(32 * q + lane) * STAGE_STRIDE + CW * j;
+                const uint32_t tm_a = TM_AHI + lane_base + (uint32_t)(CW * j);
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    *reinterpret_cast<uint4*>(ostage + lane * TC_OUT_STRIDE + 4 * j) =
-                        make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                __syncwarp();
-                // 4 rows x 128 bytes per instruction; all loads of the 8 row groups are issued
-                // before the first store so that their latencies overlap
-                const int64_t col4 = 8 * cc + c4;
-                float4 o[8], x[8];
+                for (int h = 0; h < CW / 8; ++h) {   // 8 columns at a time keeps the register count down
+                    uint32_t hi[8], lo[8];
 #pragma unroll
-                for (int rr = 0; rr < 8; ++rr) {
-                    const int rl = rr * 4 + rsub;
-                    const int64_t row = tile * TC_TILE + 32 * q + rl;
-                    o[rr] = *reinterpret_cast<const float4*>(ostage + rl * TC_OUT_STRIDE + 4 * c4);
-                    x[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (XMODE == 1 && row < n_rows) x[rr] = ld_stream_f4(reinterpret_cast<const float4*>(X) + row * (D / 4) + col4);
-                    if (XMODE == 2) {
-                        const int xi = __shfl_sync(0xffffffffu, my_xi, rl);
-                        if (row < n_rows) x[rr] = ld_nc_f4(reinterpret_cast<const float4*>(X) + (int64_t)xi * (D / 4) + col4);
+                    for (int c = 0; c < 2; ++c) {
+                        const float4 v4 = *reinterpret_cast<const float4*>(my_row + 8 * h + 4 * c);
+                        tc_split(v4.x, hi[4 * c + 0], lo[4 * c + 0]);
+                        tc_split(v4.y, hi[4 * c + 1], lo[4 * c + 1]);
+                        tc_split(v4.z, hi[4 * c + 2], lo[4 * c + 2]);
+                        tc_split(v4.w, hi[4 * c + 3], lo[4 * c + 3]);
                     }
+                    tc_st_cols8(tm_a + 8 * h, hi);
+                    tc_st_cols8(tm_a + D + 8 * h, lo);
                 }
+                __syncwarp();
+                if (lane == 0) tc_mbar_arrive(bar(BAR_SFREE0 + q));   // my share of the staging quarter is read
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) tc_mbar_arrive(bar(BAR_AREADY));   // my block of the A operand is in tensor memory
+                TC_TRACE(5);
+            }
+            // my slab is free once the quarter's four workers have read it for tile `it`
+            if (have_tile && !tc_wait(bar(BAR_SFREE0 + q), (uint32_t)(it & 1), abort_flag, status, 10)) break;
+            if (it >= 1) {
+                // -------------------------------- epilogue of tile it-1 --------------------------------
+                // accumulator block -> my slab, transposed: [32 rows][C4 float4], float4 column XOR-swizzled by row
+                const int b = (it - 1) & 1;
+                float4* const tb = reinterpret_cast<float4*>(slab);
+                const int wswz = (C4 == 8) ? (lane & 7) : ((lane >> 1) & 3);
 #pragma unroll
-                for (int rr = 0; rr < 8; ++rr) {
-                    const int64_t row = tile * TC_TILE + 32 * q + rr * 4 + rsub;
-                    if (row < n_rows) {
+                for (int h = 0; h < CW / 16; ++h) {   // 16 columns at a time keeps the register count down
+                    uint32_t v[16];
+                    tc_ld_cols16(TM_ACC + (uint32_t)(D * b) + lane_base + (uint32_t)(CW * j + 16 * h), v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        tb[lane * C4 + ((4 * h + c) ^ wswz)] = make_float4(__uint_as_float(v[4 * c]), __uint_as_float(v[4 * c + 1]),
+                                                                          __uint_as_float(v[4 * c + 2]), __uint_as_float(v[4 * c + 3]));
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) tc_mbar_arrive(bar(BAR_DFREE0 + b));   // my block of the accumulator is read
+                float4* const out_t = reinterpret_cast<float4*>(out) + (prow0 + ersub) * (D / 4) + C4 * j + ec4;
+#pragma unroll
+                for (int rr = 0; rr < NRR; ++rr) {
+                    const int rl = rr * RPI + ersub;
+                    const int swz = (C4 == 8) ? (rl & 7) : ((rl >> 1) & 3);
+                    const float4 o = tb[rl * C4 + (ec4 ^ swz)];
+                    if (rl < rows_left) {
                         float4 r;
-                        r.x = relu_ref(o[rr].x + x[rr].x);
-                        r.y = relu_ref(o[rr].y + x[rr].y);
-                        r.z = relu_ref(o[rr].z + x[rr].z);
-                        r.w = relu_ref(o[rr].w + x[rr].w);
-                        reinterpret_cast<float4*>(out)[row * (D / 4) + col4] = r;
+                        r.x = relu_ref(o.x + x[rr].x);
+                        r.y = relu_ref(o.y + x[rr].y);
+                        r.z = relu_ref(o.z + x[rr].z);
+                        r.w = relu_ref(o.w + x[rr].w);
+                        out_t[rr * RPI * (D / 4)] = r;
                     }
                 }
-                __syncwarp();
+                __syncwarp();   // the slab is rewritten by the next gather
+                TC_TRACE(6);
             }
+            xi_prev = xi_this;
+        }
+        TC_TRACE_PRINT("worker");
+    } else {
+        // =========================== MMA-issue warp ===========================
+        TC_TRACE_DECL();
+        for (int it = 0; it < my_tiles; ++it) {
+            const int b = it & 1;
+            // the whole A operand is in tensor memory, and the accumulator buffer has been read
+            bool ok = tc_wait(bar(BAR_AREADY), (uint32_t)(it & 1), abort_flag, status, 22);
+            if (ok && it >= 2) ok = tc_wait(bar(BAR_DFREE0 + b), (uint32_t)(((it - 2) >> 1) & 1), abort_flag, status, 23);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            TC_TRACE(0);
+            if (lane == 0) {
+                const uint32_t d_tmem = TM_ACC + (uint32_t)(D * b);
+                const uint32_t bhi = smem_u32(Bhi), blo = smem_u32(Blo);
+                uint32_t accumulate = 0;
+#pragma unroll 1
+                for (int pass = 0; pass < 3; ++pass) {   // lo*hi, hi*lo, hi*hi: small terms first
+                    const uint32_t a_base = (pass == 0) ? TM_AHI + D : TM_AHI;
+                    const uint32_t b_base = (pass == 1) ? blo : bhi;
+#pragma unroll 1
+                    for (int ks = 0; ks < D / 8; ++ks) {
+                        const uint32_t b_addr = b_base + (uint32_t)(ks >> 2) * (uint32_t)(D * 128) + (uint32_t)(ks & 3) * 32u;
+                        tc_mma(d_tmem, a_base + 8u * (uint32_t)ks, tc_b_desc(b_addr), Cfg::IDESC, accumulate);
+                        accumulate = 1;
+                    }
+                }
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                 bar(BAR_MMA0 + b))
+                             : "memory");
+            }
+            __syncwarp();
             TC_TRACE(1);
         }
-        TC_TRACE_PRINT("epilogue");
+        TC_TRACE_PRINT("mma");
     }
 
     // ---- teardown: everyone is done with tensor memory before it is released
@@ -548,7 +665,7 @@ int tc_launch(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const int32_t* rp, 
     int64_t blocks = num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count;
     if (blocks < 1) blocks = 1;
     kern<<<(unsigned)blocks, TC_THREADS, SMEM, st>>>(n_rows, num_tiles, rp, ci, val, H, W, X, x_index, out,
-                                                               ctx->dstatus_dev);
+                                                     ctx->dstatus_dev);
     S2V_CHECK_LAUNCH(ctx, "s2v_level_tc_kernel");
     return S2V_OK;
 }
