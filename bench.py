@@ -244,8 +244,8 @@ def level_cfg2(ctx, torch, peak_gbs, peak_kind):
             "peak_kind": peak_kind, "bytes_gather_model": gather, "bytes_compulsory_model": comp,
             "edges_per_sec": p.nnz / (mean_ms * 1e-3),
             # dram__bytes_read + dram__bytes_write of one launch on the half-size problem
-            # (the committed ncu summary of the mma.sync level kernel: 696.27 MB + 118.74 MB), times two
-            "traffic": 2 * (696272384 + 118737152), "traffic_note": "ncu capture at n=524,288, scaled x2",
+            # (the committed ncu summary of the tcgen05 level kernel: 806.40 MB + 119.01 MB), times two
+            "traffic": 2 * (806403584 + 119012864), "traffic_note": "ncu capture at n=524,288, scaled x2",
             "launches": iters,
             "l2_note": "H (268 MB) + X + out exceed the 126 MB L2"}
 
@@ -391,7 +391,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                          "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs, "peak_kind": peak_kind,
                          # dram__bytes_read + dram__bytes_write of one launch on this very input
                          # (the committed ncu summary of the tcgen05 level kernel); only known for the default workload
-                         "traffic": (259829760 + 202716416) if args.workload == "molecules" else None,
+                         "traffic": (259835136 + 204370432) if args.workload == "molecules" else None,
                          "ms_per_launch": level_ms, "launches": len(level_events), "bytes_per_launch": comp,
                          "model": "compulsory (each H row once) + CSR + tags + out + W",
                          "achieved_with_dense_X_model": survey / (level_ms * 1e-3) / 1e9},
