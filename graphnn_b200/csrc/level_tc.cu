@@ -287,17 +287,29 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             const int64_t mr = ((int64_t)blockIdx.x + (int64_t)it * gridDim.x) * TC_TILE + 32 * q + lane;
             return (XMODE == 2 && it < my_tiles && mr < n_rows) ? tc_ld_early(x_index + mr) : 0;
         };
+        constexpr int G = 32 / LPR;        // lane groups per warp (1 at d = 128, 2 at d = 64)
+        constexpr int WSZ = IDX_CAP / G;   // index window per lane group: 64 entries
+        static_assert(WSZ == 64, "one 64-bit row-end mask per window");
+        // Column indices of segment k (64 non-zeros per lane group) of a warp-tile whose row offsets sit in
+        // lanes 0..8 as `rel` (relative to `base_abs`): entry w of the buffer belongs to group w / 64.
+        // (r_mid, r_end: the offsets of rows RPG and 8, i.e. where group 0 and the last group end.)
+        auto window_index = [&](int jj, int r_mid, int r_end, int32_t base_abs, int k) -> int {
+            const int w = lane + 32 * jj;
+            const int g = w / WSZ, p_ = w % WSZ;
+            const int gs_ = (g == 0) ? 0 : r_mid, ge_ = (g == G - 1) ? r_end : r_mid;
+            const int e = gs_ + WSZ * k + p_;
+            return e < ge_ ? tc_ld_early(col_idx + base_abs + e) : 0;
+        };
         int32_t rp_next = load_rp(0);      // row offsets of the tile whose indices are fetched next
         int32_t rp_next2 = load_rp(1);
         int32_t base = 0;
-        int nnz = 0;
         {   // tile 0: fill buffer 0 directly
             base = __shfl_sync(0xffffffffu, rp_next, 0);
             const int rel = rp_next - base;
-            nnz = __shfl_sync(0xffffffffu, rel, TC_ROWS_PER_GW);
             if (lane <= TC_ROWS_PER_GW) idx_base[IDX_CAP + lane] = rel;
-            if (nnz <= IDX_CAP)
-                for (int t = lane; t < nnz; t += 32) idx_base[t] = col_idx[base + t];
+#pragma unroll
+            for (int jj = 0; jj < IPL; ++jj)
+                idx_base[lane + 32 * jj] = window_index(jj, __shfl_sync(0xffffffffu, rel, RPG), __shfl_sync(0xffffffffu, rel, TC_ROWS_PER_GW), base, 0);
             rp_next = rp_next2;
         }
         int xi_prev = 0;                   // X row index of my row in tile it-1 (the tile whose epilogue runs in iteration it)
@@ -311,65 +323,15 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                 // -------------------------------- gather --------------------------------
                 int* idx_s = idx_base + (it & 1) * IDX_BUF;
                 const int* rp_s = idx_s + IDX_CAP;
-                const bool fits = nnz <= IDX_CAP;   // warp-uniform; almost always true
-                const float* vp = HAS_VAL ? val + base : nullptr;
-#define TC_IDX(t) (fits ? idx_s[(t)] : __ldg(col_idx + base + (t)))
-                // prefetch (registers): offsets of tile it+2, indices of tile it+1
+                // prefetch (registers): offsets of tile it+2, first index window of tile it+1
                 rp_next2 = load_rp(it + 2);
                 const int32_t base1 = __shfl_sync(0xffffffffu, rp_next, 0);
                 const int rel1 = rp_next - base1;
-                const int nnz1 = __shfl_sync(0xffffffffu, rel1, TC_ROWS_PER_GW);
                 int idx_pref[IPL];
+                const int r1_mid = __shfl_sync(0xffffffffu, rel1, RPG), r1_end = __shfl_sync(0xffffffffu, rel1, TC_ROWS_PER_GW);
 #pragma unroll
-                for (int jj = 0; jj < IPL; ++jj)
-                    idx_pref[jj] = (nnz1 <= IDX_CAP && lane + 32 * jj < nnz1) ? tc_ld_early(col_idx + base1 + lane + 32 * jj) : 0;
-                // Flat stream over the non-zeros of my lane group's RPG rows, software-pipelined: the
-                // loads of chunk k+1 are in flight while chunk k is summed.  My slab of the staging
-                // tile is free: the quarter finished reading it before my last epilogue used it.
-                int row = sub * RPG;
-                const int row_stop = row + RPG;
-                int t = rp_s[row];
-                const int ee = rp_s[row_stop];
-                int row_end = rp_s[row + 1];
-                float* srow = slab + (size_t)row * STAGE_STRIDE + sl * 4;
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                float4 va[TC_U], vb[TC_U];
-// HSRC_TABLE: the gather source is not a matrix but ReLU(table[x_index[col], :]) -- the first level of
-// the classifier with one-hot inputs, where H0 = ReLU(W_in[tag]) need not be materialised
-#define TC_LOAD(v, t0)                                                                             \
-    _Pragma("unroll") for (int u = 0; u < TC_U; ++u)                                               \
-        if ((t0) + u < ee) {                                                                       \
-            if (HSRC_TABLE) {                                                                      \
-                const int tg = __ldg(x_index + TC_IDX((t0) + u));                                  \
-                const float4 w = ld_nc_f4(X4 + (int64_t)tg * LPR + sl);                            \
-                v[u] = make_float4(relu_ref(w.x), relu_ref(w.y), relu_ref(w.z), relu_ref(w.w));    \
-            } else {                                                                               \
-                v[u] = ld_nc_f4(H4 + (int64_t)TC_IDX((t0) + u) * LPR + sl);                    \
-            }                                                                                      \
-        }
-#define TC_CONSUME(v, t0)                                                                          \
-    _Pragma("unroll") for (int u = 0; u < TC_U; ++u) {                                             \
-        if ((t0) + u < ee) {                                                                       \
-            while ((t0) + u == row_end) {                                                          \
-                *reinterpret_cast<float4*>(srow) = acc;                                            \
-                acc = make_float4(0.f, 0.f, 0.f, 0.f);                                             \
-                ++row;                                                                             \
-                srow += STAGE_STRIDE;                                                              \
-                row_end = rp_s[row + 1];                                                           \
-            }                                                                                      \
-            if (HAS_VAL) {                                                                         \
-                const float a = vp[(t0) + u];                                                      \
-                acc.x = fmaf(a, v[u].x, acc.x); acc.y = fmaf(a, v[u].y, acc.y);                    \
-                acc.z = fmaf(a, v[u].z, acc.z); acc.w = fmaf(a, v[u].w, acc.w);                    \
-            } else {                                                                               \
-                acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;                \
-            }                                                                                      \
-        }                                                                                          \
-    }
-                // Fast path (warp-uniform test): the tile's indices are in shared memory and every lane
-                // group has at most 64 non-zeros, so that "element p ends a row" fits a 64-bit mask.
-                // The masks are built by the warp together: lane r+1 speaks for row r.
-                constexpr int G = 32 / LPR;   // lane groups per warp
+                for (int jj = 0; jj < IPL; ++jj) idx_pref[jj] = window_index(jj, r1_mid, r1_end, base1, 0);
+                // Row structure of my warp-tile, worked out by the warp together: lane r+1 speaks for row r.
                 const int rel = lane <= TC_ROWS_PER_GW ? rp_s[lane] : 0;
                 const int relp = __shfl_up_sync(0xffffffffu, rel, 1);
                 const int rr_ = lane - 1;                                 // my row as a speaker
@@ -379,53 +341,70 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                 const bool ne_row = isrow && rel > relp;
                 const int pos = rel - 1 - gbeg;                           // my row's last non-zero, counted within its group
                 const uint32_t ne_bits = __ballot_sync(0xffffffffu, ne_row) >> 1;        // bit r: row r is not empty
-                const bool big = __ballot_sync(0xffffffffu, isrow && pos >= 64) != 0;    // some group has more than 64 non-zeros
-                const bool fast = fits && !big;
-                if (fast) {
-                    // Branch-free form of the stream.  Per lane group: endmask bit p = 1 if the p-th
-                    // non-zero of the group is the last of its row; nxtmap holds, 4 bits per row, the next
-                    // non-empty row; empty rows are zero-filled up front.  Sums run in CSR order.
-                    const int r_lo = sub * RPG;
-                    uint32_t em_lo = 0, em_hi = 0, nxtmap = 0;
-                    const uint32_t ne_g_mine = (ne_bits >> (rg * RPG)) & ((1u << RPG) - 1u);   // speaker view: my row's group
-                    const int rin = rr_ - rg * RPG;                                          // my row within its group
-                    const uint32_t above = isrow ? (ne_g_mine >> (rin + 1)) : 0u;
-                    const uint32_t nxt_r = above ? (uint32_t)(rin + 1 + __ffs(above) - 1) : 15u;
+                const int r_lo = sub * RPG;
+                const int r_mid = __shfl_sync(0xffffffffu, rel, RPG), r_end = __shfl_sync(0xffffffffu, rel, TC_ROWS_PER_GW);
+                const int gs = (sub == 0) ? 0 : r_mid;                    // my group's non-zeros: [gs, gs + cnt)
+                const int cnt = ((sub == G - 1) ? r_end : r_mid) - gs;
+                const int cmax = (G == 1) ? r_end : max(r_mid, r_end - r_mid);
+                const int nseg = (cmax + WSZ - 1) / WSZ;                  // 64-non-zero segments (warp-uniform)
+                // nxtmap: 4 bits per row, the next non-empty row of the group (15: none)
+                uint32_t nxtmap = 0;
+                {
+                    const uint32_t ne_g_sp = (ne_bits >> (rg * RPG)) & ((1u << RPG) - 1u);   // speaker view: my row's group
+                    const int rin = rr_ - rg * RPG;                                        // my row within its group
+                    const uint32_t above = isrow ? (ne_g_sp >> (rin + 1)) : 0u;
+                    const uint32_t nxt_r = above ? (uint32_t)(rin + __ffs(above)) : 15u;
 #pragma unroll
                     for (int gg = 0; gg < G; ++gg) {
-                        const bool mine = ne_row && rg == gg;
-                        const uint32_t lo = __reduce_or_sync(0xffffffffu, (mine && pos < 32) ? (1u << pos) : 0u);
-                        const uint32_t hi = __reduce_or_sync(0xffffffffu, (mine && pos >= 32) ? (1u << (pos - 32)) : 0u);
                         const uint32_t nm = __reduce_or_sync(0xffffffffu, (isrow && rg == gg) ? (nxt_r << (4 * rin)) : 0u);
-                        if (gg == sub) { em_lo = lo; em_hi = hi; nxtmap = nm; }
+                        if (gg == sub) nxtmap = nm;
                     }
-                    unsigned long long em = ((unsigned long long)em_hi << 32) | em_lo;
-                    const uint32_t ne_g = (ne_bits >> r_lo) & ((1u << RPG) - 1u);            // worker view: my lane group
+                }
+                const uint32_t ne_g = (ne_bits >> r_lo) & ((1u << RPG) - 1u);              // worker view: my lane group
 #pragma unroll
-                    for (int r = 0; r < RPG; ++r)
-                        if (!((ne_g >> r) & 1u))
-                            *reinterpret_cast<float4*>(slab + (size_t)(r_lo + r) * STAGE_STRIDE + sl * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-                    const int nxt = ne_g ? (__ffs(ne_g) - 1) : 15;
-                    int frow = nxt;   // first non-empty row of my group (15: none)
-                    const bool any = t < ee;                  // my group has non-zeros at all
-                    const int cz = any ? idx_s[t] : 0;        // a safe column for the slots past the end: the group's first neighbour
-                    float wa[TC_U], wb[TC_U];
-#define TC_LOADF(v, wt, t0)                                                                         \
+                for (int r = 0; r < RPG; ++r)   // empty rows are zero-filled up front
+                    if (!((ne_g >> r) & 1u))
+                        *reinterpret_cast<float4*>(slab + (size_t)(r_lo + r) * STAGE_STRIDE + sl * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+                int frow = ne_g ? (__ffs(ne_g) - 1) : 15;   // the row being summed (within my group)
+                const int* win = idx_s + WSZ * sub;          // my group's index window
+                const float* vp = HAS_VAL ? val + base + gs : nullptr;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 va[TC_U], vb[TC_U];
+                float wa[TC_U], wb[TC_U];
+                auto publish_next = [&]() {
+                    // Pull the neighbour rows of the NEXT tile's first window into L2 now, a whole tile ahead of
+                    // their use (a prefetch holds no register), and publish that window in the other buffer.
+                    int* nb = idx_base + ((it + 1) & 1) * IDX_BUF;
+#pragma unroll
+                    for (int jj = 0; jj < IPL; ++jj) {
+                        if (!HSRC_TABLE && idx_pref[jj] != 0) {   // (0 also marks an unused slot; row 0 needs no prefetch)
+                            const char* rowp = reinterpret_cast<const char*>(H4 + (int64_t)idx_pref[jj] * LPR);
+#pragma unroll
+                            for (int l = 0; l < D * 4 / 128; ++l) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + 128 * l));
+                        }
+                        nb[lane + 32 * jj] = idx_pref[jj];
+                    }
+                    if (lane <= TC_ROWS_PER_GW) nb[IDX_CAP + lane] = rel1;
+                };
+// HSRC_TABLE: the gather source is not a matrix but ReLU(table[x_index[col], :]) -- the first level of
+// the classifier with one-hot inputs, where H0 = ReLU(W_in[tag]) need not be materialised.
+// Slots past the segment's end load the segment's first neighbour again (a valid row, an L1 hit) and carry
+// no end bit: only the last segment has such slots, after the group's last row was stored, and what they
+// add to acc is never stored.
+#define TC_LOADF(v, wt, p0)                                                                        \
     _Pragma("unroll") for (int u = 0; u < TC_U; ++u) {                                             \
-        const bool pv = (t0) + u < ee;                                                             \
-        const int c = pv ? idx_s[(t0) + u] : cz;                                                   \
-        if (HAS_VAL) wt[u] = pv ? __ldg(vp + (t0) + u) : 0.f;                                       \
+        const bool pv = (p0) + u < seg_n;                                                          \
+        const int c = pv ? win[(p0) + u] : cz;                                                     \
+        if (HAS_VAL) wt[u] = pv ? __ldg(vp + WSZ * k + (p0) + u) : 0.f;                             \
         if (HSRC_TABLE) {                                                                          \
             const int tg = __ldg(x_index + c);                                                     \
             const float4 xw = ld_nc_f4(X4 + (int64_t)tg * LPR + sl);                               \
             v[u] = make_float4(relu_ref(xw.x), relu_ref(xw.y), relu_ref(xw.z), relu_ref(xw.w));    \
         } else {                                                                                   \
-            v[u] = ld_nc_f4(H4 + (int64_t)c * LPR + sl);                                       \
+            v[u] = ld_nc_f4(H4 + (int64_t)c * LPR + sl);                                           \
         }                                                                                          \
     }
-// Slots past the group's end load the group's first neighbour again (a valid row, an L1 hit) and carry no
-// end bit: whatever they add to acc comes after the group's last row was stored and is never stored itself.
-#define TC_CONSF(v, wt)                                                                             \
+#define TC_CONSF(v, wt, p0)                                                                        \
     {                                                                                              \
         const uint32_t m4 = (uint32_t)em & 15u;                                                    \
         em >>= 4;                                                                                  \
@@ -443,79 +422,49 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             frow = last ? (int)((nxtmap >> (4 * frow)) & 15u) : frow;                              \
         }                                                                                          \
     }
-                    if (any) {
-                        TC_LOADF(va, wa, t)
-                        TC_LOADF(vb, wb, t + TC_U)
-                    }
-                    TC_TRACE(0);
-                    if (!HSRC_TABLE) {   // next tile's neighbour rows -> L2, a whole tile ahead of their use
+                if (nseg == 0) publish_next();
+#pragma unroll 1
+                for (int k = 0; k < nseg; ++k) {
+                    if (k > 0) {   // later windows are fetched on demand (rows this long amortise the latency)
+                        __syncwarp();
 #pragma unroll
-                        for (int jj = 0; jj < IPL; ++jj)
-                            if (nnz1 <= IDX_CAP && lane + 32 * jj < nnz1) {
-                                const char* rowp = reinterpret_cast<const char*>(H4 + (int64_t)idx_pref[jj] * LPR);
+                        for (int jj = 0; jj < IPL; ++jj) idx_s[lane + 32 * jj] = window_index(jj, r_mid, r_end, base, k);
+                        __syncwarp();
+                    }
+                    // "the p-th non-zero of this segment is the last of its row", per lane group
+                    uint32_t em_lo = 0, em_hi = 0;
 #pragma unroll
-                                for (int l = 0; l < D * 4 / 128; ++l) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + 128 * l));
-                            }
+                    for (int gg = 0; gg < G; ++gg) {
+                        const bool here = ne_row && rg == gg && (pos >> 6) == k;
+                        const uint32_t lo = __reduce_or_sync(0xffffffffu, (here && (pos & 63) < 32) ? (1u << (pos & 31)) : 0u);
+                        const uint32_t hi = __reduce_or_sync(0xffffffffu, (here && (pos & 63) >= 32) ? (1u << (pos & 31)) : 0u);
+                        if (gg == sub) { em_lo = lo; em_hi = hi; }
                     }
-                    {   // publish the prefetched slice of tile it+1 in the other buffer (last read for tile it-1)
-                        int* nb = idx_base + ((it + 1) & 1) * IDX_BUF;
-                        if (lane <= TC_ROWS_PER_GW) nb[IDX_CAP + lane] = rel1;
-#pragma unroll
-                        for (int jj = 0; jj < IPL; ++jj)
-                            if (lane + 32 * jj < nnz1 && nnz1 <= IDX_CAP) nb[lane + 32 * jj] = idx_pref[jj];
+                    unsigned long long em = ((unsigned long long)em_hi << 32) | em_lo;
+                    const int seg_n = min(WSZ, cnt - WSZ * k);   // my group's non-zeros in this segment (may be <= 0)
+                    if (seg_n > 0) {
+                        const int cz = win[0];
+                        int p = 0;
+                        TC_LOADF(va, wa, 0)
+                        TC_LOADF(vb, wb, TC_U)
+                        if (k == 0) publish_next();
+                        while (true) {
+                            TC_CONSF(va, wa, p)
+                            p += TC_U;
+                            if (p >= seg_n) break;
+                            TC_LOADF(va, wa, p + TC_U)
+                            TC_CONSF(vb, wb, p)
+                            p += TC_U;
+                            if (p >= seg_n) break;
+                            TC_LOADF(vb, wb, p + TC_U)
+                        }
+                    } else if (k == 0) {
+                        publish_next();
                     }
-                    TC_TRACE(1);
-                    while (t < ee) {
-                        TC_CONSF(va, wa)
-                        t += TC_U;
-                        if (t >= ee) break;
-                        TC_LOADF(va, wa, t + TC_U)
-                        TC_CONSF(vb, wb)
-                        t += TC_U;
-                        if (t >= ee) break;
-                        TC_LOADF(vb, wb, t + TC_U)
-                    }
+                }
 #undef TC_LOADF
 #undef TC_CONSF
-                } else {
-                TC_LOAD(va, t)
-                if (!HSRC_TABLE) {
-#pragma unroll
-                    for (int jj = 0; jj < IPL; ++jj)
-                        if (nnz1 <= IDX_CAP && lane + 32 * jj < nnz1) {
-                            const char* rowp = reinterpret_cast<const char*>(H4 + (int64_t)idx_pref[jj] * LPR);
-#pragma unroll
-                            for (int l = 0; l < D * 4 / 128; ++l) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + 128 * l));
-                        }
-                }
-                {
-                    int* nb = idx_base + ((it + 1) & 1) * IDX_BUF;
-                    if (lane <= TC_ROWS_PER_GW) nb[IDX_CAP + lane] = rel1;
-#pragma unroll
-                    for (int jj = 0; jj < IPL; ++jj)
-                        if (lane + 32 * jj < nnz1 && nnz1 <= IDX_CAP) nb[lane + 32 * jj] = idx_pref[jj];
-                }
-                while (t < ee) {
-                    TC_LOAD(vb, t + TC_U)
-                    TC_CONSUME(va, t)
-                    t += TC_U;
-                    if (t >= ee) break;
-                    TC_LOAD(va, t + TC_U)
-                    TC_CONSUME(vb, t)
-                    t += TC_U;
-                }
-                while (row < row_stop) {
-                    *reinterpret_cast<float4*>(srow) = acc;
-                    acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    ++row;
-                    srow += STAGE_STRIDE;
-                }
-                }
-#undef TC_LOAD
-#undef TC_CONSUME
-#undef TC_IDX
                 base = base1;
-                nnz = nnz1;
                 rp_next = rp_next2;
                 __syncwarp();
                 if (lane == 0) tc_mbar_arrive(bar(BAR_FULL0 + q));
