@@ -1,7 +1,7 @@
 """GPU parity of the tcgen05 form of the fused level (d = 64 and d = 128) against the CPU
 oracle.  The library picks that kernel by batch size; here a context created with
 S2V_LEVEL_TC=2 forces it on every shape, so ragged tiles, empty rows, rows longer than the
-per-warp index buffer, weighted edges and the table-lookup forms are all covered."""
+index window, weighted edges and the table-lookup forms are all covered."""
 import os
 
 import numpy as np
@@ -74,13 +74,16 @@ def test_tc_level_without_x_and_with_weights(tc_ctx, oracle_lib, d):
 
 @pytest.mark.parametrize("d", [64, 128])
 def test_tc_level_heavy_rows_and_rectangular(tc_ctx, oracle_lib, d):
-    """Rows with more non-zeros than a gather warp's index buffer (global index loads), empty
-    rows between them, and n_src != n_rows."""
+    """Rows longer than one 64-entry index window (and exactly at its edge), empty rows between
+    them, and n_src != n_rows."""
     rng = np.random.default_rng(7)
     n_rows, n_src = 300, 5000
     deg = np.zeros(n_rows, np.int64)
     deg[3] = 1500
     deg[4] = 129
+    deg[5] = 64
+    deg[6] = 65
+    deg[7] = 63
     deg[16] = 300
     deg[17] = 257
     deg[40:60] = rng.integers(0, 30, 20)
