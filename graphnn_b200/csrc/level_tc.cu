@@ -309,7 +309,10 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             if (lane <= TC_ROWS_PER_GW) idx_base[IDX_CAP + lane] = rel;
 #pragma unroll
             for (int jj = 0; jj < IPL; ++jj)
-                idx_base[lane + 32 * jj] = window_index(jj, __shfl_sync(0xffffffffu, rel, RPG), __shfl_sync(0xffffffffu, rel, TC_ROWS_PER_GW), base, 0);
+            {
+                const int c_ = window_index(jj, __shfl_sync(0xffffffffu, rel, RPG), __shfl_sync(0xffffffffu, rel, TC_ROWS_PER_GW), base, 0);
+                idx_base[lane + 32 * jj] = HSRC_TABLE ? __ldg(x_index + c_) : c_;
+            }
             rp_next = rp_next2;
         }
         int xi_prev = 0;                   // X row index of my row in tile it-1 (the tile whose epilogue runs in iteration it)
@@ -371,6 +374,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
                 float4 va[TC_U], vb[TC_U];
                 float wa[TC_U], wb[TC_U];
+                int tag_pref[IPL];
                 auto publish_next = [&]() {
                     // Pull the neighbour rows of the NEXT tile's first window into L2 now, a whole tile ahead of
                     // their use (a prefetch holds no register), and publish that window in the other buffer.
@@ -382,7 +386,10 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
 #pragma unroll
                             for (int l = 0; l < D * 4 / 128; ++l) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + 128 * l));
                         }
-                        nb[lane + 32 * jj] = idx_pref[jj];
+                        // table form: the window holds the neighbour's table row, looked up here, a tile ahead
+                        // (issued now, stored after the stream: see tag_pref below)
+                        if (HSRC_TABLE) tag_pref[jj] = __ldg(x_index + idx_pref[jj]);
+                        else nb[lane + 32 * jj] = idx_pref[jj];
                     }
                     if (lane <= TC_ROWS_PER_GW) nb[IDX_CAP + lane] = rel1;
                 };
@@ -396,9 +403,8 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
         const bool pv = (p0) + u < seg_n;                                                          \
         const int c = pv ? win[(p0) + u] : cz;                                                     \
         if (HAS_VAL) wt[u] = pv ? __ldg(vp + WSZ * k + (p0) + u) : 0.f;                             \
-        if (HSRC_TABLE) {                                                                          \
-            const int tg = __ldg(x_index + c);                                                     \
-            const float4 xw = ld_nc_f4(X4 + (int64_t)tg * LPR + sl);                               \
+        if (HSRC_TABLE) {   /* c is already the table row */                                       \
+            const float4 xw = ld_nc_f4(X4 + (int64_t)c * LPR + sl);                                \
             v[u] = make_float4(relu_ref(xw.x), relu_ref(xw.y), relu_ref(xw.z), relu_ref(xw.w));    \
         } else {                                                                                   \
             v[u] = ld_nc_f4(H4 + (int64_t)c * LPR + sl);                                           \
@@ -428,7 +434,10 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                     if (k > 0) {   // later windows are fetched on demand (rows this long amortise the latency)
                         __syncwarp();
 #pragma unroll
-                        for (int jj = 0; jj < IPL; ++jj) idx_s[lane + 32 * jj] = window_index(jj, r_mid, r_end, base, k);
+                        for (int jj = 0; jj < IPL; ++jj) {
+                            const int c_ = window_index(jj, r_mid, r_end, base, k);
+                            idx_s[lane + 32 * jj] = HSRC_TABLE ? __ldg(x_index + c_) : c_;
+                        }
                         __syncwarp();
                     }
                     // "the p-th non-zero of this segment is the last of its row", per lane group
@@ -464,6 +473,11 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                 }
 #undef TC_LOADF
 #undef TC_CONSF
+                if (HSRC_TABLE) {
+                    int* nb = idx_base + ((it + 1) & 1) * IDX_BUF;
+#pragma unroll
+                    for (int jj = 0; jj < IPL; ++jj) nb[lane + 32 * jj] = tag_pref[jj];
+                }
                 base = base1;
                 rp_next = rp_next2;
                 __syncwarp();
