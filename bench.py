@@ -251,6 +251,10 @@ def level_cfg2(ctx, torch, peak_gbs, peak_kind):
 
 
 def run_ours(args, rank: int, world: int, local_rank: int):
+    # torchrun pins OMP_NUM_THREADS to 1; the host CSR builder (timed in e2e.from_edge_list) is
+    # OpenMP-parallel, so give every rank its share of the host cores before the library loads
+    if world > 1:
+        os.environ["OMP_NUM_THREADS"] = str(max(1, (os.cpu_count() or 1) // world))
     import torch
     import torch.distributed as dist
     from graphnn_b200 import capi, engine
