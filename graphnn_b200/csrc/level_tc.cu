@@ -13,8 +13,8 @@
 // one MMA-issue warp, connected by mbarriers:
 //
 //   worker w (quarter q = w % 4 of the tensor-memory lanes, slot j = w / 4), per tile:
-//     gather   : rows 32q + 8j .. +7 of the tile: the CSR slice comes through shared memory
-//                (indices prefetched a tile ahead, their rows prefetched into L2), neighbour
+//     gather   : rows 32q + 8j .. +7 of the tile: the CSR slice comes through 64-entry index windows in
+//                shared memory (first window prefetched a tile ahead, its rows prefetched into L2), neighbour
 //                rows are summed in CSR order as one flat software-pipelined stream per group
 //                of d/4 lanes (8 loads in flight per lane, no branch per non-zero: row ends come from a
 //                bit mask built with warp votes) into a fp32 staging tile [128 x d];
@@ -49,7 +49,7 @@ constexpr uint32_t TC_SUSPEND_NS = 10000;    // a waiting thread sleeps in the b
 // Per-width configuration and shared memory map (offsets from a 1024-byte aligned base).
 template <int D>
 struct TcCfg {
-    static constexpr int IDX_CAP = (D == 64) ? 128 : 64;   // column indices of one worker's 8 rows kept in shared memory
+    static constexpr int IDX_CAP = (D == 64) ? 128 : 64;   // index-window entries per worker: 64 per lane group
     static constexpr int STAGE_STRIDE = D + 4;         // floats; an odd number of float4 per row: thread-per-row float4 reads are conflict-free
     static constexpr size_t OFF_BHI = 0;
     static constexpr size_t OFF_BLO = OFF_BHI + sizeof(float) * D * D;
