@@ -130,3 +130,32 @@ def test_tc_whole_classifier_d64(oracle_lib, monkeypatch):
     assert_close(embed.cpu().numpy(), o["levels"][-1], "embeddings")
     assert_close(logits.cpu().numpy(), o["logits"], "logits", scale=max(1.0, float(np.abs(o["logits"]).max())))
     assert_close(probs.cpu().numpy(), o["probs"], "probs")
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_tc_first_level_with_long_rows(tc_ctx, d):
+    """The table form (gather source = ReLU(W_in[tag[col]])) on rows that span several index windows:
+    the windows then hold table rows looked up on demand."""
+    rng = np.random.default_rng(11)
+    n, n_tags = 400, 9
+    deg = rng.integers(0, 12, n)
+    deg[7], deg[8], deg[200], deg[399] = 700, 64, 129, 65
+    row_ptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)
+    col = rng.integers(0, n, int(deg.sum())).astype(np.int32)
+    tags = rng.integers(0, n_tags, n).astype(np.int32)
+    table = (rng.standard_normal((n_tags, d)) * 0.3).astype(np.float32)
+    W = (rng.standard_normal((d, d)) * 0.1).astype(np.float32)
+    fused = torch.full((n, d), float("nan"), device="cuda")
+    tc_ctx.level_first(dev(row_ptr), dev(col), None, dev(W), dev(table), dev(tags), fused)
+    tc_ctx.synchronize()
+    import scipy.sparse as sp
+    h0 = np.maximum(table[tags].astype(np.float64), 0.0)
+    A = sp.csr_matrix((np.ones(len(col)), col, row_ptr), shape=(n, n))
+    z = (A @ h0) @ W.astype(np.float64) + table[tags]
+    got, want = fused.cpu().numpy(), np.where(z < 0, 0.0, z).astype(np.float32)
+    long_rows = deg > 100
+    assert_close(got[~long_rows], want[~long_rows], f"first level, rows up to 65 non-zeros, d={d}")
+    # the 700- and 129-term rows cancel heavily in the product with W: there the absolute bar scales with
+    # the size of the terms that cancel (the fp32 reference itself is no closer to this float64 result)
+    scale = float(((A @ h0) @ np.abs(W).astype(np.float64))[long_rows].max())
+    assert_close(got[long_rows], want[long_rows], f"first level, long rows, d={d}", scale=scale)
