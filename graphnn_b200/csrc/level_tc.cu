@@ -230,21 +230,35 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
     }
     // B[n][k] = W[k][n]; element (n, k) lives at  kb*(D*128) + n*128 + ((kk/4) ^ (n&7))*16 + (kk%4)*4,
     // kb = k/32, kk = k%32.  Each task converts 4 consecutive k of one n: one 16-byte store per matrix.
-    for (int e = threadIdx.x; e < D * D / 4; e += TC_THREADS) {
-        const int n = e % D, kq = e / D;   // k = 4*kq .. 4*kq+3
-        float w[4];
+    // All loads of a thread's tasks are issued before the first conversion (one memory latency, not one per task).
+    {
+        constexpr int NTASK = D * D / 4;
+        constexpr int PER = (NTASK + TC_THREADS - 1) / TC_THREADS;
+        float wv[PER][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) w[j] = __ldg(W + (int64_t)(4 * kq + j) * D + n);
-        uint32_t hi[4], lo[4];
+        for (int t = 0; t < PER; ++t) {
+            const int e = threadIdx.x + t * TC_THREADS;
+            const int n = e % D, kq = e / D;   // k = 4*kq .. 4*kq+3
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            hi[j] = tf32_rn(w[j]);
-            lo[j] = tf32_rn(w[j] - __uint_as_float(hi[j]));
+            for (int jj = 0; jj < 4; ++jj) wv[t][jj] = (e < NTASK) ? __ldg(W + (int64_t)(4 * kq + jj) * D + n) : 0.f;
         }
-        const int kb = kq >> 3, chunk = kq & 7;
-        const size_t off = (size_t)kb * (D * 128) + (size_t)n * 128 + (size_t)((chunk ^ (n & 7)) * 16);
-        *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(Bhi) + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(Blo) + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+#pragma unroll
+        for (int t = 0; t < PER; ++t) {
+            const int e = threadIdx.x + t * TC_THREADS;
+            if (e < NTASK) {
+                const int n = e % D, kq = e / D;
+                uint32_t hi[4], lo[4];
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    hi[jj] = tf32_rn(wv[t][jj]);
+                    lo[jj] = tf32_rn(wv[t][jj] - __uint_as_float(hi[jj]));
+                }
+                const int kb = kq >> 3, chunk = kq & 7;
+                const size_t off = (size_t)kb * (D * 128) + (size_t)n * 128 + (size_t)((chunk ^ (n & 7)) * 16);
+                *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(Bhi) + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(Blo) + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            }
+        }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

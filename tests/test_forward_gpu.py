@@ -107,6 +107,27 @@ def test_pooling_and_readout_separately(gpu_ctx, oracle_lib):
         assert np.array_equal(pred.cpu().numpy(), logits.cpu().numpy().argmax(1))
 
 
+@pytest.mark.parametrize("G,d,hidden,C", [(2048, 128, 256, 2), (5000, 64, 128, 3), (2049, 128, 256, 2)])
+def test_readout_large_batch(gpu_ctx, G, d, hidden, C):
+    """Batches of 2,048 graphs and more take the form of the readout that keeps W1 in shared memory;
+    the last tile of 32 graphs is ragged in two of the cases."""
+    rng = np.random.default_rng(G)
+    Y = rng.standard_normal((G, d), dtype=np.float32) * 3.0
+    W1 = rng.standard_normal((d, hidden), dtype=np.float32) * 0.1
+    W2 = rng.standard_normal((hidden, C), dtype=np.float32) * 0.1
+    logits = torch.full((G, C), float("nan"), device="cuda")
+    probs = torch.empty((G, C), device="cuda")
+    pred = torch.empty(G, dtype=torch.int32, device="cuda")
+    gpu_ctx.readout(torch.from_numpy(Y).cuda(), torch.from_numpy(W1).cuda(), torch.from_numpy(W2).cuda(), logits, probs, pred)
+    gpu_ctx.synchronize()
+    hid = np.maximum(Y.astype(np.float64) @ W1.astype(np.float64), 0)
+    lg = hid @ W2.astype(np.float64)
+    assert_close(logits.cpu().numpy(), lg, "readout logits", scale=8)
+    e = np.exp(lg - lg.max(1, keepdims=True))
+    assert_close(probs.cpu().numpy(), e / e.sum(1, keepdims=True), "readout probs", scale=8)
+    assert np.array_equal(pred.cpu().numpy(), logits.cpu().numpy().argmax(1))
+
+
 def test_full_size_properties():
     """At the benchmark's full molecule size the oracle is too slow to run per test;
     check size-independent properties instead: a permutation of the graphs permutes
