@@ -178,78 +178,19 @@ __global__ void __launch_bounds__(256) readout_kernel(int64_t G, int d, int hidd
 // a CTA takes 32 graphs; a thread owns 4 consecutive hidden units x 8 graphs, walks k in steps of
 // 4 with one 16-byte load of W1 per k (L1-resident after the first tile: W1 is at most 128 KB)
 // and one 16-byte shared load of Y per graph, 128 FMAs per 12 loads; k ascending per output.
-// W1_SMEM: one persistent CTA per SM keeps all of W1 in shared memory (bulk-async copies completing on an
-// mbarrier, bounded wait), so the inner loop reads no global memory; used for large batches when W1 fits.
 constexpr int TG4 = 32;
-constexpr int READOUT_WAIT_LIMIT = 1 << 22;
-template <bool W1_SMEM>
 __global__ void __launch_bounds__(256) readout_v4_kernel(int64_t G, int d, int hidden, int C, const float* __restrict__ Y,
                                                          const float* __restrict__ W1, const float* __restrict__ W2,
                                                          float* __restrict__ logits, float* __restrict__ probs,
-                                                         int32_t* __restrict__ pred, s2v_device_status* status)
+                                                         int32_t* __restrict__ pred)
 {
-    extern __shared__ __align__(128) float sm4[];
+    extern __shared__ __align__(16) float sm4[];
     const int ys = d + 4, hs = hidden + 4;
-    float* W1s = sm4;                                    // [d][hidden] (W1_SMEM only)
-    float* Ys = sm4 + (W1_SMEM ? (size_t)d * hidden : 0); // [TG4][d + 4]
+    float* Ys = sm4;                  // [TG4][d + 4]
     float* Hs = Ys + TG4 * ys;        // [TG4][hidden + 4]
     float* Ls = Hs + TG4 * hs;        // [TG4][C]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int d4 = d >> 2, hq = hidden >> 2;
-    if (W1_SMEM) {
-        uint64_t* mbar = reinterpret_cast<uint64_t*>(Ls + ((TG4 * C + 3) & ~3));   // 16-byte aligned, after the logits
-        const uint32_t bar = smem_u32(mbar);
-        if (threadIdx.x == 0) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(1) : "memory");
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-            const uint32_t total = (uint32_t)(sizeof(float) * (size_t)d * hidden);
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(total) : "memory");
-            constexpr uint32_t CHUNK = 8192;
-            for (uint32_t off = 0; off < total; off += CHUNK) {
-                const uint32_t n = total - off < CHUNK ? total - off : CHUNK;
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                 smem_u32(W1s) + off),
-                             "l"(reinterpret_cast<const char*>(W1) + off), "r"(n), "r"(bar)
-                             : "memory");
-            }
-        }
-        __syncthreads();   // barrier initialised before anyone polls it
-        int spins = 0;
-        bool ok = true;
-        while (true) {
-            uint32_t done;
-            asm volatile(
-                "{\n\t.reg .pred p;\n\t"
-                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                "selp.u32 %0, 1, 0, p;\n\t}"
-                : "=r"(done)
-                : "r"(bar), "r"(0)
-                : "memory");
-            if (done) break;
-            if (++spins > READOUT_WAIT_LIMIT) {   // bounded: report and leave instead of hanging the GPU
-                ok = false;
-                break;
-            }
-        }
-        if (!ok) {
-            if (threadIdx.x == 0) {
-                status->code = S2V_ERR_DEVICE_TIMEOUT;
-                status->where = 40;
-            }
-            // wait (bounded) for the copies in flight before the shared memory is released
-            int again = 0;
-            uint32_t done = 0;
-            while (!done && ++again < READOUT_WAIT_LIMIT)
-                asm volatile(
-                    "{\n\t.reg .pred p;\n\t"
-                    "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                    "selp.u32 %0, 1, 0, p;\n\t}"
-                    : "=r"(done)
-                    : "r"(bar), "r"(0)
-                    : "memory");
-            return;
-        }
-    }
     for (int64_t g0 = (int64_t)blockIdx.x * TG4; g0 < G; g0 += (int64_t)gridDim.x * TG4) {
         const int ng = (int)((G - g0) < TG4 ? (G - g0) : TG4);
         for (int e = threadIdx.x; e < TG4 * d4; e += blockDim.x) {
@@ -267,9 +208,7 @@ __global__ void __launch_bounds__(256) readout_v4_kernel(int64_t G, int d, int h
             for (int k = 0; k < d; k += 4) {
                 float4 w[4];
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk)
-                    w[kk] = W1_SMEM ? *reinterpret_cast<const float4*>(W1s + (size_t)(k + kk) * hidden + h4)
-                                    : __ldg(reinterpret_cast<const float4*>(W1 + (int64_t)(k + kk) * hidden + h4));
+                for (int kk = 0; kk < 4; ++kk) w[kk] = __ldg(reinterpret_cast<const float4*>(W1 + (int64_t)(k + kk) * hidden + h4));
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
                     const float4 y = *reinterpret_cast<const float4*>(Ys + (gb + g) * ys + k);
@@ -395,18 +334,9 @@ int s2v_readout_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int d, 
     if (!Y || !W1 || !W2 || !logits) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "readout: NULL pointer");
     const size_t smem4 = sizeof(float) * (size_t)TG4 * ((size_t)d + 4 + hidden + 4 + num_class);
     if (d % 4 == 0 && hidden % 4 == 0 && smem4 <= 96 * 1024 && s2v_aligned16(Y) && s2v_aligned16(W1)) {
-        // large batches: W1 resident in shared memory, one persistent CTA per SM
-        const size_t smem5 = smem4 + sizeof(float) * (size_t)d * hidden + 64;
-        if (num_graphs >= 2048 && smem5 <= ctx->smem_optin) {
-            S2V_CUDA_OK(ctx, cudaFuncSetAttribute(readout_v4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem5));
-            readout_v4_kernel<true><<<grid_cap(ctx, (num_graphs + TG4 - 1) / TG4, 1), 256, smem5, s2v_pick_stream(ctx, stream)>>>(
-                num_graphs, d, hidden, num_class, Y, W1, W2, logits, probs, pred, ctx->dstatus_dev);
-            S2V_CHECK_LAUNCH(ctx, "readout_v4_kernel<W1 in shared memory>");
-            return S2V_OK;
-        }
-        S2V_CUDA_OK(ctx, cudaFuncSetAttribute(readout_v4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4));
-        readout_v4_kernel<false><<<grid_cap(ctx, (num_graphs + TG4 - 1) / TG4, 2), 256, smem4, s2v_pick_stream(ctx, stream)>>>(
-            num_graphs, d, hidden, num_class, Y, W1, W2, logits, probs, pred, ctx->dstatus_dev);
+        S2V_CUDA_OK(ctx, cudaFuncSetAttribute(readout_v4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4));
+        readout_v4_kernel<<<grid_cap(ctx, (num_graphs + TG4 - 1) / TG4, 2), 256, smem4, s2v_pick_stream(ctx, stream)>>>(
+            num_graphs, d, hidden, num_class, Y, W1, W2, logits, probs, pred);
         S2V_CHECK_LAUNCH(ctx, "readout_v4_kernel");
         return S2V_OK;
     }

@@ -109,8 +109,8 @@ def test_pooling_and_readout_separately(gpu_ctx, oracle_lib):
 
 @pytest.mark.parametrize("G,d,hidden,C", [(2048, 128, 256, 2), (5000, 64, 128, 3), (2049, 128, 256, 2)])
 def test_readout_large_batch(gpu_ctx, G, d, hidden, C):
-    """Batches of 2,048 graphs and more take the form of the readout that keeps W1 in shared memory;
-    the last tile of 32 graphs is ragged in two of the cases."""
+    """Readout on batches of thousands of graphs (several 32-graph tiles per CTA); the last tile is
+    ragged in two of the cases."""
     rng = np.random.default_rng(G)
     Y = rng.standard_normal((G, d), dtype=np.float32) * 3.0
     W1 = rng.standard_normal((d, hidden), dtype=np.float32) * 0.1
