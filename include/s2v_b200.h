@@ -89,8 +89,8 @@ int s2v_level_lookup_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_
 
 /* First level of the classifier with one-hot inputs, without materialising H0:
  * out = ReLU((A * ReLU(table[tags,:])) * W + table[tags,:]), A square [n x n]; i.e. MatMul(data, w_n2l),
- * ReLU and the first level (kernel_mean_field.cpp:31-41) in one kernel.  Only the d = 128 tcgen05
- * kernel has this form (n >= 16,384 unless forced); otherwise S2V_ERR_UNSUPPORTED: run
+ * ReLU and the first level (kernel_mean_field.cpp:31-41) in one kernel.  Only the tcgen05 kernel
+ * (d = 64 or 128) has this form (n >= 16,384 unless forced); otherwise S2V_ERR_UNSUPPORTED: run
  * s2v_input_proj_onehot_f32 + s2v_level_lookup_f32 instead. */
 int s2v_level_first_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n, int d, const int32_t* row_ptr,
                         const int32_t* col_idx, const float* val, const float* W, const float* table, int n_table,
