@@ -114,11 +114,12 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
     }
     return true;
 }
-// TF32 head by truncation (the subtraction is then exact) and the tail cut to TF32 the same way:
-// integer-pipe work only, no conversion-unit instruction.  head + tail differs from v by < 2^-21 |v|.
+// TF32 head rounded to nearest (add half an ulp of TF32 to the bit pattern, then cut: integer pipe only,
+// no conversion-unit instruction), tail = v - head (exact) cut to TF32.  head + tail differs from v by
+// less than 2^-23 |v|.
 __device__ __forceinline__ void tc_split(float v, uint32_t& head, uint32_t& tail)
 {
-    head = __float_as_uint(v) & 0xffffe000u;
+    head = (__float_as_uint(v) + 0x1000u) & 0xffffe000u;
     tail = __float_as_uint(v - __uint_as_float(head)) & 0xffffe000u;
 }
 // A 32-bit load that stays where it is written: the values fetched a tile ahead (row offsets, X row
