@@ -58,6 +58,7 @@ def load_library():
         "s2v_status_str": (C.c_char_p, [i32]),
         "s2v_last_error": (C.c_char_p, [vp]),
         "s2v_launch_count": (C.c_uint64, [vp]),
+        "s2v_selftest_wait_timeout": (i32, [vp, vp]),
         "s2v_level_f32": (i32, [vp, vp, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp]),
         "s2v_level_rp64_f32": (i32, [vp, vp, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp]),
         "s2v_level_lookup_f32": (i32, [vp, vp, i64, i64, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp]),
@@ -174,6 +175,11 @@ class Context:
     @property
     def launches(self) -> int:
         return int(self.lib.s2v_launch_count(self.h))
+
+    def selftest_wait_timeout(self, stream=None):
+        """s2v_selftest_wait_timeout: a kernel whose bounded wait runs out on purpose; the next
+        synchronize() raises S2VError with the device time-out status."""
+        self.call("s2v_selftest_wait_timeout", stream)
 
     # -- operators (device tensors in, device tensors out; `stream` = raw cudaStream_t or None)
     def level(self, row_ptr, col_idx, val, H, W, X, out, n_src=None, stream=None):

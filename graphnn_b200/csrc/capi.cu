@@ -157,6 +157,12 @@ int s2v_ctx_synchronize(s2v_ctx* ctx)
     return S2V_OK;
 }
 
+int s2v_selftest_wait_timeout(s2v_ctx* ctx, s2v_stream stream)
+{
+    S2V_ENTER(ctx);
+    return s2v_launch_wait_selftest(ctx, s2v_pick_stream(ctx, stream));
+}
+
 const char* s2v_last_error(const s2v_ctx* ctx)
 {
     return ctx ? ctx->last_error.c_str() : "no context";

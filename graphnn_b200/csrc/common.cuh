@@ -136,6 +136,7 @@ inline bool s2v_use_tc(const s2v_ctx* ctx, int d, int64_t n_rows)
 int s2v_launch_level_tc(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int d, const int32_t* row_ptr,
                         const int32_t* col_idx, const float* val, const float* H, const float* W, const float* X,
                         const float* table, const int32_t* x_index, float* out);
+int s2v_launch_wait_selftest(s2v_ctx* ctx, cudaStream_t st);
 int s2v_launch_level(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int64_t n_src, int d, const void* row_ptr,
                      bool rp64, const int32_t* col_idx, const float* val, const float* H, const float* W,
                      const float* X, const float* table, const int32_t* x_index, float* out);

@@ -631,6 +631,27 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
 }
 
+// Self-test of the bounded wait: one warp waits on an mbarrier that nothing arrives at.  The wait gives up
+// after a few polls, records S2V_ERR_DEVICE_TIMEOUT (site 99) in the context's status word and the kernel
+// returns normally: no trap, no fault, the context stays usable.
+__global__ void tc_wait_selftest_kernel(s2v_device_status* status)
+{
+    __shared__ uint64_t never_arrives;
+    const uint32_t bar = smem_u32(&never_arrives);
+    if (threadIdx.x == 0) {
+        tc_mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    int polls = 0;
+    bool done = false;
+    while (!(done = tc_mbar_try(bar, 0)) && ++polls < 64) {}
+    if (!done && threadIdx.x == 0) {
+        status->code = S2V_ERR_DEVICE_TIMEOUT;
+        status->where = 99;
+    }
+}
+
 template <int D, bool HAS_VAL, int XMODE, bool HSRC_TABLE = false>
 int tc_launch(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const int32_t* rp, const int32_t* ci, const float* val,
               const float* H, const float* W, const float* X, const int32_t* x_index, float* out)
@@ -683,4 +704,11 @@ int s2v_launch_level_tc(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int d, co
     if (d == 128) return tc_dispatch<128>(ctx, st, n_rows, row_ptr, col_idx, val, H, W, X, table, x_index, out);
     if (d == 64) return tc_dispatch<64>(ctx, st, n_rows, row_ptr, col_idx, val, H, W, X, table, x_index, out);
     return S2V_ERR_UNSUPPORTED;
+}
+
+int s2v_launch_wait_selftest(s2v_ctx* ctx, cudaStream_t st)
+{
+    tc_wait_selftest_kernel<<<1, 32, 0, st>>>(ctx->dstatus_dev);
+    S2V_CHECK_LAUNCH(ctx, "tc_wait_selftest_kernel");
+    return S2V_OK;
 }

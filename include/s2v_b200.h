@@ -56,6 +56,12 @@ s2v_stream s2v_ctx_stream(const s2v_ctx* ctx);
 int s2v_ctx_synchronize(s2v_ctx* ctx);
 const char* s2v_status_str(int status);
 const char* s2v_last_error(const s2v_ctx* ctx);
+/* Diagnostic, no counterpart in the reference: launches a one-warp kernel whose bounded barrier wait runs
+ * out on purpose (nothing ever arrives).  The kernel returns normally; the next s2v_ctx_synchronize reports
+ * S2V_ERR_DEVICE_TIMEOUT (site 99) and clears it, and the context stays usable.  This is the path every
+ * wait in the level kernels takes instead of hanging the GPU. */
+int s2v_selftest_wait_timeout(s2v_ctx* ctx, s2v_stream stream);
+
 /* Number of kernels this library has launched through `ctx` since creation. */
 uint64_t s2v_launch_count(const s2v_ctx* ctx);
 

@@ -159,3 +159,17 @@ def test_tc_first_level_with_long_rows(tc_ctx, d):
     # the size of the terms that cancel (the fp32 reference itself is no closer to this float64 result)
     scale = float(((A @ h0) @ np.abs(W).astype(np.float64))[long_rows].max())
     assert_close(got[long_rows], want[long_rows], f"first level, long rows, d={d}", scale=scale)
+
+
+def test_bounded_wait_reports_and_context_survives(gpu_ctx, oracle_lib):
+    """The time-out path of the kernels' barrier waits, exercised without any fault: a wait that nothing
+    will ever satisfy gives up, the kernel returns, the host reads the status, and the same context then
+    runs a level correctly."""
+    from graphnn_b200.capi import S2VError
+    gpu_ctx.selftest_wait_timeout()
+    with pytest.raises(S2VError) as e:
+        gpu_ctx.synchronize()
+    assert e.value.status == -7 and "site 99" in str(e.value)      # S2V_ERR_DEVICE_TIMEOUT
+    gpu_ctx.synchronize()                                           # the status was cleared
+    p = synth.erdos_renyi_level(n=20000, nnz=90000, d=128, seed=3)  # large enough for the tcgen05 kernel
+    assert_close(run_level(gpu_ctx, p), oracle_level(oracle_lib, p), "level after a reported time-out")
