@@ -28,13 +28,14 @@ class S2VError(RuntimeError):
 class Model(C.Structure):
     _fields_ = [("num_feat", C.c_int), ("d", C.c_int), ("levels", C.c_int), ("hidden", C.c_int),
                 ("num_class", C.c_int), ("w_n2l", C.c_void_p), ("p_node_conv", C.c_void_p),
-                ("h1_weight", C.c_void_p), ("h2_weight", C.c_void_p)]
+                ("h1_weight", C.c_void_p), ("h2_weight", C.c_void_p), ("pool_average", C.c_int)]
 
 
 class Batch(C.Structure):
     _fields_ = [("num_graphs", C.c_int64), ("num_nodes", C.c_int64), ("num_edges", C.c_int64),
                 ("n2n_row_ptr", C.c_void_p), ("n2n_col_idx", C.c_void_p), ("n2n_val", C.c_void_p),
-                ("graph_ptr", C.c_void_p), ("tags", C.c_void_p), ("x_dense", C.c_void_p)]
+                ("graph_ptr", C.c_void_p), ("tags", C.c_void_p), ("x_dense", C.c_void_p),
+                ("max_graph_nodes", C.c_int32)]
 
 
 _lib = None
@@ -55,6 +56,8 @@ def load_library():
         "s2v_ctx_device": (i32, [vp]),
         "s2v_ctx_stream": (vp, [vp]),
         "s2v_ctx_synchronize": (i32, [vp]),
+        "s2v_stream_status": (i32, [vp, vp]),
+        "s2v_ctx_set_option": (i32, [vp, i32, i32]),
         "s2v_status_str": (C.c_char_p, [i32]),
         "s2v_last_error": (C.c_char_p, [vp]),
         "s2v_launch_count": (C.c_uint64, [vp]),
@@ -77,15 +80,30 @@ def load_library():
         "s2v_mean_f32": (i32, [vp, vp, i64, vp, vp]),
         "s2v_loss_acc_f32": (i32, [vp, vp, i64, i32, vp, vp, vp, vp, i32, vp, vp, vp]),
         "s2v_segment_sum_f32": (i32, [vp, vp, i64, i32, vp, vp, vp]),
+        "s2v_segment_pool_f32": (i32, [vp, vp, i64, i32, vp, vp, i32, vp]),
         "s2v_readout_f32": (i32, [vp, vp, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp]),
         "s2v_input_proj_onehot_f32": (i32, [vp, vp, i64, i32, i32, vp, vp, vp, vp]),
         "s2v_input_proj_dense_f32": (i32, [vp, vp, i64, i32, i32, vp, vp, vp, vp]),
+        "s2v_graph_tiles_workspace_bytes": (C.c_size_t, [i64]),
+        "s2v_graph_tiles_f32": (i32, [vp, vp, i64, i32, i32, vp, vp, vp, vp, vp, i32, vp, vp, i32, vp, C.c_size_t, vp, vp]),
         "s2v_forward_workspace_bytes": (C.c_size_t, [i64, i64, i32]),
         "s2v_forward_f32": (i32, [vp, vp, C.POINTER(Model), C.POINTER(Batch), vp, C.c_size_t, vp, vp, vp, vp]),
         "s2v_forward_static_f32": (i32, [vp, vp, C.POINTER(Model), C.POINTER(Batch), vp, vp, vp, vp]),
         "s2v_build_n2n_csr_host": (i32, [i64, i64, vp, vp, i32, vp, vp, vp]),
         "s2v_validate_csr_host": (i32, [i64, i64, i64, vp, vp]),
         "s2v_infer_host_f32": (i32, [vp, C.POINTER(Model), C.POINTER(Batch), vp, vp]),
+        "s2v_comm_create": (i32, [i32, vp, vp]),
+        "s2v_comm_unique_id": (i32, [vp]),
+        "s2v_comm_create_rank": (i32, [i32, vp, i32, i32, C.POINTER(vp)]),
+        "s2v_comm_destroy": (i32, [vp]),
+        "s2v_comm_rank": (i32, [vp]),
+        "s2v_comm_world": (i32, [vp]),
+        "s2v_comm_last_error": (C.c_char_p, [vp]),
+        "s2v_allgather_rows_f32": (i32, [vp, vp, i64, i32, vp, vp]),
+        "s2v_gather_logits": (i32, [vp, vp, vp, i32, vp, vp, vp, vp]),
+        "s2v_infer_edges_host_f32": (i32, [vp, C.POINTER(Model), i64, i64, i64, vp, vp, vp, vp, vp, vp]),
+        "s2v_build_n2n_csr_scratch_bytes": (C.c_size_t, [i64, i64]),
+        "s2v_build_n2n_csr_f32": (i32, [vp, vp, i64, i64, vp, vp, i32, vp, C.c_size_t, vp, vp, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -133,6 +151,57 @@ def validate_csr_host(m: int, k: int, row_ptr: np.ndarray, col_idx: np.ndarray) 
     return lib.s2v_validate_csr_host(m, k, int(ci.shape[0]), _ptr(rp), _ptr(ci))
 
 
+COMM_ID_BYTES = 128
+
+
+def comm_unique_id() -> bytes:
+    """s2v_comm_unique_id: the 128-byte id rank 0 hands to the other ranks."""
+    lib = load_library()
+    buf = C.create_string_buffer(COMM_ID_BYTES)
+    rc = lib.s2v_comm_unique_id(buf)
+    if rc != 0:
+        raise S2VError(rc, f"{lib.s2v_status_str(rc).decode()}: {lib.s2v_comm_last_error(None).decode()}")
+    return buf.raw
+
+
+class Comm:
+    """One s2v_comm: this rank's NCCL communicator, created from the id rank 0 distributed."""
+
+    def __init__(self, device: int, unique_id: bytes, world: int, rank: int):
+        self.lib = load_library()
+        h = C.c_void_p()
+        rc = self.lib.s2v_comm_create_rank(int(device), unique_id, int(world), int(rank), C.byref(h))
+        if rc != 0:
+            raise S2VError(rc, f"{self.lib.s2v_status_str(rc).decode()}: {self.lib.s2v_comm_last_error(None).decode()}")
+        self.h, self.world, self.rank = h, world, rank
+
+    def check(self, rc: int):
+        if rc != 0:
+            raise S2VError(rc, f"{self.lib.s2v_status_str(rc).decode()}: {self.lib.s2v_comm_last_error(self.h).decode()}")
+
+    def allgather_rows(self, slab, full, stream):
+        """full[r] = slab of rank r (equal [rows x d] slabs); asynchronous on `stream`."""
+        rows, d = slab.shape
+        self.check(self.lib.s2v_allgather_rows_f32(self.h, stream, rows, d, _ptr(slab), _ptr(full)))
+
+    def gather_logits(self, graphs_per_rank, logits_local, pred_local, logits_all, pred_all, stream):
+        counts = np.ascontiguousarray(graphs_per_rank, np.int64)
+        num_class = logits_all.shape[1] if logits_all is not None else 1
+        self.check(self.lib.s2v_gather_logits(self.h, stream, counts.ctypes.data, num_class, _ptr(logits_local),
+                                              _ptr(pred_local), _ptr(logits_all), _ptr(pred_all)))
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.s2v_comm_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class Context:
     """One s2v_ctx: a device, its stream and the library's launch counter."""
 
@@ -171,6 +240,15 @@ class Context:
 
     def synchronize(self):
         self.check(self.lib.s2v_ctx_synchronize(self.h))
+
+    def stream_status(self, stream=None):
+        """Synchronises `stream` (None = the context's own) and raises if a kernel recorded a status."""
+        self.check(self.lib.s2v_stream_status(self.h, stream))
+
+    OPT_VALIDATE_HOST_INPUT, OPT_LEVEL_TC, OPT_GRAPH_TILES = 1, 2, 3
+
+    def set_option(self, option: int, value: int):
+        self.check(self.lib.s2v_ctx_set_option(self.h, int(option), int(value)))
 
     @property
     def launches(self) -> int:
@@ -239,9 +317,20 @@ class Context:
         self.call("s2v_loss_acc_f32", stream, logits.shape[0], logits.shape[1], _ptr(logits), _ptr(label_rp), _ptr(label_ci),
                   _ptr(label_val), topk, _ptr(loss), _ptr(acc), _ptr(per_graph))
 
-    def segment_sum(self, seg_ptr, H, Y, stream=None):
-        self.call("s2v_segment_sum_f32", stream, Y.shape[0], H.shape[1], _ptr(seg_ptr), _ptr(H), _ptr(Y))
+    def segment_sum(self, seg_ptr, H, Y, stream=None, average=False):
+        self.call("s2v_segment_pool_f32", stream, Y.shape[0], H.shape[1], _ptr(seg_ptr), _ptr(H), int(average), _ptr(Y))
         return Y
+
+    def graph_tiles(self, levels, row_ptr, col_idx, val, graph_ptr, tags, W_in, W, workspace, Y, embed_out=None,
+                    pool_average=False, stream=None):
+        """s2v_graph_tiles_f32: projection + L levels + pooling of a batch of small graphs in one kernel."""
+        self.call("s2v_graph_tiles_f32", stream, Y.shape[0], Y.shape[1], levels, _ptr(row_ptr), _ptr(col_idx), _ptr(val),
+                  _ptr(graph_ptr), _ptr(tags), W_in.shape[0], _ptr(W_in), _ptr(W), int(pool_average), _ptr(workspace),
+                  workspace.numel() * workspace.element_size(), _ptr(Y), _ptr(embed_out))
+        return Y
+
+    def graph_tiles_workspace_bytes(self, num_graphs: int) -> int:
+        return int(self.lib.s2v_graph_tiles_workspace_bytes(num_graphs))
 
     def readout(self, Y, W1, W2, logits, probs=None, pred=None, stream=None):
         self.call("s2v_readout_f32", stream, Y.shape[0], Y.shape[1], W1.shape[1], W2.shape[1], _ptr(Y), _ptr(W1),
@@ -258,16 +347,18 @@ class Context:
 
     # -- whole model
     @staticmethod
-    def make_model(levels: int, w_n2l, p_node_conv, h1_weight, h2_weight) -> Model:
+    def make_model(levels: int, w_n2l, p_node_conv, h1_weight, h2_weight, pool_average: bool = False) -> Model:
         """`w_*` are DEVICE tensors (kept alive by the caller)."""
         return Model(w_n2l.shape[0], w_n2l.shape[1], levels, h1_weight.shape[1], h2_weight.shape[1],
-                     _ptr(w_n2l), _ptr(p_node_conv), _ptr(h1_weight), _ptr(h2_weight))
+                     _ptr(w_n2l), _ptr(p_node_conv), _ptr(h1_weight), _ptr(h2_weight), int(pool_average))
 
     @staticmethod
-    def make_batch(num_graphs, num_nodes, row_ptr, col_idx, val, graph_ptr, tags=None, x_dense=None) -> Batch:
-        """Arrays are torch device tensors (device entry) or numpy arrays (host entry)."""
+    def make_batch(num_graphs, num_nodes, row_ptr, col_idx, val, graph_ptr, tags=None, x_dense=None,
+                   max_graph_nodes: int = 0) -> Batch:
+        """Arrays are torch device tensors (device entry) or numpy arrays (host entry).  `max_graph_nodes`:
+        node count of the largest graph (0 = unknown: the per-level kernels are used)."""
         return Batch(num_graphs, num_nodes, int(col_idx.shape[0]), _ptr(row_ptr), _ptr(col_idx), _ptr(val),
-                     _ptr(graph_ptr), _ptr(tags), _ptr(x_dense))
+                     _ptr(graph_ptr), _ptr(tags), _ptr(x_dense), int(max_graph_nodes))
 
     def workspace_bytes(self, num_nodes, num_graphs, d) -> int:
         return int(self.lib.s2v_forward_workspace_bytes(num_nodes, num_graphs, d))
@@ -282,6 +373,24 @@ class Context:
         """s2v_forward_static_f32: like forward() but with the library's built-in scratch array."""
         self.call("s2v_forward_static_f32", stream, C.byref(model), C.byref(batch), _ptr(logits), _ptr(probs),
                   _ptr(pred), _ptr(embed_out))
+
+    def build_n2n_csr(self, num_nodes: int, edge_src, edge_dst, scratch, row_ptr, col_idx, val=None, average=False,
+                      stream=None):
+        """s2v_build_n2n_csr_f32: device edge list -> device CSR (all torch int32 device tensors)."""
+        self.call("s2v_build_n2n_csr_f32", stream, num_nodes, int(edge_src.shape[0]), _ptr(edge_src), _ptr(edge_dst),
+                  int(average), _ptr(scratch), scratch.numel() * scratch.element_size(), _ptr(row_ptr), _ptr(col_idx),
+                  _ptr(val))
+
+    def csr_scratch_bytes(self, num_nodes: int, num_edges: int) -> int:
+        return int(self.lib.s2v_build_n2n_csr_scratch_bytes(num_nodes, num_edges))
+
+    def infer_edges_host(self, model: Model, num_graphs, num_nodes, edge_src, edge_dst, graph_ptr, tags,
+                         logits_host, pred_host):
+        """s2v_infer_edges_host_f32: host edge list in, host logits / predictions out."""
+        rc = self.lib.s2v_infer_edges_host_f32(self.h, C.byref(model), num_graphs, num_nodes, int(edge_src.shape[0]),
+                                               _ptr(edge_src), _ptr(edge_dst), _ptr(graph_ptr), _ptr(tags),
+                                               _ptr(logits_host), _ptr(pred_host))
+        self.check(rc)
 
     def infer_host(self, model: Model, batch_host: Batch, logits_host: np.ndarray | None,
                    pred_host: np.ndarray | None):

@@ -24,6 +24,7 @@ const char* status_text(int s)
         case S2V_ERR_WORKSPACE: return "workspace too small";
         case S2V_ERR_NO_DEVICE: return "no CUDA device";
         case S2V_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+        case S2V_ERR_COMM: return "NCCL communication error";
         default: return "unknown status";
     }
 }
@@ -116,6 +117,8 @@ int s2v_ctx_create(int device, s2v_ctx** out)
     ctx->dstatus_host->where = 0;
     // S2V_LEVEL_TC = 0 | 1 | 2 : never / automatic / always use the tcgen05 level kernel (d = 128)
     if (const char* e = std::getenv("S2V_LEVEL_TC")) ctx->tc_mode = (e[0] == '0') ? 0 : (e[0] == '2' ? 2 : 1);
+    if (const char* e = std::getenv("S2V_GRAPH_TILES")) ctx->graph_tiles = (e[0] == '0') ? 0 : 1;
+    if (const char* e = std::getenv("S2V_VALIDATE_HOST")) ctx->validate_host = (e[0] == '0') ? 0 : 1;
     *out = ctx;
     return S2V_OK;
 }
@@ -146,8 +149,24 @@ s2v_stream s2v_ctx_stream(const s2v_ctx* ctx)
 
 int s2v_ctx_synchronize(s2v_ctx* ctx)
 {
+    return s2v_stream_status(ctx, nullptr);
+}
+
+int s2v_ctx_set_option(s2v_ctx* ctx, int option, int value)
+{
+    if (!ctx) return S2V_ERR_INVALID_ARG;
+    switch (option) {
+        case S2V_OPT_VALIDATE_HOST_INPUT: ctx->validate_host = value != 0; return S2V_OK;
+        case S2V_OPT_LEVEL_TC: ctx->tc_mode = value <= 0 ? 0 : (value >= 2 ? 2 : 1); return S2V_OK;
+        case S2V_OPT_GRAPH_TILES: ctx->graph_tiles = value != 0; return S2V_OK;
+        default: return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "set_option: unknown option");
+    }
+}
+
+int s2v_stream_status(s2v_ctx* ctx, s2v_stream stream)
+{
     S2V_ENTER(ctx);
-    S2V_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    S2V_CUDA_OK(ctx, cudaStreamSynchronize(s2v_pick_stream(ctx, stream)));
     if (ctx->dstatus_host->code != 0) {
         const int code = ctx->dstatus_host->code, where = ctx->dstatus_host->where;
         ctx->dstatus_host->code = 0;
@@ -182,7 +201,7 @@ int s2v_level_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_t n_src
     int rc = check_level_args(ctx, n_rows, n_src, d, row_ptr, col_idx, H, W, X, out);
     if (rc != S2V_OK || n_rows == 0) return rc;
     return s2v_launch_level(ctx, s2v_pick_stream(ctx, stream), n_rows, n_src, d, row_ptr, false, col_idx, val, H, W, X,
-                            nullptr, nullptr, out);
+                            nullptr, nullptr, 0, out);
 }
 
 int s2v_level_rp64_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_t n_src, int d, const int64_t* row_ptr,
@@ -193,7 +212,7 @@ int s2v_level_rp64_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_t 
     int rc = check_level_args(ctx, n_rows, n_src, d, row_ptr, col_idx, H, W, X, out);
     if (rc != S2V_OK || n_rows == 0) return rc;
     return s2v_launch_level(ctx, s2v_pick_stream(ctx, stream), n_rows, n_src, d, row_ptr, true, col_idx, val, H, W, X,
-                            nullptr, nullptr, out);
+                            nullptr, nullptr, 0, out);
 }
 
 int s2v_level_lookup_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_t n_src, int d,
@@ -205,7 +224,7 @@ int s2v_level_lookup_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_
     if (rc != S2V_OK || n_rows == 0) return rc;
     if (!table || !x_index || n_table <= 0) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level_lookup: NULL table or index");
     return s2v_launch_level(ctx, s2v_pick_stream(ctx, stream), n_rows, n_src, d, row_ptr, false, col_idx, val, H, W,
-                            nullptr, table, x_index, out);
+                            nullptr, table, x_index, n_table, out);
 }
 
 int s2v_level_first_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n, int d, const int32_t* row_ptr, const int32_t* col_idx,
@@ -220,8 +239,36 @@ int s2v_level_first_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n, int d, const
     if (!s2v_use_tc(ctx, d, n))
         return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "level_first: only the tcgen05 kernel (d = 64 or 128, large batch) has this form; materialise H0 instead");
     const int rc = s2v_launch_level_tc(ctx, s2v_pick_stream(ctx, stream), n, d, row_ptr, col_idx, val, nullptr, W, nullptr, table,
-                                       tags, out);
+                                       tags, n_table, out);
     if (rc == S2V_ERR_UNSUPPORTED) return s2v_fail(ctx, rc, "level_first: shape not supported by the tcgen05 kernel");
+    return rc;
+}
+
+// ---------------------------------------------------------------- tile kernel for batches of small graphs
+size_t s2v_graph_tiles_workspace_bytes(int64_t num_graphs)
+{
+    return num_graphs < 0 ? 0 : align_up(s2v_graph_tiles_plan_bytes(num_graphs), 256) + 256;
+}
+
+int s2v_graph_tiles_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int d, int levels, const int32_t* row_ptr,
+                        const int32_t* col_idx, const float* val, const int32_t* graph_ptr, const int32_t* tags, int num_tags,
+                        const float* W_in, const float* W, int pool_average, void* workspace, size_t workspace_bytes, float* Y,
+                        float* embed_out)
+{
+    S2V_ENTER(ctx);
+    if (num_graphs < 0 || levels < 1 || num_tags <= 0) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "graph_tiles: bad shape");
+    if (d != 128) return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "graph_tiles: the tile kernel is built for d = 128");
+    if (num_graphs == 0) return S2V_OK;
+    if (num_graphs >= (int64_t)INT32_MAX) return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "graph_tiles: int32 graph count only");
+    if (!row_ptr || !graph_ptr || !tags || !W_in || !W || !Y) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "graph_tiles: NULL pointer");
+    if (!s2v_aligned16(W_in) || !s2v_aligned16(W) || !s2v_aligned16(Y) || !s2v_aligned16(embed_out))
+        return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "graph_tiles: W_in, W, Y, embed_out must be 16-byte aligned");
+    if (!workspace || workspace_bytes < s2v_graph_tiles_workspace_bytes(num_graphs))
+        return s2v_fail(ctx, S2V_ERR_WORKSPACE, "graph_tiles: workspace smaller than s2v_graph_tiles_workspace_bytes");
+    void* plan = reinterpret_cast<void*>(align_up(reinterpret_cast<uintptr_t>(workspace), 256));
+    const int rc = s2v_launch_graph_tiles(ctx, s2v_pick_stream(ctx, stream), num_graphs, row_ptr, col_idx, val, graph_ptr, tags,
+                                          num_tags, W_in, W, levels, pool_average, plan, Y, embed_out);
+    if (rc == S2V_ERR_UNSUPPORTED) return s2v_fail(ctx, rc, "graph_tiles: this device cannot hold the kernel's shared memory");
     return rc;
 }
 
@@ -231,7 +278,7 @@ size_t s2v_forward_workspace_bytes(int64_t num_nodes, int64_t num_graphs, int d)
     if (num_nodes < 0 || num_graphs < 0 || d <= 0) return 0;
     const size_t nd = align_up(sizeof(float) * (size_t)num_nodes * d, 256);
     const size_t gd = align_up(sizeof(float) * (size_t)num_graphs * d, 256);
-    return 3 * nd + gd + 256;
+    return 3 * nd + gd + 256 + align_up(s2v_graph_tiles_plan_bytes(num_graphs), 256);
 }
 
 int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, const s2v_batch* batch, void* workspace,
@@ -259,8 +306,23 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
     float* ha = reinterpret_cast<float*>(ws + nd);
     float* hb = reinterpret_cast<float*>(ws + 2 * nd);
     float* y = reinterpret_cast<float*>(ws + 3 * nd);
+    void* plan = ws + 3 * nd + align_up(sizeof(float) * (size_t)G * d, 256);
 
     int rc;
+    // Batches of small graphs (the caller vouches for the largest one): the whole classifier up to the pooled
+    // embeddings is one kernel that keeps the node embeddings of a tile of whole graphs in shared memory.
+    if (ctx->graph_tiles && d == 128 && L >= 1 && batch->tags && batch->max_graph_nodes >= 1 &&
+        batch->max_graph_nodes <= S2V_TILE_NODES && N > 0 && G < (int64_t)INT32_MAX) {
+        if (!s2v_aligned16(model->w_n2l) || !s2v_aligned16(model->p_node_conv) || (embed_out && !s2v_aligned16(embed_out)))
+            return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "forward: weights and embed_out must be 16-byte aligned");
+        rc = s2v_launch_graph_tiles(ctx, st, G, batch->n2n_row_ptr, batch->n2n_col_idx, batch->n2n_val, batch->graph_ptr,
+                                    batch->tags, model->num_feat, model->w_n2l, model->p_node_conv, L, model->pool_average,
+                                    plan, y, embed_out);
+        if (rc == S2V_OK)
+            return s2v_readout_f32(ctx, st, G, d, model->hidden, model->num_class, y, model->h1_weight, model->h2_weight,
+                                   logits, probs, pred);
+        if (rc != S2V_ERR_UNSUPPORTED) return rc;
+    }
     // With one-hot tags the X term of every level is a lookup in W_in, so `msg` is
     // never materialised; a dense X needs it.
     const bool onehot = batch->tags != nullptr && d % 4 == 0;
@@ -298,7 +360,7 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
     }
     if (L == 0 && embed_out)
         S2V_CUDA_OK(ctx, cudaMemcpyAsync(embed_out, cur, sizeof(float) * (size_t)N * d, cudaMemcpyDeviceToDevice, st));
-    rc = s2v_segment_sum_f32(ctx, st, G, d, batch->graph_ptr, cur, y);
+    rc = s2v_segment_pool_f32(ctx, st, G, d, batch->graph_ptr, cur, model->pool_average, y);
     if (rc != S2V_OK) return rc;
     return s2v_readout_f32(ctx, st, G, d, model->hidden, model->num_class, y, model->h1_weight, model->h2_weight, logits,
                            probs, pred);
@@ -445,6 +507,37 @@ int s2v_infer_host_f32(s2v_ctx* ctx, const s2v_model* model, const s2v_batch* hb
     // cheap structural check on the host (full validation is s2v_validate_csr_host)
     if (hb->n2n_row_ptr[0] != 0 || hb->n2n_row_ptr[N] != E || hb->graph_ptr[0] != 0 || hb->graph_ptr[G] != N)
         return s2v_fail(ctx, S2V_ERR_BAD_CSR, "infer_host: row_ptr / graph_ptr ends do not match the sizes");
+    // The arrays are on the host here, so a malformed batch is turned away before anything reaches the
+    // device: monotone offsets, column indices inside the matrix, tags inside the table.  One pass over
+    // N + E integers (OpenMP for large batches); S2V_OPT_VALIDATE_HOST_INPUT = 0 skips it.
+    int32_t max_nodes = 0;
+    {
+        int T = omp_get_max_threads();
+        if (T > 16) T = 16;
+        int bad_csr = 0, bad_tag = 0;
+        const int32_t* gp = hb->graph_ptr;
+#pragma omp parallel for num_threads(T) schedule(static) reduction(max : max_nodes) reduction(| : bad_csr) if (G >= (1 << 15))
+        for (int64_t g = 0; g < G; ++g) {
+            const int32_t n = gp[g + 1] - gp[g];
+            if (n < 0) bad_csr |= 1;
+            if (n > max_nodes) max_nodes = n;
+        }
+        if (ctx->validate_host) {
+            const int32_t* rp = hb->n2n_row_ptr;
+            const int32_t* ci = hb->n2n_col_idx;
+            const int32_t* tg = hb->tags;
+#pragma omp parallel for num_threads(T) schedule(static) reduction(| : bad_csr, bad_tag) if (N >= (1 << 15))
+            for (int64_t i = 0; i < N; ++i) {
+                if (rp[i + 1] < rp[i]) bad_csr |= 1;
+                if (tg && (tg[i] < 0 || tg[i] >= F)) bad_tag |= 1;
+            }
+#pragma omp parallel for num_threads(T) schedule(static) reduction(| : bad_csr) if (E >= (1 << 15))
+            for (int64_t t = 0; t < E; ++t)
+                if (ci[t] < 0 || ci[t] >= N) bad_csr |= 1;
+        }
+        if (bad_csr) return s2v_fail(ctx, S2V_ERR_BAD_CSR, "infer_host: offsets not monotone or a column index outside [0, N)");
+        if (bad_tag) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_host: a node tag outside [0, num_feat)");
+    }
 
     // device layout: [row_ptr | col_idx | val? | graph_ptr | tags or X | logits | pred | workspace]
     size_t off = 0;
@@ -475,6 +568,7 @@ int s2v_infer_host_f32(s2v_ctx* ctx, const s2v_model* model, const s2v_batch* hb
         S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_in, hb->x_dense, sizeof(float) * (size_t)N * F, cudaMemcpyHostToDevice, st));
 
     s2v_batch db = *hb;
+    db.max_graph_nodes = max_nodes;
     db.n2n_row_ptr = reinterpret_cast<const int32_t*>(dev + o_rp);
     db.n2n_col_idx = reinterpret_cast<const int32_t*>(dev + o_ci);
     db.n2n_val = hb->n2n_val ? reinterpret_cast<const float*>(dev + o_val) : nullptr;
@@ -486,6 +580,98 @@ int s2v_infer_host_f32(s2v_ctx* ctx, const s2v_model* model, const s2v_batch* hb
     rc = s2v_forward_f32(ctx, st, model, &db, dev + o_ws, ws_bytes, d_logits, nullptr, d_pred, nullptr);
     if (rc != S2V_OK) return rc;
 
+    float* p_logits = static_cast<float*>(ctx->staging.pinned);
+    int32_t* p_pred = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(ctx->staging.pinned) +
+                                                 align_up(sizeof(float) * (size_t)G * C, 256));
+    if (logits_host)
+        S2V_CUDA_OK(ctx, cudaMemcpyAsync(p_logits, d_logits, sizeof(float) * (size_t)G * C, cudaMemcpyDeviceToHost, st));
+    if (pred_host)
+        S2V_CUDA_OK(ctx, cudaMemcpyAsync(p_pred, d_pred, sizeof(int32_t) * (size_t)G, cudaMemcpyDeviceToHost, st));
+    rc = s2v_ctx_synchronize(ctx);
+    if (rc != S2V_OK) return rc;
+    if (logits_host) std::memcpy(logits_host, p_logits, sizeof(float) * (size_t)G * C);
+    if (pred_host) std::memcpy(pred_host, p_pred, sizeof(int32_t) * (size_t)G);
+    return S2V_OK;
+}
+
+// Same from a raw edge list: the CSR is built on the device (s2v_build_n2n_csr_f32).
+int s2v_infer_edges_host_f32(s2v_ctx* ctx, const s2v_model* model, int64_t num_graphs, int64_t num_nodes, int64_t num_edges,
+                             const int32_t* edge_src_host, const int32_t* edge_dst_host, const int32_t* graph_ptr_host,
+                             const int32_t* tags_host, float* logits_host, int32_t* pred_host)
+{
+    S2V_ENTER(ctx);
+    if (!model) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_edges: NULL model");
+    const int64_t N = num_nodes, G = num_graphs, E = num_edges;
+    const int d = model->d, C = model->num_class, F = model->num_feat;
+    if (N < 0 || G < 0 || E < 0 || d <= 0 || C <= 0 || F <= 0) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_edges: bad shape");
+    if (G == 0) return S2V_OK;
+    if (!graph_ptr_host || !tags_host || (E > 0 && (!edge_src_host || !edge_dst_host)))
+        return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_edges: NULL batch array");
+    if (N >= (int64_t)INT32_MAX || E >= (int64_t)INT32_MAX) return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "infer_edges: int32 sizes only");
+    if (graph_ptr_host[0] != 0 || graph_ptr_host[G] != N)
+        return s2v_fail(ctx, S2V_ERR_BAD_CSR, "infer_edges: graph_ptr ends do not match the sizes");
+    int32_t max_nodes = 0;
+    {
+        int bad = 0, bad_tag = 0;
+        for (int64_t g = 0; g < G; ++g) {
+            const int32_t n = graph_ptr_host[g + 1] - graph_ptr_host[g];
+            if (n < 0) bad = 1;
+            if (n > max_nodes) max_nodes = n;
+        }
+        if (ctx->validate_host) {
+            int T = omp_get_max_threads();
+            if (T > 16) T = 16;
+#pragma omp parallel for num_threads(T) schedule(static) reduction(| : bad_tag) if (N >= (1 << 15))
+            for (int64_t i = 0; i < N; ++i)
+                if (tags_host[i] < 0 || tags_host[i] >= F) bad_tag |= 1;
+#pragma omp parallel for num_threads(T) schedule(static) reduction(| : bad) if (E >= (1 << 15))
+            for (int64_t e = 0; e < E; ++e)
+                if (edge_src_host[e] < 0 || edge_src_host[e] >= N || edge_dst_host[e] < 0 || edge_dst_host[e] >= N) bad |= 1;
+        }
+        if (bad) return s2v_fail(ctx, S2V_ERR_BAD_CSR, "infer_edges: graph_ptr not monotone or an edge endpoint outside [0, N)");
+        if (bad_tag) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_edges: a node tag outside [0, num_feat)");
+    }
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
+    const size_t o_es = take(sizeof(int32_t) * (size_t)E);
+    const size_t o_ed = take(sizeof(int32_t) * (size_t)E);
+    const size_t o_rp = take(sizeof(int32_t) * (size_t)(N + 1));
+    const size_t o_ci = take(sizeof(int32_t) * (size_t)E);
+    const size_t o_gp = take(sizeof(int32_t) * (size_t)(G + 1));
+    const size_t o_tg = take(sizeof(int32_t) * (size_t)N);
+    const size_t o_logits = take(sizeof(float) * (size_t)G * C);
+    const size_t o_pred = take(sizeof(int32_t) * (size_t)G);
+    const size_t sc_bytes = s2v_build_n2n_csr_scratch_bytes(N, E);
+    const size_t o_sc = take(sc_bytes);
+    const size_t ws_bytes = s2v_forward_workspace_bytes(N, G, d);
+    const size_t o_ws = take(ws_bytes);
+    int rc = ensure_staging(ctx, off, sizeof(float) * (size_t)G * C + sizeof(int32_t) * (size_t)G + 512);
+    if (rc != S2V_OK) return rc;
+    unsigned char* dev = static_cast<unsigned char*>(ctx->staging.dev);
+    cudaStream_t st = ctx->stream;
+    if (E > 0) {
+        S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_es, edge_src_host, sizeof(int32_t) * (size_t)E, cudaMemcpyHostToDevice, st));
+        S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_ed, edge_dst_host, sizeof(int32_t) * (size_t)E, cudaMemcpyHostToDevice, st));
+    }
+    S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_gp, graph_ptr_host, sizeof(int32_t) * (size_t)(G + 1), cudaMemcpyHostToDevice, st));
+    S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_tg, tags_host, sizeof(int32_t) * (size_t)N, cudaMemcpyHostToDevice, st));
+    rc = s2v_build_n2n_csr_f32(ctx, st, N, E, reinterpret_cast<const int32_t*>(dev + o_es), reinterpret_cast<const int32_t*>(dev + o_ed),
+                               0, dev + o_sc, sc_bytes, reinterpret_cast<int32_t*>(dev + o_rp), reinterpret_cast<int32_t*>(dev + o_ci),
+                               nullptr);
+    if (rc != S2V_OK) return rc;
+    s2v_batch db{};
+    db.num_graphs = G;
+    db.num_nodes = N;
+    db.num_edges = E;
+    db.n2n_row_ptr = reinterpret_cast<const int32_t*>(dev + o_rp);
+    db.n2n_col_idx = reinterpret_cast<const int32_t*>(dev + o_ci);
+    db.graph_ptr = reinterpret_cast<const int32_t*>(dev + o_gp);
+    db.tags = reinterpret_cast<const int32_t*>(dev + o_tg);
+    db.max_graph_nodes = max_nodes;
+    float* d_logits = reinterpret_cast<float*>(dev + o_logits);
+    int32_t* d_pred = reinterpret_cast<int32_t*>(dev + o_pred);
+    rc = s2v_forward_f32(ctx, st, model, &db, dev + o_ws, ws_bytes, d_logits, nullptr, d_pred, nullptr);
+    if (rc != S2V_OK) return rc;
     float* p_logits = static_cast<float*>(ctx->staging.pinned);
     int32_t* p_pred = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(ctx->staging.pinned) +
                                                  align_up(sizeof(float) * (size_t)G * C, 256));

@@ -38,6 +38,8 @@ struct s2v_ctx {
     std::mutex mu;
     s2v_staging staging;
     int tc_mode = 1;  // tcgen05 level kernel: 0 never, 1 when the batch is large enough, 2 whenever the shape allows
+    int graph_tiles = 1;    // whole-classifier tile kernel for batches of small graphs: 0 off, 1 automatic
+    int validate_host = 1;  // s2v_infer_host_f32 scans its host arrays before launching
 };
 
 inline int s2v_fail(s2v_ctx* ctx, int status, const std::string& msg)
@@ -135,8 +137,15 @@ inline bool s2v_use_tc(const s2v_ctx* ctx, int d, int64_t n_rows)
 // launchers implemented in the .cu files (host side)
 int s2v_launch_level_tc(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int d, const int32_t* row_ptr,
                         const int32_t* col_idx, const float* val, const float* H, const float* W, const float* X,
-                        const float* table, const int32_t* x_index, float* out);
+                        const float* table, const int32_t* x_index, int n_table, float* out);
 int s2v_launch_wait_selftest(s2v_ctx* ctx, cudaStream_t st);
+// whole classifier up to the pooled embeddings for batches of graphs of at most S2V_TILE_NODES nodes (d = 128, tags)
+constexpr int S2V_TILE_NODES = 128;
+size_t s2v_graph_tiles_plan_bytes(int64_t num_graphs);
+int s2v_launch_graph_tiles(s2v_ctx* ctx, cudaStream_t st, int64_t G, const int32_t* row_ptr, const int32_t* col_idx,
+                           const float* val, const int32_t* graph_ptr, const int32_t* tags, int num_tags,
+                           const float* W_in, const float* W, int levels, int pool_average, void* plan, float* Y,
+                           float* embed_out);
 int s2v_launch_level(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int64_t n_src, int d, const void* row_ptr,
                      bool rp64, const int32_t* col_idx, const float* val, const float* H, const float* W,
-                     const float* X, const float* table, const int32_t* x_index, float* out);
+                     const float* X, const float* table, const int32_t* x_index, int n_table, float* out);

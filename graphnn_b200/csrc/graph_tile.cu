@@ -1,0 +1,613 @@
+// The whole structure2vec classifier up to the pooled graph embeddings in ONE kernel, for batches of
+// small graphs (every graph at most 128 nodes, one-hot node tags, latent dimension 128):
+//
+//     H0   = ReLU(W_in[tag])                      Hl+1 = ReLU((A * Hl) * W + W_in[tag]),  l = 0..L-1
+//     Y[g] = sum of HL over the nodes of graph g  (or their mean)
+//
+// i.e. examples/graph_classification/src/kernel_mean_field.cpp:31-44 of the reference.  A batch of
+// small graphs is block diagonal, so a tile of whole graphs never needs a row of another tile: the
+// node embeddings of a tile stay in shared memory across all L levels and only the pooled [G x d]
+// matrix goes to HBM (the per-level kernels write and re-read [N x d] every level).
+//
+// Tiles.  A planning kernel packs consecutive graphs greedily into tiles of at most 128 nodes (and at
+// most 128 graphs) and writes the list of (first graph, end graph) pairs; a graph larger than a tile is
+// reported in the status word and truncated.
+//
+// One persistent 544-thread CTA per SM: sixteen worker warps + one MMA-issue warp.
+//   * The dense stage runs TRANSPOSED on the tensor cores: out^T [d x nodes] = W^T [d x d] * S^T, so the
+//     constant operand W^T (TF32 head and tail) is loaded ONCE per CTA into tensor memory as the A
+//     operand, and the per-tile operand S = A * H (neighbour sums, [nodes x d], row-major) is exactly the
+//     K-major B operand the tensor core reads from shared memory: no transposition anywhere.
+//   * Gather: eight lanes own one node row and 32 feature columns (one 128-byte line) of it; they add
+//     the neighbour rows from the shared H tile in CSR order, split the sum into TF32 head and tail and
+//     store both into an operand buffer in the 128-byte-swizzle layout (head rows 0..127, tail rows
+//     128..255).  A level is four such chunks of 32 features through two operand buffers.
+//   * MMAs per chunk and K step: W_hi * [S_hi ; S_lo] as ONE instruction with N = 256 (columns 0..127 of
+//     the accumulator collect the large term, 128..255 the small term hi*lo) and W_lo * S_hi with
+//     N = 128 onto columns 128..255.  32 instructions per level instead of 48, and the small terms never
+//     meet the large one before the epilogue adds the two halves in fp32.
+//   * Epilogue: thread = output feature (tensor-memory lane), 32 node columns per worker:
+//     tcgen05.ld, large + small + W_in[tag], ReLU, back into the H tile (conflict-free 128-byte rows).
+//   * After a tile's last level the worker warps sum its graphs in node order and write Y.
+// A CTA keeps TWO tiles resident (two "streams", each with its own H tile and CSR slice) and the workers
+// run one software-pipelined program over the alternating sequence of their levels
+//     A.0  B.0  A.1  B.1 ...         step k:  gather chunks 0,1 of level-job k
+//                                             drain the accumulator of level-job k-1, its epilogue
+//                                             gather chunks 2,3 of level-job k
+//                                             (last level of a tile: pooling, then the stream's next tile)
+// so that the MMAs of one tile run while the other tile's epilogue and gathers are done: the tensor pipe,
+// not the serial chain gather -> MMA -> epilogue of one tile, bounds the time.  The single accumulator
+// (256 of the 512 tensor-memory columns; the other 256 hold W^T) is handed over by an "accumulator read"
+// barrier as soon as its values are in registers.
+// Every wait is an mbarrier try_wait with a poll limit; on a time-out the kernel records
+// S2V_ERR_DEVICE_TIMEOUT, raises a CTA-wide flag, frees its tensor memory and returns.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace
+{
+
+constexpr int GT_NODES = 128;                    // node rows per tile
+constexpr int GT_D = 128;                        // latent dimension = MMA M
+constexpr int GT_WORKERS = 16;
+constexpr int GT_THREADS = (GT_WORKERS + 1) * 32;
+constexpr int GT_CHUNKS = 4;                     // K chunks of 32 features (one swizzle line per node row)
+constexpr int GT_SBUF = 2;                       // operand buffers
+constexpr int GT_LC_CAP = 1536;                  // non-zeros of a tile cached in shared memory
+constexpr size_t GT_S_BYTES = 256 * 128;         // one operand buffer: 128 head rows + 128 tail rows, 128 bytes each
+constexpr size_t GT_H_BYTES = sizeof(float) * GT_NODES * GT_D;
+// per-stream arrays
+constexpr size_t GT_ST_LVAL = 0;
+constexpr size_t GT_ST_REC = GT_ST_LVAL + sizeof(float) * GT_LC_CAP;     // uint4 per row: neighbour offsets, degree, first non-zero
+constexpr size_t GT_ST_LRP = GT_ST_REC + 16 * GT_NODES;
+constexpr size_t GT_ST_TAGS = GT_ST_LRP + sizeof(int) * 132;
+constexpr size_t GT_ST_GOFF = GT_ST_TAGS + sizeof(int) * GT_NODES;
+constexpr size_t GT_ST_INFO = GT_ST_GOFF + sizeof(int) * 132;           // 8 ints describing the tile
+constexpr size_t GT_ST_LCOL = GT_ST_INFO + 32;                           // local column indices are bytes
+constexpr size_t GT_ST_BYTES = (GT_ST_LCOL + GT_LC_CAP + 15) / 16 * 16;
+constexpr size_t GT_OFF_S = 0;
+constexpr size_t GT_OFF_H = GT_OFF_S + GT_SBUF * GT_S_BYTES;
+constexpr size_t GT_OFF_ST = GT_OFF_H + 2 * GT_H_BYTES;
+constexpr size_t GT_OFF_BAR = GT_OFF_ST + 2 * GT_ST_BYTES;
+constexpr size_t GT_SMEM_BYTES = GT_OFF_BAR + 128 + 1024;                 // + barriers/flags + alignment slack
+static_assert(GT_SMEM_BYTES <= 227 * 1024, "shared memory map exceeds the 227 KB a CTA may use");
+// tensor memory columns
+constexpr uint32_t GT_TM_WHI = 0, GT_TM_WLO = 128, GT_TM_ACC = 256;
+// instruction descriptors: D = f32, A = B = tf32, both K-major, M = 128, N = 256 / 128
+constexpr uint32_t GT_IDESC_BASE = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(128 >> 4) << 24);
+constexpr uint32_t GT_IDESC_N256 = GT_IDESC_BASE | ((uint32_t)(256 >> 3) << 17);
+constexpr uint32_t GT_IDESC_N128 = GT_IDESC_BASE | ((uint32_t)(128 >> 3) << 17);
+
+// mbarriers
+enum {
+    GB_FULL0 = 0,               // +b : operand buffer b holds a chunk (sixteen worker arrivals)
+    GB_EMPTY0 = GT_SBUF,        // +b : the MMAs that read operand buffer b are complete (tcgen05.commit)
+    GB_ACC_FULL = 2 * GT_SBUF,  // the MMAs of a level-job are complete
+    GB_ACC_READ,                // the accumulator is in the workers' registers (sixteen arrivals)
+    GB_WSYNC,                   // worker-wide barrier
+    GB_COUNT
+};
+
+// ------------------------------------------------------------------ tile planning
+constexpr int PLAN_SEG = 8192;      // graphs handled per pass of the single planning CTA
+constexpr int PLAN_THREADS = 1024;
+constexpr size_t PLAN_SMEM = sizeof(int) * 3 * (PLAN_SEG + 1) + (PLAN_SEG + 1) + 64;
+
+// Greedy packing of consecutive graphs into tiles, in parallel.  For every graph i the end of the tile that
+// would START at i is found by binary search in the offsets (next[i]); the tile starts actually used are
+// the orbit of graph 0 under `next`, marked by pointer doubling (after k rounds every start within 2^k
+// tiles of the front is marked); a block-wide scan compacts them.  Passes of PLAN_SEG graphs; a tile never
+// spans two passes.
+__global__ void __launch_bounds__(PLAN_THREADS) gt_plan_kernel(int64_t G, const int32_t* __restrict__ graph_ptr,
+                                                              int2* __restrict__ tile_range, int* __restrict__ tile_count,
+                                                              s2v_device_status* status)
+{
+    extern __shared__ int plan_sm[];
+    int* gp = plan_sm;
+    int* jmp_a = gp + PLAN_SEG + 1;
+    int* jmp_b = jmp_a + PLAN_SEG + 1;
+    unsigned char* mark = reinterpret_cast<unsigned char*>(jmp_b + PLAN_SEG + 1);
+    __shared__ int warp_sum[32];
+    __shared__ int seg_total;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int tiles_done = 0;
+    for (int64_t g0 = 0; g0 < G; g0 += PLAN_SEG) {
+        const int n = (int)((G - g0) < PLAN_SEG ? (G - g0) : PLAN_SEG);
+        for (int i = tid; i <= n; i += PLAN_THREADS) gp[i] = graph_ptr[g0 + i];
+        __syncthreads();
+        // end of the tile that starts at graph i: the largest j <= min(n, i + 128) with gp[j] - gp[i] <= 128
+        auto next_of = [&](int i) -> int {
+            if (i >= n) return n;
+            int lo = i, hi = (n < i + GT_NODES) ? n : i + GT_NODES;
+            const int lim = gp[i] + GT_NODES;
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (gp[mid] <= lim && gp[mid] >= gp[i]) lo = mid; else hi = mid - 1;
+            }
+            return lo;
+        };
+        for (int i = tid; i <= n; i += PLAN_THREADS) {
+            int nx = next_of(i);
+            if (i < n && nx == i) {      // graph i alone does not fit a tile: reported, and truncated by the consumer
+                nx = i + 1;
+                status->code = S2V_ERR_UNSUPPORTED;
+                status->where = 4;
+            }
+            jmp_a[i] = nx;
+            mark[i] = (i == 0) ? 1 : 0;
+        }
+        __syncthreads();
+        int* cur = jmp_a;
+        int* nxt = jmp_b;
+        for (int span = 1; span <= n; span <<= 1) {
+            for (int i = tid; i <= n; i += PLAN_THREADS) {
+                if (mark[i]) mark[cur[i]] = 1;          // only ever writes 1 to tile starts: the race is benign
+                nxt[i] = cur[cur[i]];
+            }
+            __syncthreads();
+            int* t = cur; cur = nxt; nxt = t;
+        }
+        // compaction: thread t owns graphs [t*per, (t+1)*per)
+        const int per = (n + PLAN_THREADS - 1) / PLAN_THREADS;
+        const int b = tid * per < n ? tid * per : n;
+        const int e = (b + per) < n ? (b + per) : n;
+        int cnt = 0;
+        for (int i = b; i < e; ++i) cnt += mark[i];
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        if (lane == 31) warp_sum[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = warp_sum[lane];
+            int wi = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, wi, o);
+                if (lane >= o) wi += v;
+            }
+            warp_sum[lane] = wi - w;    // exclusive
+            if (lane == 31) seg_total = wi;
+        }
+        __syncthreads();
+        int k = tiles_done + warp_sum[warp] + incl - cnt;
+        for (int i = b; i < e; ++i)
+            if (mark[i]) {
+                int nx = next_of(i);
+                if (nx == i) nx = i + 1;
+                tile_range[k++] = make_int2((int)(g0 + i), (int)(g0 + nx));
+            }
+        tiles_done += seg_total;
+        __syncthreads();   // shared arrays are reused by the next pass
+    }
+    if (tid == 0) *tile_count = tiles_done;
+}
+
+// ------------------------------------------------------------------ the tile kernel
+__device__ __forceinline__ float4 relu4(float4 v)
+{
+    return make_float4(relu_ref(v.x), relu_ref(v.y), relu_ref(v.z), relu_ref(v.w));
+}
+
+template <bool HAS_VAL>
+__global__ void __launch_bounds__(GT_THREADS, 1)
+s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict__ tile_count_p,
+                      const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ col_idx,
+                      const float* __restrict__ val, const int32_t* __restrict__ graph_ptr,
+                      const int32_t* __restrict__ tags, int num_tags, const float* __restrict__ W_in,
+                      const float* __restrict__ W, int levels, int pool_average, float* __restrict__ Y,
+                      float* __restrict__ embed_out, s2v_device_status* status)
+{
+    const int num_tiles = *tile_count_p;
+    if ((int)blockIdx.x >= num_tiles) return;   // the whole CTA leaves before it owns anything
+    extern __shared__ unsigned char gt_smem_raw[];
+    unsigned char* smem = gt_smem_raw + ((1024u - (smem_u32(gt_smem_raw) & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GT_OFF_BAR);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + GT_OFF_BAR + 8 * GB_COUNT);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + GT_OFF_BAR + 8 * GB_COUNT + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    const uint32_t s_addr0 = smem_u32(smem + GT_OFF_S);
+
+    if (threadIdx.x == 0) {
+        for (int b = 0; b < GT_SBUF; ++b) {
+            tc_mbar_init(bar(GB_FULL0 + b), GT_WORKERS);
+            tc_mbar_init(bar(GB_EMPTY0 + b), 1);
+        }
+        tc_mbar_init(bar(GB_ACC_FULL), 1);
+        tc_mbar_init(bar(GB_ACC_READ), GT_WORKERS);
+        tc_mbar_init(bar(GB_WSYNC), GT_WORKERS);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int q = warp & 3, j = (warp >> 2) & 3;            // tensor-memory lane quarter, slot within it
+    const uint32_t lane_base = (uint32_t)(32 * q) << 16;
+    if (warp < GT_WORKERS) {
+        // W^T into tensor memory: lane m = output feature, column k = input feature; A[m][k] = W[k][m].
+        // Worker (q, j): features 32q..32q+31, k in [32j, 32j+32).  Loads are coalesced across the lanes.
+        const int m = 32 * q + lane;
+        float wv[32];
+#pragma unroll
+        for (int kk = 0; kk < 32; ++kk) wv[kk] = __ldg(W + (int64_t)(32 * j + kk) * GT_D + m);
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            uint32_t hi[8], lo[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                hi[c] = tf32_rn(wv[8 * h + c]);
+                lo[c] = tf32_rn(wv[8 * h + c] - __uint_as_float(hi[c]));
+            }
+            tc_st_cols8(tmem_base + lane_base + GT_TM_WHI + (uint32_t)(32 * j + 8 * h), hi);
+            tc_st_cols8(tmem_base + lane_base + GT_TM_WLO + (uint32_t)(32 * j + 8 * h), lo);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    // This CTA's tiles blockIdx.x + i * gridDim.x, i = 0 .. my_tiles-1, go alternately to stream 0 and stream 1.
+    const int my_tiles = (num_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1;
+    const int n_lj0 = ((my_tiles + 1) >> 1) * levels, n_lj1 = (my_tiles >> 1) * levels;   // level-jobs per stream
+    const int n_steps = 2 * (n_lj0 > n_lj1 ? n_lj0 : n_lj1);
+
+    if (warp < GT_WORKERS) {
+        // =========================== worker warps ===========================
+        const int tix = threadIdx.x;                 // 0..511
+        const int g4 = lane >> 3, sl = lane & 7;     // gather: row within a pass of four, 16-byte piece of the 128-byte line
+        const float4* __restrict__ Win4 = reinterpret_cast<const float4*>(W_in);
+        uint32_t ws_phase = 0;                       // completed phases of the worker-wide barrier
+        uint32_t jobs = 0;                           // chunk jobs produced so far (operand buffer = jobs & 1)
+        uint32_t drained = 0;                        // level-jobs whose accumulator has been read
+        bool alive = true;
+        auto stream_base = [&](int s) { return smem + GT_OFF_ST + (size_t)s * GT_ST_BYTES; };
+        auto stream_h = [&](int s) { return smem + GT_OFF_H + (size_t)s * GT_H_BYTES; };
+        // arrive at the worker-wide barrier and wait for the other fifteen warps (bounded)
+        auto wsync = [&](int site) -> bool {
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive(bar(GB_WSYNC));
+            const bool ok = tc_wait(bar(GB_WSYNC), ws_phase & 1u, abort_flag, status, site);
+            ++ws_phase;
+            return ok;
+        };
+
+        // ---- a tile enters stream s: its CSR slice, tags, graph offsets, H0, and the per-row gather records
+        auto prologue = [&](int s, int tile) -> bool {
+            unsigned char* sb = stream_base(s);
+            float* lval = reinterpret_cast<float*>(sb + GT_ST_LVAL);
+            uint4* rec = reinterpret_cast<uint4*>(sb + GT_ST_REC);
+            int* lrp = reinterpret_cast<int*>(sb + GT_ST_LRP);
+            int* tag_s = reinterpret_cast<int*>(sb + GT_ST_TAGS);
+            int* goff = reinterpret_cast<int*>(sb + GT_ST_GOFF);
+            int* info = reinterpret_cast<int*>(sb + GT_ST_INFO);
+            unsigned char* lcol = sb + GT_ST_LCOL;
+            float4* H4s = reinterpret_cast<float4*>(stream_h(s));
+            const int2 tr = tile_range[tile];
+            const int node0 = __ldg(graph_ptr + tr.x);
+            int nrows = __ldg(graph_ptr + tr.y) - node0;
+            if (nrows > GT_NODES) nrows = GT_NODES;   // an oversized graph was reported by the planner; stay inside the tile
+            if (nrows < 0) nrows = 0;
+            int ngr = tr.y - tr.x;
+            if (ngr > GT_NODES) ngr = GT_NODES;
+            const int32_t base = __ldg(row_ptr + node0);
+            int nnz = __ldg(row_ptr + node0 + nrows) - base;
+            if (nnz < 0) nnz = 0;
+            const bool cached = nnz <= GT_LC_CAP;      // uniform over the CTA
+            if (tix == 0) {
+                info[0] = node0; info[1] = nrows; info[2] = ngr; info[3] = tr.x; info[4] = base; info[5] = nnz;
+            }
+            if (tix <= GT_NODES) {
+                int v = __ldg(row_ptr + node0 + (tix < nrows ? tix : nrows)) - base;
+                lrp[tix] = v < 0 ? 0 : (v > nnz ? nnz : v);
+            }
+            if (tix < GT_NODES) tag_s[tix] = tix < nrows ? tc_table_row(__ldg(tags + node0 + tix), num_tags, status) : 0;
+            if (tix <= ngr) {
+                int v = __ldg(graph_ptr + tr.x + tix) - node0;
+                goff[tix] = v < 0 ? 0 : (v > nrows ? nrows : v);
+            }
+            if (cached) {
+                for (int e = tix; e < nnz; e += GT_WORKERS * 32) {
+                    int c = __ldg(col_idx + base + e) - node0;
+                    if ((unsigned)c >= (unsigned)nrows) {   // an edge that leaves the tile: not a batch of separate graphs
+                        status->code = S2V_ERR_BAD_CSR;
+                        status->where = 5;
+                        c = 0;
+                    }
+                    lcol[e] = (unsigned char)c;
+                    if (HAS_VAL) lval[e] = __ldg(val + base + e);
+                }
+            }
+#pragma unroll
+            for (int rr = 0; rr < 8; ++rr) {
+                const int r = 8 * warp + rr;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (r < nrows) v = relu4(__ldg(Win4 + (int64_t)tc_table_row(__ldg(tags + node0 + r), num_tags, status) * 32 + lane));
+                H4s[r * 32 + lane] = v;
+            }
+            if (!wsync(30)) return false;
+            // gather record of row r: byte offsets (row * 512) of its first four neighbours, its degree, its first non-zero
+            if (tix < GT_NODES) {
+                const int beg = lrp[tix], deg = lrp[tix + 1] - beg;
+                uint32_t off[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (u < deg) {
+                        int c;
+                        if (cached) c = lcol[beg + u];
+                        else {
+                            c = __ldg(col_idx + base + beg + u) - node0;
+                            if ((unsigned)c >= (unsigned)nrows) {
+                                status->code = S2V_ERR_BAD_CSR;
+                                status->where = 5;
+                                c = 0;
+                            }
+                        }
+                        off[u] = (uint32_t)c * 512u;
+                    }
+                rec[tix] = make_uint4(off[0] | (off[1] << 16), off[2] | (off[3] << 16), (uint32_t)deg, (uint32_t)beg);
+            }
+            return wsync(35);
+        };
+
+        // ---- one chunk of S = A * H of stream s's tile: gather, split, store as MMA operand
+        auto gather_chunk = [&](int s, int c) -> bool {
+            const uint32_t b = jobs & 1u;
+            if (jobs >= (uint32_t)GT_SBUF &&
+                !tc_wait(bar(GB_EMPTY0 + b), ((jobs >> 1) - 1u) & 1u, abort_flag, status, 36))
+                return false;
+            unsigned char* sb = stream_base(s);
+            const uint4* rec = reinterpret_cast<const uint4*>(sb + GT_ST_REC);
+            const unsigned char* hb = stream_h(s) + (size_t)c * 128 + (size_t)sl * 16;
+            unsigned char* sbuf = smem + GT_OFF_S + (size_t)b * GT_S_BYTES;
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                const int r = 8 * warp + 4 * p + g4;
+                const uint4 rc = rec[r];
+                const int deg = (int)rc.z;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 v[4];
+                const uint32_t off[4] = {rc.x & 0xffffu, rc.x >> 16, rc.y & 0xffffu, rc.y >> 16};
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (u < deg) v[u] = *reinterpret_cast<const float4*>(hb + off[u]);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (u < deg) {   // adds in CSR order
+                        if (HAS_VAL) {
+                            const int* info = reinterpret_cast<const int*>(sb + GT_ST_INFO);
+                            const float a = (info[5] <= GT_LC_CAP) ? reinterpret_cast<const float*>(sb + GT_ST_LVAL)[rc.w + u]
+                                                                   : __ldg(val + info[4] + rc.w + u);
+                            acc.x = fmaf(a, v[u].x, acc.x); acc.y = fmaf(a, v[u].y, acc.y);
+                            acc.z = fmaf(a, v[u].z, acc.z); acc.w = fmaf(a, v[u].w, acc.w);
+                        } else {
+                            acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
+                        }
+                    }
+                if (deg > 4) {   // longer rows
+                    const int* info = reinterpret_cast<const int*>(sb + GT_ST_INFO);
+                    const int node0 = info[0], nrows = info[1], base = info[4];
+                    const bool cached = info[5] <= GT_LC_CAP;
+                    const unsigned char* lcol = sb + GT_ST_LCOL;
+                    for (int t = 4; t < deg; ++t) {
+                        int n;
+                        if (cached) n = lcol[rc.w + t];
+                        else {
+                            n = __ldg(col_idx + base + rc.w + t) - node0;
+                            if ((unsigned)n >= (unsigned)nrows) n = 0;
+                        }
+                        const float4 vv = *reinterpret_cast<const float4*>(hb + (size_t)n * 512);
+                        if (HAS_VAL) {
+                            const float a = cached ? reinterpret_cast<const float*>(sb + GT_ST_LVAL)[rc.w + t] : __ldg(val + base + rc.w + t);
+                            acc.x = fmaf(a, vv.x, acc.x); acc.y = fmaf(a, vv.y, acc.y);
+                            acc.z = fmaf(a, vv.z, acc.z); acc.w = fmaf(a, vv.w, acc.w);
+                        } else {
+                            acc.x += vv.x; acc.y += vv.y; acc.z += vv.z; acc.w += vv.w;
+                        }
+                    }
+                }
+                uint4 hi, lo;
+                tc_split(acc.x, hi.x, lo.x);
+                tc_split(acc.y, hi.y, lo.y);
+                tc_split(acc.z, hi.z, lo.z);
+                tc_split(acc.w, hi.w, lo.w);
+                // row r of the K-major 128-byte-swizzle layout: 16-byte piece sl sits at sl ^ (r & 7)
+                unsigned char* dst = sbuf + (size_t)r * 128 + (size_t)((sl ^ (r & 7)) * 16);
+                *reinterpret_cast<uint4*>(dst) = hi;
+                *reinterpret_cast<uint4*>(dst + 128 * 128) = lo;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // my stores -> visible to the tensor core
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive(bar(GB_FULL0 + b));
+            ++jobs;
+            return true;
+        };
+
+        // ---- accumulator of the oldest open level-job (stream s) -> registers -> + X, ReLU -> the stream's H tile
+        auto drain_epilogue = [&](int s) -> bool {
+            unsigned char* sb = stream_base(s);
+            const int* tag_s = reinterpret_cast<const int*>(sb + GT_ST_TAGS);
+            float* Hs = reinterpret_cast<float*>(stream_h(s));
+            float xv[32];   // feature = my lane, nodes 32j .. 32j+31
+#pragma unroll
+            for (int i = 0; i < 32; ++i) xv[i] = __ldg(W_in + (int64_t)tag_s[32 * j + i] * GT_D + 32 * q + lane);
+            if (!tc_wait(bar(GB_ACC_FULL), drained & 1u, abort_flag, status, 31)) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t acc_addr = tmem_base + lane_base + GT_TM_ACC + (uint32_t)(32 * j);
+            float z[32];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t big[16], sml[16];
+                tc_ld_cols16(acc_addr + (uint32_t)(16 * h), big);
+                tc_ld_cols16(acc_addr + 128u + (uint32_t)(16 * h), sml);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 16; ++i) z[16 * h + i] = __uint_as_float(big[i]) + __uint_as_float(sml[i]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive(bar(GB_ACC_READ));   // the next level-job's MMAs may overwrite the accumulator
+            ++drained;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) Hs[(32 * j + i) * GT_D + 32 * q + lane] = relu_ref(z[i] + xv[i]);
+            return true;
+        };
+
+        // ---- graph sums of stream s's finished tile (node order), optional node embeddings
+        auto pool = [&](int s) {
+            unsigned char* sb = stream_base(s);
+            const int* goff = reinterpret_cast<const int*>(sb + GT_ST_GOFF);
+            const int* info = reinterpret_cast<const int*>(sb + GT_ST_INFO);
+            const float4* H4s = reinterpret_cast<const float4*>(stream_h(s));
+            const int node0 = info[0], nrows = info[1], ngr = info[2], g0 = info[3];
+            for (int k = warp; k < ngr; k += GT_WORKERS) {
+                const int nb = goff[k], ne = goff[k + 1];
+                const float inv = pool_average ? (float)(1.0 / (double)(ne - nb)) : 1.0f;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int n = nb; n < ne; ++n) {
+                    const float4 v = H4s[n * 32 + lane];
+                    if (pool_average) {
+                        acc.x = fmaf(inv, v.x, acc.x); acc.y = fmaf(inv, v.y, acc.y);
+                        acc.z = fmaf(inv, v.z, acc.z); acc.w = fmaf(inv, v.w, acc.w);
+                    } else {
+                        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                    }
+                }
+                reinterpret_cast<float4*>(Y)[(int64_t)(g0 + k) * 32 + lane] = acc;
+            }
+            if (embed_out) {
+#pragma unroll
+                for (int rr = 0; rr < 8; ++rr) {
+                    const int r = 8 * warp + rr;
+                    if (r < nrows) reinterpret_cast<float4*>(embed_out)[(int64_t)(node0 + r) * 32 + lane] = H4s[r * 32 + lane];
+                }
+            }
+        };
+
+        // the first tile of each stream
+        alive = prologue(0, (int)blockIdx.x);
+        if (alive && my_tiles > 1) alive = prologue(1, (int)blockIdx.x + (int)gridDim.x);
+        int pending = -1;                      // stream whose level-job awaits its epilogue
+        int lv_of[2] = {0, 0};                 // level the stream's tile is at
+        int tiles_done[2] = {0, 0};            // tiles the stream has finished
+        // step k: level-job (k >> 1) of stream (k & 1), if that stream still has one
+        for (int k = 0; k <= n_steps && alive; ++k) {
+            const int s = k & 1;
+            const bool have = (k >> 1) < (s == 0 ? n_lj0 : n_lj1);
+            if (have) {
+                if (!gather_chunk(s, 0) || !gather_chunk(s, 1)) { alive = false; break; }
+            }
+            bool tile_finished = false;
+            if (pending >= 0) {
+                if (!drain_epilogue(pending)) { alive = false; break; }
+                tile_finished = ++lv_of[pending] == levels;
+            }
+            if (have) {
+                if (!gather_chunk(s, 2) || !gather_chunk(s, 3)) { alive = false; break; }
+            }
+            if (!wsync(32)) { alive = false; break; }           // H of the drained level complete for every warp
+            if (tile_finished) {
+                pool(pending);
+                lv_of[pending] = 0;
+                const int next_i = 2 * (++tiles_done[pending]) + pending;   // the stream's next tile among this CTA's
+                if (!wsync(33)) { alive = false; break; }       // pooling has read H before the next tile overwrites it
+                if (next_i < my_tiles && !prologue(pending, (int)blockIdx.x + next_i * (int)gridDim.x)) { alive = false; break; }
+            }
+            pending = have ? s : -1;
+        }
+    } else {
+        // =========================== MMA-issue warp ===========================
+        uint32_t jobs = 0, lj = 0;
+        bool alive = true;
+        for (int k = 0; k < n_steps && alive; ++k) {
+            if ((k >> 1) >= ((k & 1) == 0 ? n_lj0 : n_lj1)) continue;
+#pragma unroll 1
+            for (int c = 0; c < GT_CHUNKS; ++c) {
+                const uint32_t b = jobs & 1u;
+                if (!tc_wait(bar(GB_FULL0 + b), (jobs >> 1) & 1u, abort_flag, status, 34)) { alive = false; break; }
+                // the previous level-job's accumulator must be in the workers' registers before it is overwritten
+                if (c == 0 && lj > 0 && !tc_wait(bar(GB_ACC_READ), (lj - 1u) & 1u, abort_flag, status, 37)) { alive = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (lane == 0) {
+                    const uint32_t sb = s_addr0 + b * (uint32_t)GT_S_BYTES;
+#pragma unroll
+                    for (int s = 0; s < 4; ++s) {
+                        const uint32_t ks = (uint32_t)(4 * c + s);
+                        const uint64_t bd = tc_b_desc(sb + 32u * (uint32_t)s);
+                        // W_hi * [S_hi ; S_lo]: large term -> columns 0..127, hi*lo -> columns 128..255
+                        tc_mma(tmem_base + GT_TM_ACC, tmem_base + GT_TM_WHI + 8u * ks, bd, GT_IDESC_N256, ks != 0u);
+                        // W_lo * S_hi onto the small-term half
+                        tc_mma(tmem_base + GT_TM_ACC + 128u, tmem_base + GT_TM_WLO + 8u * ks, bd, GT_IDESC_N128, 1u);
+                    }
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar(GB_EMPTY0 + b))
+                                 : "memory");
+                    if (c == GT_CHUNKS - 1)
+                        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar(GB_ACC_FULL))
+                                     : "memory");
+                }
+                __syncwarp();
+                ++jobs;
+            }
+            ++lj;
+        }
+    }
+
+    // ---- teardown: everyone is done with tensor memory before it is released
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+}
+
+}  // namespace
+
+size_t s2v_graph_tiles_plan_bytes(int64_t num_graphs)
+{
+    return sizeof(int2) * (size_t)(num_graphs > 0 ? num_graphs : 0) + 256;
+}
+
+// Plans the tiles and runs the tile kernel: Y [G x 128] = pooled last-level embeddings.  `plan` is device
+// scratch of s2v_graph_tiles_plan_bytes(G) bytes, 256-byte aligned.
+int s2v_launch_graph_tiles(s2v_ctx* ctx, cudaStream_t st, int64_t G, const int32_t* row_ptr, const int32_t* col_idx,
+                           const float* val, const int32_t* graph_ptr, const int32_t* tags, int num_tags,
+                           const float* W_in, const float* W, int levels, int pool_average, void* plan, float* Y,
+                           float* embed_out)
+{
+    if (GT_SMEM_BYTES > ctx->smem_optin || PLAN_SMEM > ctx->smem_optin) return S2V_ERR_UNSUPPORTED;
+    int* tile_count = static_cast<int*>(plan);
+    int2* tile_range = reinterpret_cast<int2*>(static_cast<unsigned char*>(plan) + 256);
+    S2V_CUDA_OK(ctx, cudaFuncSetAttribute(gt_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PLAN_SMEM));
+    gt_plan_kernel<<<1, PLAN_THREADS, PLAN_SMEM, st>>>(G, graph_ptr, tile_range, tile_count, ctx->dstatus_dev);
+    S2V_CHECK_LAUNCH(ctx, "gt_plan_kernel");
+    int64_t blocks = G < ctx->sm_count ? G : ctx->sm_count;   // at most one tile per graph; idle CTAs leave at once
+    if (blocks < 1) blocks = 1;
+    if (val) {
+        auto kern = s2v_graph_tile_kernel<true>;
+        S2V_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM_BYTES));
+        kern<<<(unsigned)blocks, GT_THREADS, GT_SMEM_BYTES, st>>>(tile_range, tile_count, row_ptr, col_idx, val, graph_ptr, tags,
+                                                                  num_tags, W_in, W, levels, pool_average, Y, embed_out,
+                                                                  ctx->dstatus_dev);
+    } else {
+        auto kern = s2v_graph_tile_kernel<false>;
+        S2V_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM_BYTES));
+        kern<<<(unsigned)blocks, GT_THREADS, GT_SMEM_BYTES, st>>>(tile_range, tile_count, row_ptr, col_idx, val, graph_ptr, tags,
+                                                                  num_tags, W_in, W, levels, pool_average, Y, embed_out,
+                                                                  ctx->dstatus_dev);
+    }
+    S2V_CHECK_LAUNCH(ctx, "s2v_graph_tile_kernel");
+    return S2V_OK;
+}

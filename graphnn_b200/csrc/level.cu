@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(LevelCfg<D>::WARPS * 32, LevelCfg<D>::MIN_BLOC
 s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_ptr,
                  const int32_t* __restrict__ col_idx, const float* __restrict__ val, const float* __restrict__ H,
                  const float* __restrict__ W, const float* __restrict__ X, const int32_t* __restrict__ x_index,
-                 float* __restrict__ out, s2v_device_status* status)
+                 int n_table, float* __restrict__ out, s2v_device_status* status)
 {
     constexpr int WARPS = LevelCfg<D>::WARPS;
     constexpr int U = LevelCfg<D>::U;
@@ -344,7 +344,16 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
                 const float4 o = *reinterpret_cast<const float4*>(S + lr * S_STRIDE + sl * 4);
                 float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (XMODE == 1) x = ld_stream_f4(reinterpret_cast<const float4*>(X) + row * LPR + sl);
-                if (XMODE == 2) x = ld_nc_f4(reinterpret_cast<const float4*>(X) + (int64_t)__ldg(x_index + row) * LPR + sl);
+                if (XMODE == 2) {
+                    // the index is caller data (a node tag): outside [0, n_table) it is recorded and row 0 is used
+                    int xi = __ldg(x_index + row);
+                    if ((unsigned)xi >= (unsigned)n_table) {
+                        status->code = S2V_ERR_INVALID_ARG;
+                        status->where = 3;
+                        xi = 0;
+                    }
+                    x = ld_nc_f4(reinterpret_cast<const float4*>(X) + (int64_t)xi * LPR + sl);
+                }
                 float4 r;
                 r.x = relu_ref(o.x + x.x);
                 r.y = relu_ref(o.y + x.y);
@@ -359,7 +368,8 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
 
 template <int D, typename RpT, bool HAS_VAL, int XMODE>
 int launch_one(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const RpT* row_ptr, const int32_t* col_idx,
-               const float* val, const float* H, const float* W, const float* X, const int32_t* x_index, float* out)
+               const float* val, const float* H, const float* W, const float* X, const int32_t* x_index, int n_table,
+               float* out)
 {
     constexpr int WARPS = LevelCfg<D>::WARPS;
     auto kern = s2v_level_kernel<D, RpT, HAS_VAL, XMODE>;
@@ -374,7 +384,7 @@ int launch_one(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const RpT* row_ptr
     const int64_t persistent = (int64_t)ctx->sm_count * resident;
     if (blocks > persistent) blocks = persistent;
     if (blocks < 1) blocks = 1;
-    kern<<<(unsigned)blocks, WARPS * 32, smem, st>>>(n_rows, num_tiles, row_ptr, col_idx, val, H, W, X, x_index, out,
+    kern<<<(unsigned)blocks, WARPS * 32, smem, st>>>(n_rows, num_tiles, row_ptr, col_idx, val, H, W, X, x_index, n_table, out,
                                                       ctx->dstatus_dev);
     S2V_CHECK_LAUNCH(ctx, "s2v_level_kernel");
     return S2V_OK;
@@ -382,11 +392,12 @@ int launch_one(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const RpT* row_ptr
 
 template <int D, typename RpT>
 int launch_d(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const RpT* rp, const int32_t* ci, const float* val,
-             const float* H, const float* W, const float* X, const float* table, const int32_t* x_index, float* out)
+             const float* H, const float* W, const float* X, const float* table, const int32_t* x_index, int n_table,
+             float* out)
 {
     const int xmode = table ? 2 : (X ? 1 : 0);
     const float* xa = table ? table : X;
-#define S2V_LVL(HV, XM) return launch_one<D, RpT, HV, XM>(ctx, st, n_rows, rp, ci, val, H, W, xa, x_index, out)
+#define S2V_LVL(HV, XM) return launch_one<D, RpT, HV, XM>(ctx, st, n_rows, rp, ci, val, H, W, xa, x_index, n_table, out)
     if (val) {
         if (xmode == 0) S2V_LVL(true, 0);
         if (xmode == 1) S2V_LVL(true, 1);
@@ -402,21 +413,21 @@ int launch_d(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const RpT* rp, const
 
 int s2v_launch_level(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int64_t n_src, int d, const void* row_ptr,
                      bool rp64, const int32_t* col_idx, const float* val, const float* H, const float* W,
-                     const float* X, const float* table, const int32_t* x_index, float* out)
+                     const float* X, const float* table, const int32_t* x_index, int n_table, float* out)
 {
     (void)n_src;
     if (n_rows == 0) return S2V_OK;
     if (!rp64 && s2v_use_tc(ctx, d, n_rows)) {
         const int rc = s2v_launch_level_tc(ctx, st, n_rows, d, (const int32_t*)row_ptr, col_idx, val, H, W, X, table,
-                                           x_index, out);
+                                           x_index, n_table, out);
         if (rc != S2V_ERR_UNSUPPORTED) return rc;
     }
 #define S2V_D(DD)                                                                                                  \
     case DD:                                                                                                       \
         return rp64 ? launch_d<DD, int64_t>(ctx, st, n_rows, (const int64_t*)row_ptr, col_idx, val, H, W, X, table, \
-                                            x_index, out)                                                          \
+                                            x_index, n_table, out)                                                 \
                     : launch_d<DD, int32_t>(ctx, st, n_rows, (const int32_t*)row_ptr, col_idx, val, H, W, X, table, \
-                                            x_index, out)
+                                            x_index, n_table, out)
     switch (d) {
         S2V_D(32);
         S2V_D(64);

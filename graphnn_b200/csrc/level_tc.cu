@@ -33,6 +33,7 @@
 // is bounded: on a time-out the kernel records S2V_ERR_DEVICE_TIMEOUT, raises a CTA-wide
 // abort flag, drains, frees its tensor memory and returns.
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace
 {
@@ -43,8 +44,6 @@ constexpr int TC_MW = 1;               // MMA-issue warp (one elected lane)
 constexpr int TC_THREADS = (TC_GW + TC_MW) * 32;
 constexpr int TC_ROWS_PER_GW = TC_TILE / TC_GW;   // 8
 constexpr int TC_U = 4;
-constexpr int TC_WAIT_LIMIT = 1 << 17;        // polls before a wait gives up (each may sleep up to TC_SUSPEND_NS)
-constexpr uint32_t TC_SUSPEND_NS = 10000;    // a waiting thread sleeps in the barrier unit instead of spinning through the issue port
 
 // Per-width configuration and shared memory map (offsets from a 1024-byte aligned base).
 template <int D>
@@ -78,120 +77,12 @@ enum {
     BAR_COUNT
 };
 
-__device__ __forceinline__ void tc_mbar_init(uint32_t bar, int count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void tc_mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool tc_mbar_try(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(TC_SUSPEND_NS)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false when the CTA is aborting (time-out here or elsewhere).
-__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, s2v_device_status* status,
-                                        int site)
-{
-    int spins = 0;
-    while (!tc_mbar_try(bar, parity)) {
-        if (*abort_flag) return false;
-        if (++spins > TC_WAIT_LIMIT) {
-            *abort_flag = 1;
-            status->code = S2V_ERR_DEVICE_TIMEOUT;
-            status->where = site;
-            return false;
-        }
-    }
-    return true;
-}
-// TF32 head rounded to nearest (add half an ulp of TF32 to the bit pattern, then cut: integer pipe only,
-// no conversion-unit instruction), tail = v - head (exact) cut to TF32.  head + tail differs from v by
-// less than 2^-23 |v|.
-__device__ __forceinline__ void tc_split(float v, uint32_t& head, uint32_t& tail)
-{
-    head = (__float_as_uint(v) + 0x1000u) & 0xffffe000u;
-    tail = __float_as_uint(v - __uint_as_float(head)) & 0xffffe000u;
-}
-// A 32-bit load that stays where it is written: the values fetched a tile ahead (row offsets, X row
-// indices) must be issued early, and a plain load may be moved down to its first use.
-__device__ __forceinline__ int32_t tc_ld_early(const int32_t* p)
-{
-    int32_t v;
-    asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ uint32_t tf32_rn(float v)
-{
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
-    return r;
-}
-// shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
-__device__ __forceinline__ uint64_t tc_b_desc(uint32_t smem_addr)
-{
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);   // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                        // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                        // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
-    return d;
-}
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
-        :
-        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// tcgen05.st / tcgen05.ld of this thread's tensor-memory lane, 8 or 16 consecutive 32-bit columns
-__device__ __forceinline__ void tc_st_cols8(uint32_t addr, const uint32_t* r)
-{
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(addr), "r"(r[0]), "r"(r[1]),
-                 "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
-}
-__device__ __forceinline__ void tc_ld_cols16(uint32_t addr, uint32_t* v)
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(addr)
-        : "memory");
-}
-
-// Optional cycle accounting per warp role (compile with -DS2V_TC_TRACE): block 0 prints, per
-// role, the cycles spent in each numbered section.  Compiled out by default.
-#ifdef S2V_TC_TRACE
-#define TC_TRACE_DECL() long long tr__[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long t0__ = clock64()
-#define TC_TRACE(slot) do { const long long t1__ = clock64(); tr__[slot] += t1__ - t0__; t0__ = t1__; } while (0)
-#define TC_TRACE_PRINT(role) do { if (blockIdx.x == 0 && lane == 0) printf("%s warp %d tiles %d: %lld %lld %lld %lld %lld %lld %lld %lld\n", role, warp, my_tiles, tr__[0], tr__[1], tr__[2], tr__[3], tr__[4], tr__[5], tr__[6], tr__[7]); } while (0)
-#else
-#define TC_TRACE_DECL() do {} while (0)
-#define TC_TRACE(slot) do {} while (0)
-#define TC_TRACE_PRINT(role) do {} while (0)
-#endif
-
 template <int D, bool HAS_VAL, int XMODE, bool HSRC_TABLE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict__ row_ptr,
                     const int32_t* __restrict__ col_idx, const float* __restrict__ val, const float* __restrict__ H,
                     const float* __restrict__ W, const float* __restrict__ X, const int32_t* __restrict__ x_index,
-                    float* __restrict__ out, s2v_device_status* status)
+                    int n_table, float* __restrict__ out, s2v_device_status* status)
 {
     extern __shared__ unsigned char tc_smem_raw[];
     // 1024-byte alignment as an OFFSET from the shared array: a pointer rebuilt from an integer would lose
@@ -300,7 +191,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
         // X row index of "my" epilogue row (lane = row within the quarter)
         auto load_xi = [&](int it) -> int {
             const int64_t mr = ((int64_t)blockIdx.x + (int64_t)it * gridDim.x) * TC_TILE + 32 * q + lane;
-            return (XMODE == 2 && it < my_tiles && mr < n_rows) ? tc_ld_early(x_index + mr) : 0;
+            return (XMODE == 2 && it < my_tiles && mr < n_rows) ? tc_table_row(tc_ld_early(x_index + mr), n_table, status) : 0;
         };
         constexpr int G = 32 / LPR;        // lane groups per warp (1 at d = 128, 2 at d = 64)
         constexpr int WSZ = IDX_CAP / G;   // index window per lane group: 64 entries
@@ -326,13 +217,12 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             for (int jj = 0; jj < IPL; ++jj)
             {
                 const int c_ = window_index(jj, __shfl_sync(0xffffffffu, rel, RPG), __shfl_sync(0xffffffffu, rel, TC_ROWS_PER_GW), base, 0);
-                idx_base[lane + 32 * jj] = HSRC_TABLE ? __ldg(x_index + c_) : c_;
+                idx_base[lane + 32 * jj] = HSRC_TABLE ? tc_table_row(__ldg(x_index + c_), n_table, status) : c_;
             }
             rp_next = rp_next2;
         }
         int xi_prev = 0;                   // X row index of my row in tile it-1 (the tile whose epilogue runs in iteration it)
         __syncwarp();
-        TC_TRACE_DECL();
         // iteration `it`: gather + operand of tile it (it < my_tiles), epilogue of tile it-1 (it >= 1)
         for (int it = 0; it <= my_tiles; ++it) {
             const bool have_tile = it < my_tiles;
@@ -403,7 +293,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                         }
                         // table form: the window holds the neighbour's table row, looked up here, a tile ahead
                         // (issued now, stored after the stream: see tag_pref below)
-                        if (HSRC_TABLE) tag_pref[jj] = __ldg(x_index + idx_pref[jj]);
+                        if (HSRC_TABLE) tag_pref[jj] = tc_table_row(__ldg(x_index + idx_pref[jj]), n_table, status);
                         else nb[lane + 32 * jj] = idx_pref[jj];
                     }
                     if (lane <= TC_ROWS_PER_GW) nb[IDX_CAP + lane] = rel1;
@@ -451,7 +341,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
 #pragma unroll
                         for (int jj = 0; jj < IPL; ++jj) {
                             const int c_ = window_index(jj, r_mid, r_end, base, k);
-                            idx_s[lane + 32 * jj] = HSRC_TABLE ? __ldg(x_index + c_) : c_;
+                            idx_s[lane + 32 * jj] = HSRC_TABLE ? tc_table_row(__ldg(x_index + c_), n_table, status) : c_;
                         }
                         __syncwarp();
                     }
@@ -497,7 +387,6 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                 rp_next = rp_next2;
                 __syncwarp();
                 if (lane == 0) tc_mbar_arrive(bar(BAR_FULL0 + q));
-                TC_TRACE(2);
             }
             // X term of tile it-1, my rows and columns: in flight across the waits below
             const int64_t prow0 = (((int64_t)blockIdx.x + (int64_t)(it - 1) * gridDim.x) * TC_TILE) + 32 * q;
@@ -516,12 +405,10 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             // The MMAs of tile it-1 are complete: the A operand may be overwritten, the accumulator read.
             if (it >= 1 && !tc_wait(bar(BAR_MMA0 + ((it - 1) & 1)), (uint32_t)(((it - 1) >> 1) & 1), abort_flag, status, 21)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            TC_TRACE(3);
             if (have_tile) {
                 // -------------------------------- operand --------------------------------
                 // the quarter's 32 rows are complete; thread = row, my CW columns -> TF32 head and tail
                 if (!tc_wait(bar(BAR_FULL0 + q), (uint32_t)(it & 1), abort_flag, status, 20)) break;
-                TC_TRACE(4);
                 const float* my_row = stage + (size_t)(32 * q + lane) * STAGE_STRIDE + CW * j;
                 const uint32_t tm_a = TM_AHI + lane_base + (uint32_t)(CW * j);
 #pragma unroll
@@ -544,7 +431,6 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) tc_mbar_arrive(bar(BAR_AREADY));   // my block of the A operand is in tensor memory
-                TC_TRACE(5);
             }
             // my slab is free once the quarter's four workers have read it for tile `it`
             if (have_tile && !tc_wait(bar(BAR_SFREE0 + q), (uint32_t)(it & 1), abort_flag, status, 10)) break;
@@ -583,14 +469,11 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                     }
                 }
                 __syncwarp();   // the slab is rewritten by the next gather
-                TC_TRACE(6);
             }
             xi_prev = xi_this;
         }
-        TC_TRACE_PRINT("worker");
     } else {
         // =========================== MMA-issue warp ===========================
-        TC_TRACE_DECL();
         for (int it = 0; it < my_tiles; ++it) {
             const int b = it & 1;
             // the whole A operand is in tensor memory, and the accumulator buffer has been read
@@ -598,7 +481,6 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             if (ok && it >= 2) ok = tc_wait(bar(BAR_DFREE0 + b), (uint32_t)(((it - 2) >> 1) & 1), abort_flag, status, 23);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            TC_TRACE(0);
             if (lane == 0) {
                 const uint32_t d_tmem = TM_ACC + (uint32_t)(D * b);
                 const uint32_t bhi = smem_u32(Bhi), blo = smem_u32(Blo);
@@ -619,9 +501,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                              : "memory");
             }
             __syncwarp();
-            TC_TRACE(1);
         }
-        TC_TRACE_PRINT("mma");
     }
 
     // ---- teardown: everyone is done with tensor memory before it is released
@@ -631,30 +511,39 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
 }
 
-// Self-test of the bounded wait: one warp waits on an mbarrier that nothing arrives at.  The wait gives up
-// after a few polls, records S2V_ERR_DEVICE_TIMEOUT (site 99) in the context's status word and the kernel
+// Self-test of the bounded wait, through tc_wait itself.  Two warps, two mbarriers that nothing ever arrives
+// at.  Warp 0 waits with a small poll limit: its wait runs out, raises the abort flag and records
+// S2V_ERR_DEVICE_TIMEOUT (site 98).  Warp 1 waits with a larger limit and must leave because it sees the
+// flag, not because its own limit ran out.  If both happened the site is rewritten to 99.  The kernel
 // returns normally: no trap, no fault, the context stays usable.
 __global__ void tc_wait_selftest_kernel(s2v_device_status* status)
 {
-    __shared__ uint64_t never_arrives;
-    const uint32_t bar = smem_u32(&never_arrives);
+    __shared__ uint64_t never_arrives[2];
+    __shared__ int abort_flag_s;
+    __shared__ int saw_abort;
+    const int warp = threadIdx.x >> 5;
     if (threadIdx.x == 0) {
-        tc_mbar_init(bar, 1);
+        tc_mbar_init(smem_u32(&never_arrives[0]), 1);
+        tc_mbar_init(smem_u32(&never_arrives[1]), 1);
+        abort_flag_s = 0;
+        saw_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    __syncwarp();
-    int polls = 0;
-    bool done = false;
-    while (!(done = tc_mbar_try(bar, 0)) && ++polls < 64) {}
-    if (!done && threadIdx.x == 0) {
-        status->code = S2V_ERR_DEVICE_TIMEOUT;
-        status->where = 99;
+    __syncthreads();
+    volatile int* abort_flag = &abort_flag_s;
+    if (warp == 0) {
+        tc_wait(smem_u32(&never_arrives[0]), 0, abort_flag, status, 98, 32);
+    } else {
+        const bool ok = tc_wait(smem_u32(&never_arrives[1]), 0, abort_flag, status, 97, 1 << 12);
+        if (!ok && *abort_flag && status->where == 98 && threadIdx.x == 32) saw_abort = 1;
     }
+    __syncthreads();
+    if (threadIdx.x == 0 && saw_abort && status->code == S2V_ERR_DEVICE_TIMEOUT) status->where = 99;
 }
 
 template <int D, bool HAS_VAL, int XMODE, bool HSRC_TABLE = false>
 int tc_launch(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const int32_t* rp, const int32_t* ci, const float* val,
-              const float* H, const float* W, const float* X, const int32_t* x_index, float* out)
+              const float* H, const float* W, const float* X, const int32_t* x_index, int n_table, float* out)
 {
     auto kern = s2v_level_tc_kernel<D, HAS_VAL, XMODE, HSRC_TABLE>;
     constexpr size_t SMEM = TcCfg<D>::SMEM_BYTES;
@@ -663,7 +552,7 @@ int tc_launch(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const int32_t* rp, 
     const int64_t num_tiles = (n_rows + TC_TILE - 1) / TC_TILE;
     int64_t blocks = num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count;
     if (blocks < 1) blocks = 1;
-    kern<<<(unsigned)blocks, TC_THREADS, SMEM, st>>>(n_rows, num_tiles, rp, ci, val, H, W, X, x_index, out,
+    kern<<<(unsigned)blocks, TC_THREADS, SMEM, st>>>(n_rows, num_tiles, rp, ci, val, H, W, X, x_index, n_table, out,
                                                      ctx->dstatus_dev);
     S2V_CHECK_LAUNCH(ctx, "s2v_level_tc_kernel");
     return S2V_OK;
@@ -676,16 +565,16 @@ int tc_launch(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const int32_t* rp, 
 template <int D>
 static int tc_dispatch(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const int32_t* row_ptr, const int32_t* col_idx,
                        const float* val, const float* H, const float* W, const float* X, const float* table,
-                       const int32_t* x_index, float* out)
+                       const int32_t* x_index, int n_table, float* out)
 {
     if (!H) {
         if (!table || !x_index) return S2V_ERR_UNSUPPORTED;
-        return val ? tc_launch<D, true, 2, true>(ctx, st, n_rows, row_ptr, col_idx, val, nullptr, W, table, x_index, out)
-                   : tc_launch<D, false, 2, true>(ctx, st, n_rows, row_ptr, col_idx, val, nullptr, W, table, x_index, out);
+        return val ? tc_launch<D, true, 2, true>(ctx, st, n_rows, row_ptr, col_idx, val, nullptr, W, table, x_index, n_table, out)
+                   : tc_launch<D, false, 2, true>(ctx, st, n_rows, row_ptr, col_idx, val, nullptr, W, table, x_index, n_table, out);
     }
     const int xmode = table ? 2 : (X ? 1 : 0);
     const float* xa = table ? table : X;
-#define TC_GO(HV, XM) return tc_launch<D, HV, XM>(ctx, st, n_rows, row_ptr, col_idx, val, H, W, xa, x_index, out)
+#define TC_GO(HV, XM) return tc_launch<D, HV, XM>(ctx, st, n_rows, row_ptr, col_idx, val, H, W, xa, x_index, n_table, out)
     if (val) {
         if (xmode == 0) TC_GO(true, 0);
         if (xmode == 1) TC_GO(true, 1);
@@ -699,16 +588,16 @@ static int tc_dispatch(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, const int3
 
 int s2v_launch_level_tc(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int d, const int32_t* row_ptr,
                         const int32_t* col_idx, const float* val, const float* H, const float* W, const float* X,
-                        const float* table, const int32_t* x_index, float* out)
+                        const float* table, const int32_t* x_index, int n_table, float* out)
 {
-    if (d == 128) return tc_dispatch<128>(ctx, st, n_rows, row_ptr, col_idx, val, H, W, X, table, x_index, out);
-    if (d == 64) return tc_dispatch<64>(ctx, st, n_rows, row_ptr, col_idx, val, H, W, X, table, x_index, out);
+    if (d == 128) return tc_dispatch<128>(ctx, st, n_rows, row_ptr, col_idx, val, H, W, X, table, x_index, n_table, out);
+    if (d == 64) return tc_dispatch<64>(ctx, st, n_rows, row_ptr, col_idx, val, H, W, X, table, x_index, n_table, out);
     return S2V_ERR_UNSUPPORTED;
 }
 
 int s2v_launch_wait_selftest(s2v_ctx* ctx, cudaStream_t st)
 {
-    tc_wait_selftest_kernel<<<1, 32, 0, st>>>(ctx->dstatus_dev);
+    tc_wait_selftest_kernel<<<1, 64, 0, st>>>(ctx->dstatus_dev);
     S2V_CHECK_LAUNCH(ctx, "tc_wait_selftest_kernel");
     return S2V_OK;
 }

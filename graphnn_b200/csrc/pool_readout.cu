@@ -60,16 +60,19 @@ __global__ void __launch_bounds__(256) input_proj_dense_kernel(int64_t n, int F,
 // node row with float4, 32/(d/4) node rows are summed side by side and combined with
 // warp shuffles at the end.  Replaces the [G x N] CSR x dense product of
 // SubgraphMsgPass (src/nn/msg_pass.cpp:156-177) when every graph owns a contiguous
-// node range.
+// node range.  `average` gives the mean-pooling form (SubgraphMsgPass with average = true,
+// src/nn/msg_pass.cpp:170): every node row is weighted by 1 / |graph| as it is added.
 template <int LPR>
 __global__ void __launch_bounds__(256) segment_sum_kernel(int64_t G, const int32_t* __restrict__ seg,
-                                                           const float4* __restrict__ H4, float4* __restrict__ Y4)
+                                                           const float4* __restrict__ H4, float4* __restrict__ Y4,
+                                                           int average)
 {
     constexpr int RPP = 32 / LPR;
     const int lane = threadIdx.x & 31, sub = lane / LPR, sl = lane % LPR;
     const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t g = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; g < G; g += warps) {
         const int beg = seg[g], end = seg[g + 1];
+        const float wgt = average ? (float)(1.0 / (double)(end - beg)) : 1.0f;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         int t = beg + sub;
         for (; t + 3 * RPP < end; t += 4 * RPP) {
@@ -77,11 +80,23 @@ __global__ void __launch_bounds__(256) segment_sum_kernel(int64_t G, const int32
 #pragma unroll
             for (int u = 0; u < 4; ++u) v[u] = __ldcs(H4 + (int64_t)(t + u * RPP) * LPR + sl);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+            for (int u = 0; u < 4; ++u) {
+                if (average) {
+                    acc.x = fmaf(wgt, v[u].x, acc.x); acc.y = fmaf(wgt, v[u].y, acc.y);
+                    acc.z = fmaf(wgt, v[u].z, acc.z); acc.w = fmaf(wgt, v[u].w, acc.w);
+                } else {
+                    acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
+                }
+            }
         }
         for (; t < end; t += RPP) {
             const float4 v = __ldcs(H4 + (int64_t)t * LPR + sl);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            if (average) {
+                acc.x = fmaf(wgt, v.x, acc.x); acc.y = fmaf(wgt, v.y, acc.y);
+                acc.z = fmaf(wgt, v.z, acc.z); acc.w = fmaf(wgt, v.w, acc.w);
+            } else {
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
         }
 #pragma unroll
         for (int o = 16; o >= LPR; o >>= 1) {
@@ -96,15 +111,17 @@ __global__ void __launch_bounds__(256) segment_sum_kernel(int64_t G, const int32
 
 // generic d: one warp per graph, lanes stride columns, nodes in order
 __global__ void __launch_bounds__(256) segment_sum_generic_kernel(int64_t G, int d, const int32_t* __restrict__ seg,
-                                                                   const float* __restrict__ H, float* __restrict__ Y)
+                                                                   const float* __restrict__ H, float* __restrict__ Y,
+                                                                   int average)
 {
     const int lane = threadIdx.x & 31;
     const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t g = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; g < G; g += warps) {
         const int beg = seg[g], end = seg[g + 1];
+        const float wgt = average ? (float)(1.0 / (double)(end - beg)) : 1.0f;
         for (int c = lane; c < d; c += 32) {
             float acc = 0.f;
-            for (int t = beg; t < end; ++t) acc += H[(int64_t)t * d + c];
+            for (int t = beg; t < end; ++t) acc = average ? fmaf(wgt, H[(int64_t)t * d + c], acc) : acc + H[(int64_t)t * d + c];
             Y[g * d + c] = acc;
         }
     }
@@ -303,6 +320,12 @@ int s2v_input_proj_dense_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n, int num
 int s2v_segment_sum_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int d, const int32_t* seg_ptr,
                         const float* H, float* Y)
 {
+    return s2v_segment_pool_f32(ctx, stream, num_graphs, d, seg_ptr, H, 0, Y);
+}
+
+int s2v_segment_pool_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int d, const int32_t* seg_ptr,
+                         const float* H, int average, float* Y)
+{
     S2V_ENTER(ctx);
     if (num_graphs < 0 || d <= 0) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "segment_sum: bad shape");
     if (num_graphs == 0) return S2V_OK;
@@ -313,13 +336,13 @@ int s2v_segment_sum_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int
     const float4* H4 = reinterpret_cast<const float4*>(H);
     float4* Y4 = reinterpret_cast<float4*>(Y);
     if (vec && d == 32)
-        segment_sum_kernel<8><<<grid, 256, 0, st>>>(num_graphs, seg_ptr, H4, Y4);
+        segment_sum_kernel<8><<<grid, 256, 0, st>>>(num_graphs, seg_ptr, H4, Y4, average);
     else if (vec && d == 64)
-        segment_sum_kernel<16><<<grid, 256, 0, st>>>(num_graphs, seg_ptr, H4, Y4);
+        segment_sum_kernel<16><<<grid, 256, 0, st>>>(num_graphs, seg_ptr, H4, Y4, average);
     else if (vec && d == 128)
-        segment_sum_kernel<32><<<grid, 256, 0, st>>>(num_graphs, seg_ptr, H4, Y4);
+        segment_sum_kernel<32><<<grid, 256, 0, st>>>(num_graphs, seg_ptr, H4, Y4, average);
     else
-        segment_sum_generic_kernel<<<grid, 256, 0, st>>>(num_graphs, d, seg_ptr, H, Y);
+        segment_sum_generic_kernel<<<grid, 256, 0, st>>>(num_graphs, d, seg_ptr, H, Y, average);
     S2V_CHECK_LAUNCH(ctx, "segment_sum_kernel");
     return S2V_OK;
 }

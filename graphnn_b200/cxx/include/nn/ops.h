@@ -49,13 +49,13 @@ public:
         : Factor(_name, _properr), transA(_transA), transB(_transB) {}
     void Forward(std::vector<std::shared_ptr<Variable>>& operands, std::vector<std::shared_ptr<Variable>>& outputs, Phase) override
     {
-        ASSERT(operands.size() == 2, "unexpected input size for " << StrType());
-        ASSERT(outputs.size() == 1, "unexpected output size for " << StrType());
+        ASSERT(operands.size() == 2, StrType() << ": wrong number of operands");
+        ASSERT(outputs.size() == 1, StrType() << ": wrong number of outputs");
         auto& output = detail::dense<mode, Dtype>(outputs[0]);
         auto* lhs = dynamic_cast<TensorVar<mode, Dtype>*>(operands[0].get());
         auto* rhs = dynamic_cast<TensorVar<mode, Dtype>*>(operands[1].get());
         ASSERT(lhs && rhs, "operands of the wrong mode/type for " << StrType());
-        ASSERT(rhs->GetMatType() == MatType::dense, "only support [sparse/dense] x [dense]");
+        ASSERT(rhs->GetMatType() == MatType::dense, StrType() << ": the right-hand operand must be a dense matrix");
         auto& right = rhs->template Derived<DENSE>().value;
         if (lhs->GetMatType() == MatType::dense)
             output.MM(lhs->template Derived<DENSE>().value, right, transA, transB, 1.0, 0.0);
@@ -75,15 +75,15 @@ public:
         : Factor(_name, _properr), coeff(_coeff) {}
     void Forward(std::vector<std::shared_ptr<Variable>>& operands, std::vector<std::shared_ptr<Variable>>& outputs, Phase) override
     {
-        ASSERT(operands.size() >= 2, "unexpected input size for " << StrType());
-        ASSERT(outputs.size() == 1, "unexpected output size for " << StrType());
+        ASSERT(operands.size() >= 2, StrType() << ": wrong number of operands");
+        ASSERT(outputs.size() == 1, StrType() << ": wrong number of outputs");
         ASSERT(coeff.size() == 0 || operands.size() == coeff.size(), "wrong number of coefficients");
         auto& output = detail::dense<mode, Dtype>(outputs[0]);
         output.CopyFrom(detail::dense<mode, Dtype>(operands[0]));
         if (coeff.size()) output.Scale(coeff[0]);
         for (size_t i = 1; i < operands.size(); ++i) {
             auto& op_i = detail::dense<mode, Dtype>(operands[i]);
-            ASSERT(op_i.shape == output.shape, "no broadcasting is supported right now");
+            ASSERT(op_i.shape == output.shape, StrType() << ": every operand must have the shape of the output");
             output.Axpy(coeff.size() ? coeff[i] : 1.0, op_i);
         }
     }
@@ -99,8 +99,8 @@ public:
     ReLU(std::string _name, PropErr _properr = PropErr::T) : Factor(_name, _properr) {}
     void Forward(std::vector<std::shared_ptr<Variable>>& operands, std::vector<std::shared_ptr<Variable>>& outputs, Phase) override
     {
-        ASSERT(operands.size() == 1, "unexpected input size for " << StrType());
-        ASSERT(outputs.size() == 1, "unexpected output size for " << StrType());
+        ASSERT(operands.size() == 1, StrType() << ": wrong number of operands");
+        ASSERT(outputs.size() == 1, StrType() << ": wrong number of outputs");
         auto& in = detail::dense<mode, Dtype>(operands[0]);
         auto& out = detail::dense<mode, Dtype>(outputs[0]);
         out.Reshape(in.shape.dims);
@@ -117,8 +117,8 @@ public:
     Softmax(std::string _name, PropErr _properr = PropErr::T) : Factor(_name, _properr) {}
     void Forward(std::vector<std::shared_ptr<Variable>>& operands, std::vector<std::shared_ptr<Variable>>& outputs, Phase) override
     {
-        ASSERT(operands.size() == 1, "unexpected input size for " << StrType());
-        ASSERT(outputs.size() == 1, "unexpected output size for " << StrType());
+        ASSERT(operands.size() == 1, StrType() << ": wrong number of operands");
+        ASSERT(outputs.size() == 1, StrType() << ": wrong number of outputs");
         auto& out = detail::dense<mode, Dtype>(outputs[0]);
         out.CopyFrom(detail::dense<mode, Dtype>(operands[0]));
         out.Softmax();
@@ -135,12 +135,12 @@ public:
     OutType CreateOutVar() { return std::make_shared<DTensorVar<mode, int>>(this->name + ":out_0"); }
     ArgMax(std::string _name, uint _axis = 0) : Factor(_name, PropErr::N), axis(_axis)
     {
-        ASSERT(axis == 0, StrType() << " not implemented for axis other than 0");
+        ASSERT(axis == 0, StrType() << ": only axis 0 (per-row) is built");
     }
     void Forward(std::vector<std::shared_ptr<Variable>>& operands, std::vector<std::shared_ptr<Variable>>& outputs, Phase) override
     {
-        ASSERT(operands.size() == 1, "unexpected input size for " << StrType());
-        ASSERT(outputs.size() == 1, "unexpected output size for " << StrType());
+        ASSERT(operands.size() == 1, StrType() << ": wrong number of operands");
+        ASSERT(outputs.size() == 1, StrType() << ": wrong number of outputs");
         auto* out = dynamic_cast<DTensorVar<mode, int>*>(outputs[0].get());
         ASSERT(out, "wrong output type for " << StrType());
         auto* in = dynamic_cast<TensorVar<mode, Dtype>*>(operands[0].get());
@@ -168,10 +168,10 @@ public:
         : Factor(_name, _properr), need_softmax(_need_softmax) {}
     void Forward(std::vector<std::shared_ptr<Variable>>& operands, std::vector<std::shared_ptr<Variable>>& outputs, Phase) override
     {
-        ASSERT(operands.size() == 2, "unexpected input size for " << StrType());
+        ASSERT(operands.size() == 2, StrType() << ": wrong number of operands");
         auto& pred = detail::dense<mode, Dtype>(operands[0]);
         auto& label = detail::sparse<mode, Dtype>(operands[1]);
-        ASSERT(pred.cols() == label.cols() && pred.rows() == label.rows(), "# class doesn't match");
+        ASSERT(pred.cols() == label.cols() && pred.rows() == label.rows(), StrType() << ": prediction and label matrices differ in shape");
         auto& out = detail::dense<mode, Dtype>(outputs[0]);
         out.Reshape({pred.rows(), 1});
         S2V_ASSERT_OK(s2v_cross_entropy_f32(GpuHandle::ctx(), nullptr, (int64_t)pred.rows(), (int)pred.cols(), pred.data->ptr,
@@ -191,8 +191,8 @@ public:
         : Factor(_name, _properr), axis(_axis), keep_dim(_keep_dim) {}
     void Forward(std::vector<std::shared_ptr<Variable>>& operands, std::vector<std::shared_ptr<Variable>>& outputs, Phase) override
     {
-        ASSERT(operands.size() == 1, "unexpected input size for " << StrType());
-        ASSERT(axis == -1 && keep_dim == false, "currently only support axis=-1 and keep_dim=false in " << StrType());
+        ASSERT(operands.size() == 1, StrType() << ": wrong number of operands");
+        ASSERT(axis == -1 && keep_dim == false, StrType() << ": only the mean over all elements (axis = -1, keep_dim = false) is built");
         auto& in = detail::dense<mode, Dtype>(operands[0]);
         auto& out = detail::dense<mode, Dtype>(outputs[0]);
         out.Reshape({1});
@@ -213,12 +213,12 @@ public:
     InTopK(std::string _name, int _topK = 1) : Factor(_name, PropErr::N), topK(_topK) {}
     void Forward(std::vector<std::shared_ptr<Variable>>& operands, std::vector<std::shared_ptr<Variable>>& outputs, Phase) override
     {
-        ASSERT(operands.size() == 2, "unexpected input size for " << StrType());
+        ASSERT(operands.size() == 2, StrType() << ": wrong number of operands");
         auto& pred = detail::dense<mode, Dtype>(operands[0]);
         auto* lab = dynamic_cast<DTensorVar<mode, int>*>(operands[1].get());
         auto* out = dynamic_cast<DTensorVar<mode, int>*>(outputs[0].get());
         ASSERT(lab && out, "wrong operand types for " << StrType());
-        ASSERT(pred.rows() == lab->value.shape.Count(), "# instances doesn't match");
+        ASSERT(pred.rows() == lab->value.shape.Count(), StrType() << ": one label per prediction row is required");
         out->value.Reshape(lab->value.shape.dims);
         S2V_ASSERT_OK(s2v_in_top_k_f32(GpuHandle::ctx(), nullptr, (int64_t)pred.rows(), (int)pred.cols(), pred.data->ptr,
                                        lab->value.data->ptr, topK, out->value.data->ptr));
@@ -235,7 +235,7 @@ public:
     TypeCast(std::string _name, PropErr _properr = PropErr::T) : Factor(_name, _properr) {}
     void Forward(std::vector<std::shared_ptr<Variable>>& operands, std::vector<std::shared_ptr<Variable>>& outputs, Phase) override
     {
-        ASSERT(operands.size() == 1, "unexpected input size for " << StrType());
+        ASSERT(operands.size() == 1, StrType() << ": wrong number of operands");
         auto* in = dynamic_cast<DTensorVar<mode, int>*>(operands[0].get());
         ASSERT(in, StrType() << " is implemented for int -> float");
         auto& out = detail::dense<mode, Dtype>(outputs[0]);

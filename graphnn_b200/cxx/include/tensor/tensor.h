@@ -337,7 +337,7 @@ public:
     void Axpy(Dtype a, DTensor<mode, Dtype>& x)
     {
         static_assert(std::is_same<mode, GPU>::value && std::is_same<Dtype, float>::value, "GPU float only");
-        ASSERT(shape == x.shape, "shape doesn't match in Axpy");
+        ASSERT(shape == x.shape, "Axpy: the two tensors differ in shape");
         S2V_ASSERT_OK(s2v_axpy_f32(GpuHandle::ctx(), nullptr, (int64_t)shape.Count(), a, x.data->ptr, data->ptr));
     }
     void MM(DTensor<mode, Dtype>& a, DTensor<mode, Dtype>& b, Trans transA, Trans transB, Dtype alpha, Dtype beta)

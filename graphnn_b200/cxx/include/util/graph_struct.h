@@ -4,7 +4,6 @@
 #ifndef S2V_GRAPH_STRUCT_H
 #define S2V_GRAPH_STRUCT_H
 
-#include <algorithm>
 #include <cassert>
 #include <utility>
 #include <vector>
@@ -17,36 +16,34 @@ template <typename T>
 class LinkedTable
 {
 public:
-    LinkedTable() : n(0), ncap(0) {}
+    LinkedTable() : n(0) {}
 
+    // Appends `content` to the list of key `head_id`; keys past the current count extend the table.
     void AddEntry(int head_id, T content)
     {
-        if (head_id >= n) {
-            if (head_id + 1 > ncap) {
-                ncap = std::max(ncap * 2, head_id + 1);
-                head.resize(ncap);
-            }
-            n = head_id + 1;
-        }
+        EnsureKeys(head_id + 1);
+        if (head_id >= n) n = head_id + 1;
         head[head_id].push_back(content);
     }
 
-    // keeps the capacity of every list, empties them all
+    // Sets the number of keys and empties every list; the lists keep the storage they had, so refilling a
+    // table of the same shape batch after batch does not allocate.
     void Resize(int new_n)
     {
-        if (new_n > ncap) {
-            ncap = std::max(ncap * 2, new_n);
-            head.resize(ncap);
-        }
+        EnsureKeys(new_n);
         n = new_n;
-        for (auto& l : head) l.clear();
+        for (std::vector<T>& list : head) list.clear();
     }
 
     int n;
     std::vector<std::vector<T>> head;
 
 private:
-    int ncap;
+    // `head` only ever grows (std::vector's own geometric growth applies); shrinking `n` keeps the lists alive
+    void EnsureKeys(int keys)
+    {
+        if (keys > static_cast<int>(head.size())) head.resize(static_cast<size_t>(keys));
+    }
 };
 
 class GraphStruct

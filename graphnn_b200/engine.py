@@ -25,6 +25,7 @@ class HostBatch:
     col_idx: torch.Tensor    # int32 [E], pinned
     graph_ptr: torch.Tensor  # int32 [G+1], pinned
     tags: torch.Tensor       # int32 [N], pinned
+    max_graph_nodes: int = 0 # node count of the largest graph (0 = unknown)
 
     def nbytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.row_ptr, self.col_idx, self.graph_ptr, self.tags))
@@ -40,6 +41,7 @@ class DeviceBatch:
     tags: torch.Tensor | None
     x_dense: torch.Tensor | None = None
     val: torch.Tensor | None = None
+    max_graph_nodes: int = 0
 
 
 def _pin(a: np.ndarray) -> torch.Tensor:
@@ -52,19 +54,19 @@ def build_host_batch(batch) -> HostBatch:
     Node2NodeMsgPass / SubgraphMsgPass::InitCPUWeight, src/nn/msg_pass.cpp:46-67,156-177)."""
     row_ptr, col_idx, _ = capi.build_n2n_csr_host(batch.num_nodes, batch.edge_src, batch.edge_dst, with_val=False)
     return HostBatch(batch.num_graphs, batch.num_nodes, _pin(row_ptr), _pin(col_idx), _pin(batch.graph_offsets()),
-                     _pin(batch.tags.astype(np.int32)))
+                     _pin(batch.tags.astype(np.int32)), int(batch.nodes_per_graph.max()) if batch.num_graphs else 0)
 
 
 class S2VInference:
     """The classifier of kernel_mean_field.cpp:28-47 with weights resident on one GPU."""
 
-    def __init__(self, weights: dict, levels: int, device: int = 0):
+    def __init__(self, weights: dict, levels: int, device: int = 0, pool_average: bool = False):
         self.ctx = capi.Context(device)
         self.device = torch.device("cuda", device)
         self.levels = levels
         self.w = {k: torch.from_numpy(np.ascontiguousarray(v, np.float32)).to(self.device) for k, v in weights.items()}
         self.model = self.ctx.make_model(levels, self.w["w_n2l"], self.w["p_node_conv"], self.w["h1_weight"],
-                                         self.w["h2_weight"])
+                                         self.w["h2_weight"], pool_average)
         self.d = int(self.w["w_n2l"].shape[1])
         self.num_class = int(self.w["h2_weight"].shape[1])
         self._ws = None
@@ -73,7 +75,7 @@ class S2VInference:
         dev = self.device
         x = None if dense_x is None else torch.from_numpy(dense_x).to(dev)
         return DeviceBatch(hb.num_graphs, hb.num_nodes, hb.row_ptr.to(dev), hb.col_idx.to(dev), hb.graph_ptr.to(dev),
-                           None if dense_x is not None else hb.tags.to(dev), x)
+                           None if dense_x is not None else hb.tags.to(dev), x, None, hb.max_graph_nodes)
 
     def _workspace(self, n: int, g: int) -> torch.Tensor:
         need = self.ctx.workspace_bytes(n, g, self.d)
@@ -88,7 +90,8 @@ class S2VInference:
         probs = torch.empty_like(logits)
         pred = torch.empty((G,), dtype=torch.int32, device=self.device)
         embed = torch.empty((N, self.d), dtype=torch.float32, device=self.device) if want_embed else None
-        cb = self.ctx.make_batch(G, N, db.row_ptr, db.col_idx, db.val, db.graph_ptr, db.tags, db.x_dense)
+        cb = self.ctx.make_batch(G, N, db.row_ptr, db.col_idx, db.val, db.graph_ptr, db.tags, db.x_dense,
+                                 db.max_graph_nodes)
         self.ctx.forward(self.model, cb, self._workspace(N, G), logits, probs, pred, embed, stream=stream)
         return logits, probs, pred, embed
 

@@ -63,12 +63,18 @@ def shard_csr(row_ptr: np.ndarray, col_idx: np.ndarray, n_cols: int, rank: int, 
 
 
 def rmat_shard_on_device(scale: int, num_edges: int, rank: int, world: int, device, a=0.57, b=0.19, c=0.19, seed=0,
-                         chunk=1 << 26) -> CsrShard:
+                         chunk=1 << 26, relabel: bool = True) -> CsrShard:
     """Symmetrised, deduplicated R-MAT(a,b,c,d) graph with 2^scale nodes, generated on the
     device: every rank draws the same edge stream (counter-based: the generator is re-seeded
     per chunk with (seed, chunk index)) and keeps the directed copies whose row falls in its
-    slab, then sorts and deduplicates only those.  Self loops are kept as generated."""
+    slab, then sorts and deduplicates only those.  Self loops are kept as generated.
+
+    R-MAT puts its heavy rows at the node ids with many zero bits, i.e. mostly in the first row slab.
+    With `relabel` every node id v is replaced by (v * 0x9E3779B1) mod 2^scale -- a bijection (the
+    multiplier is odd), i.e. the same graph with its nodes renumbered -- which spreads the heavy rows
+    evenly over equal row slabs, so that equal row counts are also nearly equal work."""
     n = 1 << scale
+    mult = 0x9E3779B1
     lo, hi = row_range(n, rank, world)
     keys = []
     gen = torch.Generator(device=device)
@@ -83,6 +89,9 @@ def rmat_shard_on_device(scale: int, num_edges: int, rank: int, world: int, devi
             down = r >= a + b
             s = (s << 1) | down
             t = (t << 1) | right
+        if relabel:
+            s = (s * mult) & (n - 1)
+            t = (t * mult) & (n - 1)
         for row, col in ((s, t), (t, s)):
             keep = (row >= lo) & (row < hi)
             keys.append(((row[keep] - lo) << scale) | col[keep])
@@ -160,88 +169,194 @@ def plan_hubs(shard: CsrShard, threshold: int = 2048, piece: int = 512) -> HubPl
 
 
 class GiantGraphLevels:
-    """L levels  H <- ReLU(A*H*W [+ X])  on a row-partitioned graph."""
+    """L levels  H <- ReLU(A*H*W [+ X])  on a row-partitioned graph.
+
+    Layout of a rank's full copy of H.  The local slab is cut into `chunks` row blocks (the same
+    cut on every rank); `full` stores the blocks one after another and, inside block k, the ranks
+    one after another:  full = [block 0: rank 0 rows | rank 1 rows | ...][block 1: ...] ... [hub rows].
+    Block k of all ranks is therefore ONE contiguous range, and its exchange is a single in-place
+    all-gather (send = this rank's piece where it already lies) that can start as soon as the local
+    rows of block k are computed, while block k+1 is still being computed.  The column indices of the
+    shard are renumbered once, at construction, to positions in this layout.
+
+    `exchange(region, piece, rank)` performs that all-gather: `region` is the [world * rows_k, d]
+    range of `full`, `piece` this rank's [rows_k, d] part of it.  It is injectable, like the compute
+    step: NCCL through the library's C ABI on the GPU, torch.distributed (gloo) in the CPU tests."""
 
     def __init__(self, shard: CsrShard, d: int, rank: int, world: int, level_fn, chunks: int = 4, group=None,
-                 hub_plan: HubPlan | None = None, spmm_fn=None, segsum_fn=None):
+                 hub_plan: HubPlan | None = None, spmm_fn=None, segsum_fn=None, exchange=None):
         self.hub = hub_plan
         self.spmm_fn, self.segsum_fn = spmm_fn, segsum_fn
         if hub_plan is not None:
             assert spmm_fn is not None and segsum_fn is not None
             shard = hub_plan.light
-        self.shard, self.d, self.rank, self.world, self.level_fn = shard, d, rank, world, level_fn
+        self.d, self.rank, self.world, self.level_fn = d, rank, world, level_fn
         self.chunks = max(1, min(chunks, shard.rows))
         self.group = group
         dev = shard.col_idx.device
         self.device = dev
-        extra = hub_plan.n_hub if hub_plan is not None else 0       # rank-private source rows N .. N+n_hub
-        self.full = [torch.empty((shard.n_cols + extra, d), dtype=torch.float32, device=dev) for _ in range(2)]
-        self.partial = torch.empty((hub_plan.n_sub, d), dtype=torch.float32, device=dev) if hub_plan is not None else None
-        self.comm_stream = torch.cuda.Stream(device=dev) if dev.type == "cuda" else None
-        # row blocks of the local slab
         rows = shard.rows
+        self.rows = rows
+        self.n = shard.n_cols
+        assert self.n == rows * world, "equal row slabs: the number of columns must be world * rows"
         edges = [rows * k // self.chunks for k in range(self.chunks + 1)]
         self.blocks = [(edges[k], edges[k + 1]) for k in range(self.chunks) if edges[k + 1] > edges[k]]
-        rp = shard.row_ptr
+        # position of global row (r * rows + i) in the block-major layout
+        self._edges = torch.tensor([lo for lo, _ in self.blocks] + [rows], dtype=torch.int64, device=dev)
+        col = shard.col_idx.to(torch.int64)
+        real = col < self.n                                   # hub rows (>= n) keep their place behind the blocks
+        r = torch.div(col, rows, rounding_mode="floor")
+        i = col - r * rows
+        k = torch.bucketize(i, self._edges[1:], right=True)
+        lo_k = self._edges[k.clamp(max=len(self.blocks) - 1)]
+        rk = self._edges[(k + 1).clamp(max=len(self.blocks))] - lo_k
+        pos = world * lo_k + r * rk + (i - lo_k)
+        new_col = torch.where(real, pos, col).to(torch.int32)
+        self.shard = CsrShard(shard.row_lo, shard.row_hi, shard.n_cols, shard.row_ptr, new_col)
+        del col, real, r, i, k, lo_k, rk, pos
+        extra = hub_plan.n_hub if hub_plan is not None else 0       # rank-private source rows N .. N+n_hub
+        if hub_plan is not None:                                    # the hubs' own column lists use the same layout
+            hc = hub_plan.sub_col_idx.to(torch.int64)
+            r = torch.div(hc, rows, rounding_mode="floor")
+            i = hc - r * rows
+            k = torch.bucketize(i, self._edges[1:], right=True).clamp(max=len(self.blocks) - 1)
+            lo_k = self._edges[k]
+            rk = self._edges[k + 1] - lo_k
+            self.hub_cols = (world * lo_k + r * rk + (i - lo_k)).to(torch.int32)
+        # full[0] holds the input H0 and is never written by run(); the levels alternate between full[1] and full[2]
+        self.full = [torch.empty((self.n + extra, d), dtype=torch.float32, device=dev) for _ in range(3)]
+        self.partial = torch.empty((hub_plan.n_sub, d), dtype=torch.float32, device=dev) if hub_plan is not None else None
+        self.comm_stream = torch.cuda.Stream(device=dev) if dev.type == "cuda" else None
+        self.exchange = exchange if exchange is not None else self._exchange_torch
+        rp = self.shard.row_ptr
         self._block_rp = []
         for lo, hi in self.blocks:
             seg = rp[lo:hi + 1]
             self._block_rp.append((seg - seg[0]).contiguous())
         self._block_base = [int(rp[lo]) for lo, _ in self.blocks]
         self._block_nnz = [int(rp[hi]) - int(rp[lo]) for lo, hi in self.blocks]
+        self.timing = None      # set by run(..., timed=True): per level {"compute_ms", "exchange_ms"}
 
     def all_gather_bytes_per_level(self) -> int:
-        return (self.world - 1) * self.shard.rows * self.d * 4
+        return (self.world - 1) * self.rows * self.d * 4
 
-    def _gather_block(self, full: torch.Tensor, lo: int, hi: int):
-        """All-gather rows [lo, hi) of every rank's slab into `full` (in place).  Block k of rank r
-        lives at rows r*rows + [lo, hi); the ranks' pieces are not contiguous in `full`, so the
-        collective runs on views collected in a list."""
+    def _region(self, full: torch.Tensor, k: int):
+        lo, hi = self.blocks[k]
+        rk = hi - lo
+        region = full[self.world * lo:self.world * hi]
+        return region, region[self.rank * rk:(self.rank + 1) * rk]
+
+    def _exchange_torch(self, region, piece, rank):
         if self.world == 1:
             return
-        rows = self.shard.rows
-        outs = [full[r * rows + lo:r * rows + hi] for r in range(self.world)]
-        dist.all_gather(outs, full[self.rank * rows + lo:self.rank * rows + hi], group=self.group)
+        if region.device.type == "cuda":
+            dist.all_gather_into_tensor(region, piece, group=self.group)
+        else:   # gloo: list form on views of the contiguous region
+            rk = piece.shape[0]
+            dist.all_gather([region[r * rk:(r + 1) * rk] for r in range(self.world)], piece.clone(), group=self.group)
 
     def set_input(self, slab: torch.Tensor):
-        """Local slab of H0 -> full H0 on every rank."""
-        rows = self.shard.rows
-        self.full[0][self.rank * rows:(self.rank + 1) * rows].copy_(slab)
-        self._gather_block(self.full[0], 0, rows)
+        """Local slab of H0 -> full H0 on every rank (block by block)."""
+        for k, (lo, hi) in enumerate(self.blocks):
+            region, piece = self._region(self.full[0], k)
+            piece.copy_(slab[lo:hi])
+            self.exchange(region, piece, self.rank)
         self.cur = 0
 
-    def run(self, W: torch.Tensor, levels: int, X_slab: torch.Tensor | None = None) -> torch.Tensor:
-        """Returns the local slab of H_L (a view into the rank's full copy)."""
-        rows = self.shard.rows
+    def local_slab(self) -> torch.Tensor:
+        """This rank's rows of the current H, in row order (a copy)."""
+        return torch.cat([self._region(self.full[self.cur], k)[1] for k in range(len(self.blocks))])
+
+    def gather_rows(self, which: int, positions_of_global_rows: torch.Tensor) -> torch.Tensor:
+        return self.full[which][positions_of_global_rows]
+
+    def position_of(self, global_rows: torch.Tensor) -> torch.Tensor:
+        """Row index inside `full` of the given global node ids (int64 tensor)."""
+        r = torch.div(global_rows, self.rows, rounding_mode="floor")
+        i = global_rows - r * self.rows
+        k = torch.bucketize(i, self._edges[1:], right=True).clamp(max=len(self.blocks) - 1)
+        lo_k = self._edges[k]
+        rk = self._edges[k + 1] - lo_k
+        return self.world * lo_k + r * rk + (i - lo_k)
+
+    def run(self, W: torch.Tensor, levels: int, X_slab: torch.Tensor | None = None, timed: bool = False) -> torch.Tensor:
+        """Runs `levels` levels from the input set by set_input (which stays intact, so run() can be repeated);
+        returns the local slab of H_L in row order (a copy)."""
+        cuda = self.comm_stream is not None
+        self.timing = [] if timed and cuda else None
+        self.cur = 0
         for _ in range(levels):
-            src, dst = self.full[self.cur], self.full[1 - self.cur]
+            nxt = 1 if self.cur != 1 else 2
+            src, dst = self.full[self.cur], self.full[nxt]
             events = []
+            marks = []
+            if timed and cuda:
+                t_begin = torch.cuda.Event(enable_timing=True)
+                t_begin.record(torch.cuda.current_stream())
             if self.hub is not None:   # hub sums of this level -> the extra source rows of `src`
-                n = self.shard.n_cols
-                self.spmm_fn(self.hub.sub_row_ptr, self.hub.sub_col_idx, src[:n], self.partial)
+                n = self.n
+                self.spmm_fn(self.hub.sub_row_ptr, self.hub_cols, src[:n], self.partial)
                 self.segsum_fn(self.hub.hub_seg_ptr, self.partial, src[n:])
             for k, (lo, hi) in enumerate(self.blocks):
-                out_rows = dst[self.rank * rows + lo:self.rank * rows + hi]
+                region, piece = self._region(dst, k)
                 base = self._block_base[k]
                 nnz = self._block_nnz[k]
                 self.level_fn(self._block_rp[k], self.shard.col_idx[base:base + nnz], src, W,
-                              None if X_slab is None else X_slab[lo:hi], out_rows)
+                              None if X_slab is None else X_slab[lo:hi], piece)
                 if self.world > 1:
-                    if self.comm_stream is not None:
+                    if cuda:
                         ev = torch.cuda.Event()
                         ev.record(torch.cuda.current_stream())
                         with torch.cuda.stream(self.comm_stream):
                             self.comm_stream.wait_event(ev)
-                            self._gather_block(dst, lo, hi)
-                            done = torch.cuda.Event()
+                            if timed:
+                                x0 = torch.cuda.Event(enable_timing=True)
+                                x0.record(self.comm_stream)
+                            self.exchange(region, piece, self.rank)
+                            done = torch.cuda.Event(enable_timing=timed)
                             done.record(self.comm_stream)
+                            if timed:
+                                marks.append((x0, done))
                         events.append(done)
                     else:
-                        self._gather_block(dst, lo, hi)
+                        self.exchange(region, piece, self.rank)
+            if timed and cuda:
+                t_compute = torch.cuda.Event(enable_timing=True)
+                t_compute.record(torch.cuda.current_stream())
             for ev in events:          # the next level reads every row of dst
                 torch.cuda.current_stream().wait_event(ev)
-            self.cur = 1 - self.cur
-        return self.full[self.cur][self.rank * rows:(self.rank + 1) * rows]
+            if timed and cuda:
+                t_end = torch.cuda.Event(enable_timing=True)
+                t_end.record(torch.cuda.current_stream())
+                self.timing.append((t_begin, t_compute, t_end, marks))
+            self.cur = nxt
+        return self.local_slab()
+
+    def level_buffers(self, level: int):
+        """(input, output) buffers of level `level` (1-based) of the last run()."""
+        out = 1 if level % 2 == 1 else 2
+        src = 0 if level == 1 else (2 if out == 1 else 1)
+        return self.full[src], self.full[out]
+
+    def timing_summary(self) -> list[dict]:
+        """After run(..., timed=True) and a synchronise: per level, compute time, time from the end of the
+        compute to the end of the last exchange (the exposed part), and the summed exchange time."""
+        out = []
+        for t_begin, t_compute, t_end, marks in (self.timing or []):
+            out.append({"compute_ms": t_begin.elapsed_time(t_compute), "exposed_exchange_ms": t_compute.elapsed_time(t_end),
+                        "exchange_ms_sum": float(sum(a.elapsed_time(b) for a, b in marks))})
+        return out
+
+
+def make_comm_exchange(comm, stream_getter=None):
+    """exchange() for GiantGraphLevels on the library's NCCL entry point (s2v_allgather_rows_f32): one
+    contiguous in-place all-gather per block, on torch's current stream."""
+
+    def exchange(region, piece, rank):
+        st = torch.cuda.current_stream().cuda_stream
+        comm.allgather_rows(piece, region, st)
+
+    return exchange
 
 
 def make_gpu_hub_fns(ctx):

@@ -43,7 +43,8 @@ typedef enum s2v_status {
     S2V_ERR_BAD_CSR = -4,       /* row_ptr not monotone, col_idx out of range */
     S2V_ERR_WORKSPACE = -5,     /* caller's workspace too small */
     S2V_ERR_NO_DEVICE = -6,     /* no CUDA device / driver */
-    S2V_ERR_DEVICE_TIMEOUT = -7 /* a bounded device-side wait gave up */
+    S2V_ERR_DEVICE_TIMEOUT = -7, /* a bounded device-side wait gave up */
+    S2V_ERR_COMM = -8            /* the NCCL library is missing or one of its calls failed; see s2v_comm_last_error */
 } s2v_status;
 
 /* ---- context: GpuHandle::Init / Destroy (include/tensor/gpu_handle.h:38-59,
@@ -53,13 +54,33 @@ int s2v_ctx_create(int device, s2v_ctx** out);
 int s2v_ctx_destroy(s2v_ctx* ctx);
 int s2v_ctx_device(const s2v_ctx* ctx);
 s2v_stream s2v_ctx_stream(const s2v_ctx* ctx);
+/* Synchronises the context's own stream, then reports and clears the device status word (below). */
 int s2v_ctx_synchronize(s2v_ctx* ctx);
+/* Device status word.  Kernels never trap: a bounded wait that gives up, a node tag outside the table, an
+ * edge that leaves its tile or a graph too large for the tile kernel is recorded in ONE status word per
+ * context (not per stream; the last writer wins) and the kernel carries on with a harmless substitute.
+ * s2v_stream_status synchronises `stream` (NULL = the context's stream), returns the recorded status
+ * (S2V_OK if none) and clears the word.  Callers that launch on their own stream use this instead of
+ * s2v_ctx_synchronize; reading the word while kernels of another stream of the same context still run
+ * may miss or clear their report, so collect the status after the last stream has been synchronised. */
+int s2v_stream_status(s2v_ctx* ctx, s2v_stream stream);
 const char* s2v_status_str(int status);
 const char* s2v_last_error(const s2v_ctx* ctx);
-/* Diagnostic, no counterpart in the reference: launches a one-warp kernel whose bounded barrier wait runs
- * out on purpose (nothing ever arrives).  The kernel returns normally; the next s2v_ctx_synchronize reports
- * S2V_ERR_DEVICE_TIMEOUT (site 99) and clears it, and the context stays usable.  This is the path every
- * wait in the level kernels takes instead of hanging the GPU. */
+/* Per-context switches (no counterpart in the reference).  Returns S2V_ERR_INVALID_ARG for an unknown option. */
+typedef enum s2v_option {
+    S2V_OPT_VALIDATE_HOST_INPUT = 1, /* s2v_infer_host_f32 scans its host arrays before any launch (default 1;
+                                        the environment variable S2V_VALIDATE_HOST=0 sets the default to 0) */
+    S2V_OPT_LEVEL_TC = 2,            /* tcgen05 level kernel: 0 never, 1 automatic (default), 2 whenever the shape allows
+                                        (default from S2V_LEVEL_TC) */
+    S2V_OPT_GRAPH_TILES = 3          /* whole-classifier tile kernel for batches of small graphs: 0 off, 1 automatic
+                                        (default; default from S2V_GRAPH_TILES) */
+} s2v_option;
+int s2v_ctx_set_option(s2v_ctx* ctx, int option, int value);
+/* Diagnostic, no counterpart in the reference: launches a two-warp kernel whose bounded barrier waits (the
+ * very routine every wait of the tensor-core kernels goes through) can never be satisfied.  Warp 0 runs out
+ * of polls, raises the block's abort flag and records the time-out; warp 1 must notice the flag and leave
+ * too.  The kernel returns normally; the next status read reports S2V_ERR_DEVICE_TIMEOUT at site 99 (98 if
+ * warp 1 did not see the flag) and clears it, and the context stays usable. */
 int s2v_selftest_wait_timeout(s2v_ctx* ctx, s2v_stream stream);
 
 /* Number of kernels this library has launched through `ctx` since creation. */
@@ -158,6 +179,10 @@ int s2v_loss_acc_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int nu
  * through s2v_spmm_csr_f32. */
 int s2v_segment_sum_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int d, const int32_t* seg_ptr,
                         const float* H, float* Y);
+/* Same with the mean-pooling form: average != 0 weights every node row by 1 / |graph| as it is added
+ * (SubgraphMsgPass with average = true, src/nn/msg_pass.cpp:170). */
+int s2v_segment_pool_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int d, const int32_t* seg_ptr,
+                         const float* H, int average, float* Y);
 
 /* ---- readout: logits = ReLU(Y*W1)*W2, probs = softmax(logits), pred = argmax(logits).
  * Replaces MatMul, ReLU, MatMul (kernel_mean_field.cpp:45-47) + Softmax + ArgMax.
@@ -173,6 +198,21 @@ int s2v_input_proj_onehot_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n, int nu
 int s2v_input_proj_dense_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n, int num_feat, int d, const float* X,
                              const float* W_in, float* msg, float* h0);
 
+/* ---- batches of small graphs: input projection, all L levels and the pooling in ONE kernel.
+ * Y[g,:] = sum (or mean) over the nodes of graph g of H_L, with H_0 = ReLU(W_in[tags]),
+ * H_{l+1} = ReLU((A*H_l)*W + W_in[tags]) -- kernel_mean_field.cpp:31-44 for one-hot inputs.
+ * Requires d = 128, every graph at most 128 nodes with a contiguous node range (graph_ptr, nn_common.h:63-73)
+ * and no edge between graphs.  Consecutive graphs are packed into tiles of at most 128 nodes; a tile's node
+ * embeddings stay in shared memory across the levels, the dense stage runs on the tcgen05 tensor cores in
+ * 3xTF32, and only Y [G x d] (plus embed_out [N x d] if given) is written.  A larger graph, an edge that
+ * leaves its graph's tile or a tag outside [0, num_tags) is reported through the status word, not faulted.
+ * val may be NULL (all ones).  workspace: s2v_graph_tiles_workspace_bytes(G) bytes of device memory. */
+size_t s2v_graph_tiles_workspace_bytes(int64_t num_graphs);
+int s2v_graph_tiles_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int d, int levels, const int32_t* row_ptr,
+                        const int32_t* col_idx, const float* val, const int32_t* graph_ptr, const int32_t* tags, int num_tags,
+                        const float* W_in, const float* W, int pool_average, void* workspace, size_t workspace_bytes, float* Y,
+                        float* embed_out);
+
 /* ---- the whole classifier on device buffers (FactorGraph::FeedForward of the model
  *      in kernel_mean_field.cpp:28-47 with targets = output). ---- */
 typedef struct s2v_model {
@@ -185,6 +225,7 @@ typedef struct s2v_model {
     const float* p_node_conv; /* [d x d]       "linear-node-conv"     */
     const float* h1_weight;   /* [d x hidden]  */
     const float* h2_weight;   /* [hidden x C]  */
+    int pool_average;         /* 0: sum pooling (the shipped model, kernel_mean_field.cpp:12); 1: mean pooling */
 } s2v_model;
 
 typedef struct s2v_batch {
@@ -197,9 +238,15 @@ typedef struct s2v_batch {
     const int32_t* graph_ptr;   /* [G+1] node range of each graph */
     const int32_t* tags;        /* [N] one-hot node types, or NULL when x_dense is given */
     const float* x_dense;       /* [N x F] or NULL */
+    int32_t max_graph_nodes;    /* node count of the largest graph of the batch, or 0 if unknown.  Device entry
+                                   points cannot read graph_ptr on the host; with 1..128 here (and d = 128, tags)
+                                   s2v_forward_f32 runs the whole classifier as one tile kernel that keeps the
+                                   embeddings in shared memory.  A value that understates the truth is reported
+                                   through the status word (S2V_ERR_UNSUPPORTED) and the oversized graphs are
+                                   truncated.  s2v_infer_host_f32 computes it itself. */
 } s2v_batch;
 
-/* Bytes of device workspace s2v_forward_f32 needs (three [N x d] buffers + [G x d]). */
+/* Bytes of device workspace s2v_forward_f32 needs (three [N x d] buffers + [G x d] + the tile plan). */
 size_t s2v_forward_workspace_bytes(int64_t num_nodes, int64_t num_graphs, int d);
 /* logits [G x C]; probs, pred, embed_out ([N x d], the last level) may be NULL.
  * model weights and batch arrays are device pointers. */
@@ -217,7 +264,10 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
  * the array are rejected with S2V_ERR_WORKSPACE.  The first call on a device resolves
  * the array's address (do it at set-up, before any stream capture begins).  All calls
  * on a GPU share the array and keep its last contents; nothing needs zeroing, but
- * calls that overlap on the same GPU race and must be serialised by the caller. */
+ * calls that overlap on the same GPU race and must be serialised by the caller.
+ * With d = 128 the array bounds the batch to fewer than 10,900 nodes, below the 16,384 rows from which the
+ * per-level tcgen05 kernel is chosen: this entry runs the warp-level (mma.sync) level kernel, or the tile
+ * kernel when max_graph_nodes allows it. */
 #define S2V_STATIC_SCRATCH_BYTES (16u << 20)
 int s2v_forward_static_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, const s2v_batch* batch,
                            float* logits, float* probs, int32_t* pred, float* embed_out);
@@ -232,15 +282,65 @@ int s2v_build_n2n_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* 
 /* Checks a host CSR: row_ptr[0]==0, monotone, row_ptr[m]==nnz, 0 <= col_idx < k. */
 int s2v_validate_csr_host(int64_t m, int64_t k, int64_t nnz, const int32_t* row_ptr, const int32_t* col_idx);
 
+/* The same sort on the DEVICE (device pointers, int32 arrays): a stable counting sort of the edge list by
+ * destination with this library's own kernels, output bit-identical to s2v_build_n2n_csr_host.
+ * `scratch` needs s2v_build_n2n_csr_scratch_bytes(num_nodes, num_edges) bytes.  Edges with an endpoint
+ * outside [0, num_nodes) are dropped from the count and reported through the status word (S2V_ERR_BAD_CSR). */
+size_t s2v_build_n2n_csr_scratch_bytes(int64_t num_nodes, int64_t num_edges);
+int s2v_build_n2n_csr_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_nodes, int64_t num_edges, const int32_t* edge_src,
+                          const int32_t* edge_dst, int average, void* scratch, size_t scratch_bytes, int32_t* row_ptr,
+                          int32_t* col_idx, float* val);
+
 /* ---- the whole classifier from HOST buffers: what one FeedForward call of the
  * reference driver does per batch, uploads included (SpTensor<GPU>::CopyFrom(CPU),
  * src/tensor/gpu_sparse_tensor.cu:55-63; input.CopyFrom(x_cpu), nn_common.h:101).
  * `batch` arrays are host pointers (pinned memory makes the copies asynchronous);
  * `model` weights are DEVICE pointers (parameters live on the device in the
  * reference too).  Writes logits_host [G x C] and pred_host [G] (either may be NULL)
- * and returns after they are valid.  Staging buffers are owned by ctx and only grow. */
+ * and returns after they are valid.  Staging buffers are owned by ctx and only grow.
+ * Before anything is launched the host arrays are scanned (unless S2V_OPT_VALIDATE_HOST_INPUT is 0): row_ptr and
+ * graph_ptr monotone with the right ends, 0 <= col_idx < N, 0 <= tags < F; a violation returns S2V_ERR_BAD_CSR
+ * (or S2V_ERR_INVALID_ARG for a tag) with nothing copied or launched. */
 int s2v_infer_host_f32(s2v_ctx* ctx, const s2v_model* model, const s2v_batch* batch_host, float* logits_host,
                        int32_t* pred_host);
+
+/* The same from a raw directed edge list in AddEdge order (what GraphStruct::edge_list holds after GetBatch,
+ * src/util/graph_struct.cpp:62-70, nn_common.h:76-90): the edge list is uploaded and the node-to-node CSR is
+ * built on the device by s2v_build_n2n_csr_f32, so the host does no sorting at all.  All array arguments are HOST
+ * pointers (pinned memory makes the copies asynchronous); validation as for s2v_infer_host_f32. */
+int s2v_infer_edges_host_f32(s2v_ctx* ctx, const s2v_model* model, int64_t num_graphs, int64_t num_nodes, int64_t num_edges,
+                             const int32_t* edge_src_host, const int32_t* edge_dst_host, const int32_t* graph_ptr_host,
+                             const int32_t* tags_host, float* logits_host, int32_t* pred_host);
+
+/* ---- several GPUs (no counterpart in the reference, which drives one GPU: src/tensor/gpu_handle.cu:17-44).
+ * The path needs two exchanges and no reduction: the final gather of the logits when a batch is sharded by
+ * graph, and one all-gather of the embedding slabs per level when a single giant graph is partitioned by rows.
+ * Both go straight to NCCL, which is opened at run time (libnccl.so.2, or the library named by the environment
+ * variable S2V_NCCL_LIBRARY); a process that already has an NCCL loaded shares it.  Any NCCL failure is returned
+ * as S2V_ERR_COMM with NCCL's message in s2v_comm_last_error (pass NULL for failures before a communicator
+ * exists).  Calls are asynchronous on `stream`, which belongs to the communicator's device. */
+typedef struct s2v_comm s2v_comm;
+#define S2V_COMM_ID_BYTES 128
+/* One process, several GPUs: out[0..ngpu) receive one communicator per device of devs (ncclCommInitAll);
+ * each is then used by the host thread that drives that GPU. */
+int s2v_comm_create(int ngpu, const int* devs, s2v_comm** out);
+/* One process per GPU: rank 0 obtains an id and hands its S2V_COMM_ID_BYTES bytes to the other ranks by any
+ * means (a file, MPI, a key-value store); every rank then calls s2v_comm_create_rank with its own device.
+ * device = -1 leaves the device selection to the caller. */
+int s2v_comm_unique_id(void* id_out);
+int s2v_comm_create_rank(int device, const void* id, int world, int rank, s2v_comm** out);
+int s2v_comm_destroy(s2v_comm* comm);
+int s2v_comm_rank(const s2v_comm* comm);
+int s2v_comm_world(const s2v_comm* comm);
+const char* s2v_comm_last_error(const s2v_comm* comm);
+/* full[r*rows*d ..] = slab of rank r, for equal slabs of rows x d floats (in place if slab already sits at
+ * full + rank*rows*d): the per-level exchange of a row-partitioned graph. */
+int s2v_allgather_rows_f32(s2v_comm* comm, s2v_stream stream, int64_t rows, int d, const float* slab, float* full);
+/* Gather of the results of a batch sharded by graph: rank r holds graphs_per_rank[r] rows (a HOST array of
+ * `world` counts, the same on every rank); logits_all [sum x C] and pred_all [sum] receive all ranks' rows in
+ * rank order on EVERY rank.  Either pair (logits / pred) may be NULL. */
+int s2v_gather_logits(s2v_comm* comm, s2v_stream stream, const int64_t* graphs_per_rank, int num_class, const float* logits_local,
+                      const int32_t* pred_local, float* logits_all, int32_t* pred_all);
 
 #ifdef __cplusplus
 }

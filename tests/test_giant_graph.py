@@ -62,6 +62,7 @@ def _cpu_rank(rank, world, port, scale, d, levels, chunks, out_dir):
     lo, hi = giant.row_range(p.n_rows, rank, world)
     g.set_input(torch.from_numpy(p.H[lo:hi]))
     slab = g.run(torch.from_numpy(p.W), levels)
+    assert torch.equal(slab, g.local_slab())
     np.save(os.path.join(out_dir, f"slab{rank}.npy"), slab.numpy())
     dist.barrier()
     dist.destroy_process_group()
@@ -120,21 +121,18 @@ def test_giant_graph_levels_one_gpu(gpu_ctx, oracle_lib, scale, d):
 def _shard_rank(rank, world, port, out_dir):
     sys.path.insert(0, REPO)
     from oracle import bindings as ob
+    from graphnn_b200 import sharding
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     full = synth.molecule_like(37, 5, 30, 9, 32, 2, 24, 3, 0.1, "uniform", seed=11)
-    mine = full.shard(rank, world)                       # contiguous graphs, balanced by node count
+    mine = sharding.shard_of(full, rank, world)          # contiguous graphs, balanced by node count
     o = ob.forward(mine, "oracle", want_levels=False)
-    bounds = synth.shard_bounds(full.nodes_per_graph, world)
-    max_rows = max(hi - lo for lo, hi in bounds)         # logits gather: ranks pad to the largest shard
-    padded = torch.zeros((max_rows, full.num_class))
-    padded[: mine.num_graphs] = torch.from_numpy(o["logits"])
-    gathered = [torch.zeros_like(padded) for _ in range(world)]
-    dist.all_gather(gathered, padded)
+    gather = sharding.ResultGather(sharding.shard_counts(full.nodes_per_graph, world), full.num_class, torch.device("cpu"))
+    logits, pred = gather(torch.from_numpy(o["logits"]), torch.from_numpy(o["argmax"]))
     if rank == 0:
-        logits = torch.cat([g[: hi - lo] for g, (lo, hi) in zip(gathered, bounds)]).numpy()
-        np.save(os.path.join(out_dir, "logits.npy"), logits)
+        np.save(os.path.join(out_dir, "logits.npy"), logits.numpy())
+        np.save(os.path.join(out_dir, "pred.npy"), pred.numpy())
     dist.barrier()
     dist.destroy_process_group()
 
@@ -144,5 +142,6 @@ def test_shard_by_graph_and_logits_gather_two_cpu_ranks(oracle_lib, tmp_path):
     the single-process result."""
     mp.spawn(_shard_rank, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     full = synth.molecule_like(37, 5, 30, 9, 32, 2, 24, 3, 0.1, "uniform", seed=11)
-    want = oracle_lib.forward(full, "oracle", want_levels=False)["logits"]
-    assert np.array_equal(np.load(tmp_path / "logits.npy"), want)
+    want = oracle_lib.forward(full, "oracle", want_levels=False)
+    assert np.array_equal(np.load(tmp_path / "logits.npy"), want["logits"])
+    assert np.array_equal(np.load(tmp_path / "pred.npy"), want["argmax"])

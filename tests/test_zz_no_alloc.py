@@ -27,12 +27,19 @@ def both_ways(eng, batch):
     pred = torch.full((G,), -1, dtype=torch.int32, device=dev)
     embed = torch.full((N, eng.d), float("nan"), device=dev)
     cb = eng.ctx.make_batch(G, N, db.row_ptr, db.col_idx, None, db.graph_ptr, db.tags, None)
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]               # cudaMemGetInfo: free device memory in bytes
     eng.ctx.forward_static(eng.model, cb, logits, probs, pred, embed)
     eng.ctx.synchronize()
-    return ref, (logits, probs, pred, embed)
+    free_after = torch.cuda.mem_get_info()[0]
+    return ref, (logits, probs, pred, embed), free_before - free_after
 
 
-def check(ref, got):
+def check(ref, got, consumed=None, allow_setup=False):
+    # Once the first call on the device has resolved the array's address (and the driver has loaded the
+    # kernels), a call must leave the amount of free device memory exactly as it found it.
+    if consumed is not None and not allow_setup:
+        assert consumed == 0, f"the no-allocation entry point consumed {consumed} bytes of device memory"
     for name, a, b in zip(("logits", "probs", "pred", "embed"), ref, got):
         a, b = a.cpu().numpy(), b.cpu().numpy()
         if name == "pred":
@@ -45,7 +52,7 @@ def test_static_scratch_forward_matches_twice_in_a_row():
     first = synth.mutag_like(seed=0)
     eng = engine.S2VInference(first.weights, first.levels)
     assert eng.ctx.workspace_bytes(first.num_nodes, first.num_graphs, first.d) <= SCRATCH_LIMIT
-    check(*both_ways(eng, first))
+    check(*both_ways(eng, first), allow_setup=True)
     # second call in a row: the array still holds the first call's data, and this batch is
     # larger (different node count), so stale contents would show up as wrong numbers
     second = synth.molecule_like(200, 10, 28, 7, 64, 3, 128, 2, 0.1, "uniform", seed=9)
