@@ -249,14 +249,14 @@ class ClassifierStep:
     """One inference step on one rank, composed from the library's operators so that the dominant kernel
     can be bracketed by CUDA events on the launching stream."""
 
-    def __init__(self, torch, eng, batch, stream, gather=None):
+    def __init__(self, torch, eng, batch, stream, gather=None, use_tiles=False):
         from graphnn_b200 import engine
         self.torch, self.eng, self.ctx, self.b, self.stream, self.gather = torch, eng, eng.ctx, batch, stream, gather
         dev = eng.device
         self.hb = engine.build_host_batch(batch)
         self.db = eng.to_device(self.hb)
         G, N, d, C = batch.num_graphs, batch.num_nodes, batch.d, batch.num_class
-        self.tiles = d == 128 and int(batch.nodes_per_graph.max()) <= 128
+        self.tiles = bool(use_tiles) and d == 128 and int(batch.nodes_per_graph.max()) <= 128
         self.Y = torch.empty((G, d), device=dev)
         self.logits = torch.empty((G, C), device=dev)
         self.pred = torch.empty((G,), dtype=torch.int32, device=dev)
@@ -403,7 +403,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     torch.cuda.synchronize()
     torch.cuda.set_stream(stream)
     gather = sharding.ResultGather(counts, full.num_class, dev, comm=comm) if world > 1 else None
-    step = ClassifierStep(torch, eng, mine, stream, gather)
+    ctx.set_option(ctx.OPT_GRAPH_TILES, int(args.tiles))    # the host-buffer entry points follow the same choice
+    step = ClassifierStep(torch, eng, mine, stream, gather, use_tiles=args.tiles)
     launches0 = ctx.launches
     elapsed_ms, clocks = device_timed(torch, dist, world, stream, step, args.steps, args.warmup, local_rank)
     launches = (ctx.launches - launches0) * args.steps // (args.steps + max(args.warmup, 3))
@@ -458,7 +459,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     weak = None
     if world > 1:
         per_rank = make_workload(args.workload, seed=rank)
-        wstep = ClassifierStep(torch, eng, per_rank, stream, sharding.ResultGather([per_rank.num_graphs] * world, C, dev, comm=comm))
+        wstep = ClassifierStep(torch, eng, per_rank, stream, sharding.ResultGather([per_rank.num_graphs] * world, C, dev, comm=comm),
+                               use_tiles=args.tiles)
         w_ms, _ = device_timed(torch, dist, world, stream, wstep, args.steps, args.warmup, local_rank)
         (w_ms,) = max_over_ranks(torch, dist, world, dev, [w_ms])
         weak = {"value": world * per_rank.num_graphs * args.steps / (w_ms * 1e-3), "unit": "graphs/s", "ms_per_step": w_ms / args.steps,
@@ -475,9 +477,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD_TEXT[args.workload], "graphs_total": total_graphs,
                        "graphs_rank0": G, "nodes_rank0": N, "edges_rank0": E, "parallelism": f"shard-by-graph x{world}, logits gathered with s2v_gather_logits (NCCL)",
-                       "l2": ("the per-step working set of rank 0 is small enough to stay in the 126 MB L2 on several GPUs; the kernel is "
-                              "tensor-pipe bound, not DRAM bound, and no flush is done") if step.tiles else
-                             "per-step working set (3 x [N x d] fp32) exceeds the 126 MB L2; no flush needed",
+                       "l2": ("tile kernel: inputs of a few MB, embeddings never leave shared memory; no flush is done" if step.tiles else
+                              ("per-step working set (two [N x d] fp32 matrices + CSR, > 500 MB) exceeds the 126 MB L2; no flush needed"
+                               if 2 * N * d * 4 > 126e6 else
+                               "rank 0's per-step working set fits the 126 MB L2 at this shard size; the step is launch- and "
+                               "latency-bound there, and no flush is done")),
+                       "path": "tile kernel" if step.tiles else "per-level kernels",
                        "input_digest": full.digest()},
             "e2e": {"value": total_graphs * e2e_steps / (e2e_edges_ms * 1e-3), "unit": "graphs/s",
                     "h2d_bytes_per_step": e2e_bytes_in, "d2h_bytes_per_step": int(logits_h.nbytes + pred_h.nbytes),
@@ -518,6 +523,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                                 "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
                                 "peak_kind": peaks["kind"], "ms_per_launch": lv_ms, "launches": lv_n, "bytes_per_launch": comp,
                                 "model": "compulsory (each H row once) + CSR + tags + out + W", "traffic": None}
+            if args.workload == "molecules" and world == 1:
+                traffic, source = NCU_TRAFFIC["level_tc_mol_d128"]
+                line["roofline"].update({"traffic": traffic, "traffic_source": source,
+                                         "frac_dram": traffic / (lv_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]})
             if "level_first" in kms:
                 f_ms, f_n = kms["level_first"]
                 fb = level_bytes(N, E, d, "compulsory", "lookup", h_form="table")
@@ -541,6 +550,20 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                               "checked_by": f"the reference build (kind={kind}) on the whole batch, against the logits the e2e entry point returned"}
             if not args.skip_level:
                 line["level_cfg2"] = level_cfg2(ctx, torch, peaks)
+            if not args.tiles and d == 128 and int(full.nodes_per_graph.max()) <= 128:
+                # the opt-in whole-classifier tile kernel on the same batch, device-timed, checked against the default path
+                tstep = ClassifierStep(torch, eng, full, stream, None, use_tiles=True)
+                t_ms, _ = device_timed(torch, dist, 1, stream, tstep, min(args.steps, 20), 3, local_rank)
+                ctx.stream_status(stream.cuda_stream)
+                tk = tstep.kernel_ms()
+                flops_tf32 = 3 * 2 * N * d * d * L
+                line["tile_kernel"] = {
+                    "note": "s2v_graph_tiles_f32 (S2V_OPT_GRAPH_TILES = 1): input projection + all levels + pooling in one kernel, embeddings in shared memory",
+                    "value": full.num_graphs * min(args.steps, 20) / (t_ms * 1e-3), "unit": "graphs/s", "ms_per_step": t_ms / min(args.steps, 20),
+                    "kernel_ms": tk["tiles"][0], "bound": "tensor", "achieved_tflops_tf32": flops_tf32 / (tk["tiles"][0] * 1e-3) / 1e12,
+                    "peak_tflops_tf32": peaks["bf16_tflops"] / 2, "frac": flops_tf32 / (tk["tiles"][0] * 1e-3) / 1e12 / (peaks["bf16_tflops"] / 2),
+                    "argmax_equal_to_default_path": bool(np.array_equal(tstep.pred.cpu().numpy(), step.pred.cpu().numpy())),
+                    "max_abs_logit_diff_to_default_path": float((tstep.logits - step.logits).abs().max().item())}
     # ---- several GPUs: the row-partitioned giant graph at a scale that runs in seconds
     giant_block = None
     if world > 1 and args.giant_scale > 0 and args.workload == "molecules":
@@ -763,6 +786,8 @@ def main():
     ap.add_argument("--giant-scale", type=int, default=22,
                     help="default multi-GPU run: log2 node count of the giant-graph block appended to the line (0 = leave it out)")
     ap.add_argument("--skip-level", action="store_true", help="leave out the 1M-node fused-level measurement")
+    ap.add_argument("--tiles", type=int, default=0, choices=[0, 1],
+                    help="1: run the classifier through the whole-classifier tile kernel (S2V_OPT_GRAPH_TILES) instead of the per-level kernels")
     ap.add_argument("--case", default=None, choices=["er_d64", "er_d64_full", "mol_d128", "prot_d64", "mol_tiles", "mol_tiles_small"],
                     help="run one small launch case (for profiler captures) instead of the benchmark")
     ap.add_argument("--launches", type=int, default=3)

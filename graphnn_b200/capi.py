@@ -91,6 +91,9 @@ def load_library():
         "s2v_forward_static_f32": (i32, [vp, vp, C.POINTER(Model), C.POINTER(Batch), vp, vp, vp, vp]),
         "s2v_build_n2n_csr_host": (i32, [i64, i64, vp, vp, i32, vp, vp, vp]),
         "s2v_validate_csr_host": (i32, [i64, i64, i64, vp, vp]),
+        "s2v_build_e2n_csr_host": (i32, [i64, i64, vp, vp, i32, vp, vp, vp]),
+        "s2v_build_n2e_csr_host": (i32, [i64, i64, vp, vp, vp, vp]),
+        "s2v_build_e2e_csr_host": (i32, [i64, i64, vp, vp, vp, vp, vp, i64, C.POINTER(C.c_int64)]),
         "s2v_infer_host_f32": (i32, [vp, C.POINTER(Model), C.POINTER(Batch), vp, vp]),
         "s2v_comm_create": (i32, [i32, vp, vp]),
         "s2v_comm_unique_id": (i32, [vp]),
@@ -142,6 +145,33 @@ def build_n2n_csr_host(num_nodes: int, edge_src: np.ndarray, edge_dst: np.ndarra
     if rc != 0:
         raise S2VError(rc, lib.s2v_status_str(rc).decode())
     return row_ptr, col_idx[:E], (val[:E] if with_val else None)
+
+
+def build_edge_csrs_host(num_nodes: int, edge_src: np.ndarray, edge_dst: np.ndarray, average: bool = False) -> dict:
+    """The edge-level message-passing matrices of the reference (edge-to-node, node-to-edge, edge-to-edge) as
+    {"e2n": (row_ptr, col_idx, val), "n2e": ..., "e2e": ...}, built by the library's host builders."""
+    lib = load_library()
+    E = int(edge_src.shape[0])
+    es = np.ascontiguousarray(edge_src, np.int32)
+    ed = np.ascontiguousarray(edge_dst, np.int32)
+
+    def check(rc):
+        if rc != 0:
+            raise S2VError(rc, lib.s2v_status_str(rc).decode())
+    out = {}
+    rp, ci, val = np.empty(num_nodes + 1, np.int32), np.empty(max(E, 1), np.int32), np.empty(max(E, 1), np.float32)
+    check(lib.s2v_build_e2n_csr_host(num_nodes, E, _ptr(es), _ptr(ed), int(average), _ptr(rp), _ptr(ci), _ptr(val)))
+    out["e2n"] = (rp, ci[:E], val[:E])
+    rp, ci, val = np.empty(E + 1, np.int32), np.empty(max(E, 1), np.int32), np.empty(max(E, 1), np.float32)
+    check(lib.s2v_build_n2e_csr_host(num_nodes, E, _ptr(es), _ptr(rp), _ptr(ci), _ptr(val)))
+    out["n2e"] = (rp, ci[:E], val[:E])
+    nnz = C.c_int64(0)
+    rp = np.empty(E + 1, np.int32)
+    check(lib.s2v_build_e2e_csr_host(num_nodes, E, _ptr(es), _ptr(ed), _ptr(rp), None, None, 0, C.byref(nnz)))
+    ci, val = np.empty(max(nnz.value, 1), np.int32), np.empty(max(nnz.value, 1), np.float32)
+    check(lib.s2v_build_e2e_csr_host(num_nodes, E, _ptr(es), _ptr(ed), _ptr(rp), _ptr(ci), _ptr(val), nnz.value, C.byref(nnz)))
+    out["e2e"] = (rp, ci[:nnz.value], val[:nnz.value])
+    return out
 
 
 def validate_csr_host(m: int, k: int, row_ptr: np.ndarray, col_idx: np.ndarray) -> int:

@@ -367,8 +367,14 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
 }
 
 // ---------------------------------------------------------------- host-side CSR
-int s2v_build_n2n_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* edge_src, const int32_t* edge_dst,
-                           int average, int32_t* row_ptr, int32_t* col_idx, float* val)
+}  // extern "C"
+
+namespace
+{
+// Row y of the result lists, for every edge x -> y in edge order, either x (payload_edge_id = false: the
+// node-to-node matrix) or the edge's index (true: the edge-to-node matrix).
+int build_in_edge_csr(int64_t num_nodes, int64_t num_edges, const int32_t* edge_src, const int32_t* edge_dst, bool payload_edge_id,
+                      int average, int32_t* row_ptr, int32_t* col_idx, float* val)
 {
     if (num_nodes < 0 || num_edges < 0 || !row_ptr) return S2V_ERR_INVALID_ARG;
     if (num_edges > 0 && (!edge_src || !edge_dst || !col_idx)) return S2V_ERR_INVALID_ARG;
@@ -388,7 +394,7 @@ int s2v_build_n2n_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* 
         }
         for (int64_t i = 0; i < N; ++i) fill[i + 1] += fill[i];
         std::memcpy(row_ptr, fill.data(), sizeof(int32_t) * ((size_t)N + 1));
-        for (int64_t e = 0; e < E; ++e) col_idx[fill[edge_dst[e]]++] = edge_src[e];
+        for (int64_t e = 0; e < E; ++e) col_idx[fill[edge_dst[e]]++] = payload_edge_id ? (int32_t)e : edge_src[e];
     } else {
         // large batch: the same stable sort in three parallel passes.
         //   1. every thread histograms its contiguous slice of the edge list over NB buckets of
@@ -440,7 +446,7 @@ int s2v_build_n2n_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* 
                 for (int64_t e = e0; e < e1; ++e) {
                     const int32_t y = edge_dst[e];
                     const int64_t pos = h[y >> shift]++;
-                    tmp_src[pos] = edge_src[e];
+                    tmp_src[pos] = payload_edge_id ? (int32_t)e : edge_src[e];
                     tmp_dst[pos] = y;
                 }
             }
@@ -477,6 +483,72 @@ int s2v_build_n2n_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* 
             for (int32_t t = row_ptr[i]; t < row_ptr[i + 1]; ++t) val[t] = v;
         }
     }
+    return S2V_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int s2v_build_n2n_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* edge_src, const int32_t* edge_dst,
+                           int average, int32_t* row_ptr, int32_t* col_idx, float* val)
+{
+    return build_in_edge_csr(num_nodes, num_edges, edge_src, edge_dst, false, average, row_ptr, col_idx, val);
+}
+
+int s2v_build_e2n_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* edge_src, const int32_t* edge_dst,
+                           int average, int32_t* row_ptr, int32_t* col_idx, float* val)
+{
+    return build_in_edge_csr(num_nodes, num_edges, edge_src, edge_dst, true, average, row_ptr, col_idx, val);
+}
+
+int s2v_build_n2e_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* edge_src, int32_t* row_ptr, int32_t* col_idx,
+                           float* val)
+{
+    if (num_nodes < 0 || num_edges < 0 || !row_ptr || (num_edges > 0 && (!edge_src || !col_idx))) return S2V_ERR_INVALID_ARG;
+    if (num_edges >= (int64_t)INT32_MAX) return S2V_ERR_UNSUPPORTED;
+    for (int64_t e = 0; e < num_edges; ++e) {
+        if (edge_src[e] < 0 || edge_src[e] >= num_nodes) return S2V_ERR_BAD_CSR;
+        row_ptr[e] = (int32_t)e;
+        col_idx[e] = edge_src[e];
+        if (val) val[e] = 1.0f;
+    }
+    row_ptr[num_edges] = (int32_t)num_edges;
+    return S2V_OK;
+}
+
+int s2v_build_e2e_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* edge_src, const int32_t* edge_dst,
+                           int32_t* row_ptr, int32_t* col_idx, float* val, int64_t capacity, int64_t* nnz_out)
+{
+    if (num_nodes < 0 || num_edges < 0 || !row_ptr || !nnz_out) return S2V_ERR_INVALID_ARG;
+    if (num_edges > 0 && (!edge_src || !edge_dst)) return S2V_ERR_INVALID_ARG;
+    const int64_t N = num_nodes, E = num_edges;
+    // in-edge lists of every node, in insertion order: (edge index, source) pairs
+    std::vector<int32_t> in_rp((size_t)N + 1), in_edge((size_t)std::max<int64_t>(E, 1)), in_src((size_t)std::max<int64_t>(E, 1));
+    int rc = build_in_edge_csr(N, E, edge_src, edge_dst, true, 0, in_rp.data(), in_edge.data(), nullptr);
+    if (rc != S2V_OK) return rc;
+    for (int64_t t = 0; t < E; ++t) in_src[t] = edge_src[in_edge[t]];
+    // row e = (from -> to): the edges into `from`, except those that come from `to`
+    int64_t nnz = 0;
+    for (int64_t e = 0; e < E; ++e) {
+        const int32_t from = edge_src[e], to = edge_dst[e];
+        for (int32_t t = in_rp[from]; t < in_rp[from + 1]; ++t)
+            if (in_src[t] != to) ++nnz;
+    }
+    *nnz_out = nnz;
+    if (nnz >= (int64_t)INT32_MAX) return S2V_ERR_UNSUPPORTED;
+    if (!col_idx || capacity < nnz) return (capacity < nnz && col_idx) ? S2V_ERR_WORKSPACE : S2V_OK;   // size query
+    int64_t pos = 0;
+    for (int64_t e = 0; e < E; ++e) {
+        row_ptr[e] = (int32_t)pos;
+        const int32_t from = edge_src[e], to = edge_dst[e];
+        for (int32_t t = in_rp[from]; t < in_rp[from + 1]; ++t)
+            if (in_src[t] != to) {
+                col_idx[pos] = in_edge[t];
+                if (val) val[pos] = 1.0f;
+                ++pos;
+            }
+    }
+    row_ptr[E] = (int32_t)pos;
     return S2V_OK;
 }
 

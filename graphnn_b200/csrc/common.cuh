@@ -38,7 +38,7 @@ struct s2v_ctx {
     std::mutex mu;
     s2v_staging staging;
     int tc_mode = 1;  // tcgen05 level kernel: 0 never, 1 when the batch is large enough, 2 whenever the shape allows
-    int graph_tiles = 1;    // whole-classifier tile kernel for batches of small graphs: 0 off, 1 automatic
+    int graph_tiles = 0;    // whole-classifier tile kernel for batches of small graphs: 0 off (default), 1 whenever the batch allows
     int validate_host = 1;  // s2v_infer_host_f32 scans its host arrays before launching
 };
 

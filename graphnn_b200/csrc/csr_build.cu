@@ -11,8 +11,8 @@
 //   4. rank     : every edge counts the edge indices of its row that are smaller than its own; that rank
 //                 is its position in insertion order, where it writes its source.  Rows are short in
 //                 this domain (degree 2..30), so the count is a handful of cached loads per edge;
-//   5. long rows: rows above CSR_LONG_ROW entries are left out of step 4 and sorted by edge index by
-//                 one CTA each (bitonic network in global memory), so the cost never becomes quadratic.
+//   5. long rows: rows above CSR_LONG_ROW entries (listed by step 2) are left out of step 4 and sorted by
+//                 edge index by one CTA each (bitonic network in global memory), so the cost never becomes quadratic.
 // The result is deterministic although steps 1 and 3 use atomics.
 #include "common.cuh"
 
@@ -108,9 +108,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) csr_scan_totals_kernel(int num_b
     if (threadIdx.x == 0) block_sum[num_blocks] = carry;
 }
 
-// adds the block offsets, writes row_ptr[N], and clears the counters so that they can serve as the row cursors
+// adds the block offsets, writes row_ptr[N], clears the counters so that they can serve as the row cursors, and
+// lists the rows above CSR_LONG_ROW entries (long_list[0] = how many, then the rows, in no particular order)
 __global__ void __launch_bounds__(SCAN_THREADS) csr_scan_add_kernel(int64_t N, int num_blocks, const int32_t* __restrict__ block_sum,
-                                                                   int32_t* __restrict__ row_ptr, int32_t* __restrict__ cnt)
+                                                                   int32_t* __restrict__ row_ptr, int32_t* __restrict__ cnt,
+                                                                   int32_t* __restrict__ long_list)
 {
     const int off = block_sum[blockIdx.x];
     const int64_t i0 = (int64_t)blockIdx.x * SCAN_BLOCK + (int64_t)threadIdx.x * SCAN_ITEMS;
@@ -118,6 +120,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) csr_scan_add_kernel(int64_t N, i
     for (int k = 0; k < SCAN_ITEMS; ++k)
         if (i0 + k < N) {
             row_ptr[i0 + k] += off;
+            if (cnt[i0 + k] > CSR_LONG_ROW) long_list[1 + atomicAdd(long_list, 1)] = (int32_t)(i0 + k);
             cnt[i0 + k] = 0;
         }
     if (blockIdx.x == 0 && threadIdx.x == 0) row_ptr[N] = block_sum[num_blocks];
@@ -157,14 +160,15 @@ __global__ void __launch_bounds__(256) csr_rank_kernel(int64_t N, int64_t E, con
 // comparators all point the same way (stage k first compares every element with its mirror image inside the
 // block of k, then runs the half-cleaners k/4, k/8, .. 1): with the positions past the row's end standing
 // for +infinity no such element ever has to move, so comparators that touch them are simply skipped.
-__global__ void __launch_bounds__(1024) csr_long_rows_kernel(int64_t N, const int32_t* __restrict__ src,
+__global__ void __launch_bounds__(1024) csr_long_rows_kernel(const int32_t* __restrict__ long_list, const int32_t* __restrict__ src,
                                                              const int32_t* __restrict__ row_ptr, int32_t* __restrict__ slot_edge,
                                                              int average, int32_t* __restrict__ col_idx, float* __restrict__ val)
 {
-    for (int64_t row = blockIdx.x; row < N; row += gridDim.x) {
+    const int n_long = long_list[0];
+    for (int li = blockIdx.x; li < n_long; li += gridDim.x) {
+        const int64_t row = long_list[1 + li];
         const int32_t b = row_ptr[row];
         const int n = row_ptr[row + 1] - b;
-        if (n <= CSR_LONG_ROW) continue;     // uniform over the CTA
         int32_t* a = slot_edge + b;
         int m = 1;
         while (m < n) m <<= 1;
@@ -209,7 +213,7 @@ size_t s2v_build_n2n_csr_scratch_bytes(int64_t num_nodes, int64_t num_edges)
     if (num_nodes < 0 || num_edges < 0) return 0;
     const size_t blocks = (size_t)((num_nodes + SCAN_BLOCK - 1) / SCAN_BLOCK);
     return up256(sizeof(int32_t) * (size_t)num_nodes) + up256(sizeof(int32_t) * (size_t)num_edges) +
-           up256(sizeof(int32_t) * (blocks + 1)) + 256;
+           up256(sizeof(int32_t) * (blocks + 1)) + up256(sizeof(int32_t) * ((size_t)num_edges / CSR_LONG_ROW + 2)) + 256;
 }
 
 int s2v_build_n2n_csr_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_nodes, int64_t num_edges, const int32_t* edge_src,
@@ -233,7 +237,9 @@ int s2v_build_n2n_csr_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_nodes, in
     int32_t* slot_edge = reinterpret_cast<int32_t*>(p + up256(sizeof(int32_t) * (size_t)N));
     int32_t* block_sum = reinterpret_cast<int32_t*>(p + up256(sizeof(int32_t) * (size_t)N) + up256(sizeof(int32_t) * (size_t)E));
     const int num_blocks = (int)((N + SCAN_BLOCK - 1) / SCAN_BLOCK);
+    int32_t* long_list = reinterpret_cast<int32_t*>(reinterpret_cast<unsigned char*>(block_sum) + up256(sizeof(int32_t) * ((size_t)num_blocks + 1)));
     S2V_CUDA_OK(ctx, cudaMemsetAsync(cnt, 0, sizeof(int32_t) * (size_t)N, st));
+    S2V_CUDA_OK(ctx, cudaMemsetAsync(long_list, 0, sizeof(int32_t), st));
     if (E > 0) {
         csr_count_kernel<<<grid_for(ctx, E, 256, 8), 256, 0, st>>>(N, E, edge_src, edge_dst, cnt, ctx->dstatus_dev);
         S2V_CHECK_LAUNCH(ctx, "csr_count_kernel");
@@ -242,14 +248,14 @@ int s2v_build_n2n_csr_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_nodes, in
     S2V_CHECK_LAUNCH(ctx, "csr_scan_blocks_kernel");
     csr_scan_totals_kernel<<<1, SCAN_THREADS, 0, st>>>(num_blocks, block_sum);
     S2V_CHECK_LAUNCH(ctx, "csr_scan_totals_kernel");
-    csr_scan_add_kernel<<<num_blocks, SCAN_THREADS, 0, st>>>(N, num_blocks, block_sum, row_ptr, cnt);
+    csr_scan_add_kernel<<<num_blocks, SCAN_THREADS, 0, st>>>(N, num_blocks, block_sum, row_ptr, cnt, long_list);
     S2V_CHECK_LAUNCH(ctx, "csr_scan_add_kernel");
     if (E > 0) {
         csr_place_kernel<<<grid_for(ctx, E, 256, 8), 256, 0, st>>>(N, E, edge_src, edge_dst, row_ptr, cnt, slot_edge);
         S2V_CHECK_LAUNCH(ctx, "csr_place_kernel");
         csr_rank_kernel<<<grid_for(ctx, E, 256, 8), 256, 0, st>>>(N, E, edge_src, edge_dst, row_ptr, slot_edge, average, col_idx, val);
         S2V_CHECK_LAUNCH(ctx, "csr_rank_kernel");
-        csr_long_rows_kernel<<<grid_for(ctx, N, 1, 2), 1024, 0, st>>>(N, edge_src, row_ptr, slot_edge, average, col_idx, val);
+        csr_long_rows_kernel<<<grid_for(ctx, E / CSR_LONG_ROW + 1, 1, 1), 1024, 0, st>>>(long_list, edge_src, row_ptr, slot_edge, average, col_idx, val);
         S2V_CHECK_LAUNCH(ctx, "csr_long_rows_kernel");
     }
     return S2V_OK;

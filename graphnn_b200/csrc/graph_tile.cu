@@ -49,8 +49,12 @@ namespace
 
 constexpr int GT_NODES = 128;                    // node rows per tile
 constexpr int GT_D = 128;                        // latent dimension = MMA M
-constexpr int GT_WORKERS = 16;
+constexpr int GT_WORKERS = 16;                   // worker warps: four per tensor-memory lane quarter (measured: 16 warps 0.83 ms, 8 warps
+                                                 // 1.01 ms per 16,384-graph batch: the kernel lives on warps that hide each other's waits)
 constexpr int GT_THREADS = (GT_WORKERS + 1) * 32;
+constexpr int GT_ROWS_PER_WARP = GT_NODES / GT_WORKERS;          // gather rows of a worker: 16
+constexpr int GT_PASSES = GT_ROWS_PER_WARP / 4;                  // four rows side by side per pass
+constexpr int GT_NODES_PER_SLOT = GT_NODES / (GT_WORKERS / 4);   // epilogue node columns of a worker: 64
 constexpr int GT_CHUNKS = 4;                     // K chunks of 32 features (one swizzle line per node row)
 constexpr int GT_SBUF = 2;                       // operand buffers
 constexpr int GT_LC_CAP = 1536;                  // non-zeros of a tile cached in shared memory
@@ -58,7 +62,7 @@ constexpr size_t GT_S_BYTES = 256 * 128;         // one operand buffer: 128 head
 constexpr size_t GT_H_BYTES = sizeof(float) * GT_NODES * GT_D;
 // per-stream arrays
 constexpr size_t GT_ST_LVAL = 0;
-constexpr size_t GT_ST_REC = GT_ST_LVAL + sizeof(float) * GT_LC_CAP;     // uint4 per row: neighbour offsets, degree, first non-zero
+constexpr size_t GT_ST_REC = GT_ST_LVAL + sizeof(float) * GT_LC_CAP;     // uint4 per row: shared-memory offsets of its first four neighbour rows
 constexpr size_t GT_ST_LRP = GT_ST_REC + 16 * GT_NODES;
 constexpr size_t GT_ST_TAGS = GT_ST_LRP + sizeof(int) * 132;
 constexpr size_t GT_ST_GOFF = GT_ST_TAGS + sizeof(int) * GT_NODES;
@@ -68,7 +72,8 @@ constexpr size_t GT_ST_BYTES = (GT_ST_LCOL + GT_LC_CAP + 15) / 16 * 16;
 constexpr size_t GT_OFF_S = 0;
 constexpr size_t GT_OFF_H = GT_OFF_S + GT_SBUF * GT_S_BYTES;
 constexpr size_t GT_OFF_ST = GT_OFF_H + 2 * GT_H_BYTES;
-constexpr size_t GT_OFF_BAR = GT_OFF_ST + 2 * GT_ST_BYTES;
+constexpr size_t GT_OFF_ZERO = GT_OFF_ST + 2 * GT_ST_BYTES;              // one row of zeros: the "neighbour" of unused gather slots
+constexpr size_t GT_OFF_BAR = GT_OFF_ZERO + sizeof(float) * GT_D;
 constexpr size_t GT_SMEM_BYTES = GT_OFF_BAR + 128 + 1024;                 // + barriers/flags + alignment slack
 static_assert(GT_SMEM_BYTES <= 227 * 1024, "shared memory map exceeds the 227 KB a CTA may use");
 // tensor memory columns
@@ -230,30 +235,35 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    if (threadIdx.x < GT_D) reinterpret_cast<float*>(smem + GT_OFF_ZERO)[threadIdx.x] = 0.f;
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    const int q = warp & 3, j = (warp >> 2) & 3;            // tensor-memory lane quarter, slot within it
+    const int q = warp & 3, j = (warp >> 2) % (GT_WORKERS / 4);   // tensor-memory lane quarter, slot within it
     const uint32_t lane_base = (uint32_t)(32 * q) << 16;
     if (warp < GT_WORKERS) {
         // W^T into tensor memory: lane m = output feature, column k = input feature; A[m][k] = W[k][m].
-        // Worker (q, j): features 32q..32q+31, k in [32j, 32j+32).  Loads are coalesced across the lanes.
+        // Worker (q, j): features 32q..32q+31, a block of GT_NODES_PER_SLOT values of k.  Loads are coalesced across the lanes.
         const int m = 32 * q + lane;
-        float wv[32];
+#pragma unroll 1
+        for (int kb = 0; kb < GT_NODES_PER_SLOT / 32; ++kb) {
+            const int k0 = GT_NODES_PER_SLOT * j + 32 * kb;
+            float wv[32];
 #pragma unroll
-        for (int kk = 0; kk < 32; ++kk) wv[kk] = __ldg(W + (int64_t)(32 * j + kk) * GT_D + m);
+            for (int kk = 0; kk < 32; ++kk) wv[kk] = __ldg(W + (int64_t)(k0 + kk) * GT_D + m);
 #pragma unroll
-        for (int h = 0; h < 4; ++h) {
-            uint32_t hi[8], lo[8];
+            for (int h = 0; h < 4; ++h) {
+                uint32_t hi[8], lo[8];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                hi[c] = tf32_rn(wv[8 * h + c]);
-                lo[c] = tf32_rn(wv[8 * h + c] - __uint_as_float(hi[c]));
+                for (int c = 0; c < 8; ++c) {
+                    hi[c] = tf32_rn(wv[8 * h + c]);
+                    lo[c] = tf32_rn(wv[8 * h + c] - __uint_as_float(hi[c]));
+                }
+                tc_st_cols8(tmem_base + lane_base + GT_TM_WHI + (uint32_t)(k0 + 8 * h), hi);
+                tc_st_cols8(tmem_base + lane_base + GT_TM_WLO + (uint32_t)(k0 + 8 * h), lo);
             }
-            tc_st_cols8(tmem_base + lane_base + GT_TM_WHI + (uint32_t)(32 * j + 8 * h), hi);
-            tc_st_cols8(tmem_base + lane_base + GT_TM_WLO + (uint32_t)(32 * j + 8 * h), lo);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     }
@@ -268,7 +278,7 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
 
     if (warp < GT_WORKERS) {
         // =========================== worker warps ===========================
-        const int tix = threadIdx.x;                 // 0..511
+        const int tix = threadIdx.x;                 // 0 .. 32 * GT_WORKERS - 1
         const int g4 = lane >> 3, sl = lane & 7;     // gather: row within a pass of four, 16-byte piece of the 128-byte line
         const float4* __restrict__ Win4 = reinterpret_cast<const float4*>(W_in);
         uint32_t ws_phase = 0;                       // completed phases of the worker-wide barrier
@@ -332,20 +342,22 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
                     if (HAS_VAL) lval[e] = __ldg(val + base + e);
                 }
             }
-#pragma unroll
-            for (int rr = 0; rr < 8; ++rr) {
-                const int r = 8 * warp + rr;
+#pragma unroll 4
+            for (int rr = 0; rr < GT_ROWS_PER_WARP; ++rr) {
+                const int r = GT_ROWS_PER_WARP * warp + rr;
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (r < nrows) v = relu4(__ldg(Win4 + (int64_t)tc_table_row(__ldg(tags + node0 + r), num_tags, status) * 32 + lane));
                 H4s[r * 32 + lane] = v;
             }
             if (!wsync(30)) return false;
-            // gather record of row r: byte offsets (row * 512) of its first four neighbours, its degree, its first non-zero
+            // gather record of row r: offsets (from the shared-memory base) of the rows of its first four neighbours;
+            // unused slots point at the row of zeros, so the gather needs no test per slot
             if (tix < GT_NODES) {
                 const int beg = lrp[tix], deg = lrp[tix + 1] - beg;
-                uint32_t off[4] = {0u, 0u, 0u, 0u};
+                uint32_t off[4];
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
+                for (int u = 0; u < 4; ++u) {
+                    off[u] = (uint32_t)GT_OFF_ZERO;
                     if (u < deg) {
                         int c;
                         if (cached) c = lcol[beg + u];
@@ -357,62 +369,87 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
                                 c = 0;
                             }
                         }
-                        off[u] = (uint32_t)c * 512u;
+                        off[u] = (uint32_t)(GT_OFF_H + (size_t)s * GT_H_BYTES) + (uint32_t)c * 512u;
                     }
-                rec[tix] = make_uint4(off[0] | (off[1] << 16), off[2] | (off[3] << 16), (uint32_t)deg, (uint32_t)beg);
+                }
+                rec[tix] = make_uint4(off[0], off[1], off[2], off[3]);
             }
             return wsync(35);
         };
 
-        // ---- one chunk of S = A * H of stream s's tile: gather, split, store as MMA operand
+        // ---- my gather rows of stream s (rows GT_ROWS_PER_WARP*warp + 4p + g4): neighbour offsets, store offset, extent
+        uint32_t na[GT_PASSES][4], da[GT_PASSES];
+        int gbeg[GT_PASSES], gdeg[GT_PASSES];
+        bool long_rows = false;        // warp-uniform: some row of mine has more than four neighbours
+        auto load_rows = [&](int s) {
+            unsigned char* sb = stream_base(s);
+            const uint4* rec = reinterpret_cast<const uint4*>(sb + GT_ST_REC);
+            const int* lrp = reinterpret_cast<const int*>(sb + GT_ST_LRP);
+            bool lng = false;
+#pragma unroll
+            for (int p = 0; p < GT_PASSES; ++p) {
+                const int r = GT_ROWS_PER_WARP * warp + 4 * p + g4;
+                const uint4 rc = rec[r];
+                na[p][0] = rc.x + (uint32_t)sl * 16u; na[p][1] = rc.y + (uint32_t)sl * 16u;
+                na[p][2] = rc.z + (uint32_t)sl * 16u; na[p][3] = rc.w + (uint32_t)sl * 16u;
+                // row r of the K-major 128-byte-swizzle layout: 16-byte piece sl sits at sl ^ (r & 7)
+                da[p] = (uint32_t)GT_OFF_S + (uint32_t)r * 128u + (uint32_t)((sl ^ (r & 7)) * 16);
+                gbeg[p] = lrp[r];
+                gdeg[p] = lrp[r + 1] - gbeg[p];
+                lng |= gdeg[p] > 4;
+            }
+            long_rows = __any_sync(0xffffffffu, lng);
+        };
+
+        // ---- one chunk (32 features) of S = A * H of stream s's tile: gather, split, store as MMA operand
         auto gather_chunk = [&](int s, int c) -> bool {
             const uint32_t b = jobs & 1u;
             if (jobs >= (uint32_t)GT_SBUF &&
                 !tc_wait(bar(GB_EMPTY0 + b), ((jobs >> 1) - 1u) & 1u, abort_flag, status, 36))
                 return false;
-            unsigned char* sb = stream_base(s);
-            const uint4* rec = reinterpret_cast<const uint4*>(sb + GT_ST_REC);
-            const unsigned char* hb = stream_h(s) + (size_t)c * 128 + (size_t)sl * 16;
-            unsigned char* sbuf = smem + GT_OFF_S + (size_t)b * GT_S_BYTES;
+            const unsigned char* hb = smem + (size_t)c * 128;
+            unsigned char* sbuf = smem + (size_t)b * GT_S_BYTES;
 #pragma unroll
-            for (int p = 0; p < 2; ++p) {
-                const int r = 8 * warp + 4 * p + g4;
-                const uint4 rc = rec[r];
-                const int deg = (int)rc.z;
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                float4 v[4];
-                const uint32_t off[4] = {rc.x & 0xffffu, rc.x >> 16, rc.y & 0xffffu, rc.y >> 16};
+            for (int p = 0; p < GT_PASSES; ++p) {
+                const float4 v0 = *reinterpret_cast<const float4*>(hb + na[p][0]);
+                const float4 v1 = *reinterpret_cast<const float4*>(hb + na[p][1]);
+                const float4 v2 = *reinterpret_cast<const float4*>(hb + na[p][2]);
+                const float4 v3 = *reinterpret_cast<const float4*>(hb + na[p][3]);
+                float4 acc;
+                if (HAS_VAL) {
+                    unsigned char* sb = stream_base(s);
+                    const int* info = reinterpret_cast<const int*>(sb + GT_ST_INFO);
+                    const bool cached = info[5] <= GT_LC_CAP;
+                    const float* lv = reinterpret_cast<const float*>(sb + GT_ST_LVAL) + gbeg[p];
+                    const float* gv = val + info[4] + gbeg[p];
+                    float a[4];
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (u < deg) v[u] = *reinterpret_cast<const float4*>(hb + off[u]);
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (u < deg) {   // adds in CSR order
-                        if (HAS_VAL) {
-                            const int* info = reinterpret_cast<const int*>(sb + GT_ST_INFO);
-                            const float a = (info[5] <= GT_LC_CAP) ? reinterpret_cast<const float*>(sb + GT_ST_LVAL)[rc.w + u]
-                                                                   : __ldg(val + info[4] + rc.w + u);
-                            acc.x = fmaf(a, v[u].x, acc.x); acc.y = fmaf(a, v[u].y, acc.y);
-                            acc.z = fmaf(a, v[u].z, acc.z); acc.w = fmaf(a, v[u].w, acc.w);
-                        } else {
-                            acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
-                        }
-                    }
-                if (deg > 4) {   // longer rows
+                    for (int u = 0; u < 4; ++u) a[u] = u < gdeg[p] ? (cached ? lv[u] : __ldg(gv + u)) : 0.f;
+                    acc = make_float4(a[0] * v0.x, a[0] * v0.y, a[0] * v0.z, a[0] * v0.w);
+                    acc.x = fmaf(a[1], v1.x, acc.x); acc.y = fmaf(a[1], v1.y, acc.y); acc.z = fmaf(a[1], v1.z, acc.z); acc.w = fmaf(a[1], v1.w, acc.w);
+                    acc.x = fmaf(a[2], v2.x, acc.x); acc.y = fmaf(a[2], v2.y, acc.y); acc.z = fmaf(a[2], v2.z, acc.z); acc.w = fmaf(a[2], v2.w, acc.w);
+                    acc.x = fmaf(a[3], v3.x, acc.x); acc.y = fmaf(a[3], v3.y, acc.y); acc.z = fmaf(a[3], v3.z, acc.z); acc.w = fmaf(a[3], v3.w, acc.w);
+                } else {   // adds in CSR order; an unused slot adds the row of zeros
+                    acc = make_float4((((v0.x + v1.x) + v2.x) + v3.x), (((v0.y + v1.y) + v2.y) + v3.y),
+                                      (((v0.z + v1.z) + v2.z) + v3.z), (((v0.w + v1.w) + v2.w) + v3.w));
+                }
+                if (long_rows && gdeg[p] > 4) {   // rows with more than four neighbours
+                    unsigned char* sb = stream_base(s);
                     const int* info = reinterpret_cast<const int*>(sb + GT_ST_INFO);
                     const int node0 = info[0], nrows = info[1], base = info[4];
                     const bool cached = info[5] <= GT_LC_CAP;
                     const unsigned char* lcol = sb + GT_ST_LCOL;
-                    for (int t = 4; t < deg; ++t) {
+                    const unsigned char* hrow = stream_h(s) + (size_t)c * 128 + (size_t)sl * 16;
+                    for (int t = 4; t < gdeg[p]; ++t) {
                         int n;
-                        if (cached) n = lcol[rc.w + t];
+                        if (cached) n = lcol[gbeg[p] + t];
                         else {
-                            n = __ldg(col_idx + base + rc.w + t) - node0;
+                            n = __ldg(col_idx + base + gbeg[p] + t) - node0;
                             if ((unsigned)n >= (unsigned)nrows) n = 0;
                         }
-                        const float4 vv = *reinterpret_cast<const float4*>(hb + (size_t)n * 512);
+                        const float4 vv = *reinterpret_cast<const float4*>(hrow + (size_t)n * 512);
                         if (HAS_VAL) {
-                            const float a = cached ? reinterpret_cast<const float*>(sb + GT_ST_LVAL)[rc.w + t] : __ldg(val + base + rc.w + t);
+                            const float a = cached ? reinterpret_cast<const float*>(sb + GT_ST_LVAL)[gbeg[p] + t] : __ldg(val + base + gbeg[p] + t);
                             acc.x = fmaf(a, vv.x, acc.x); acc.y = fmaf(a, vv.y, acc.y);
                             acc.z = fmaf(a, vv.z, acc.z); acc.w = fmaf(a, vv.w, acc.w);
                         } else {
@@ -425,10 +462,8 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
                 tc_split(acc.y, hi.y, lo.y);
                 tc_split(acc.z, hi.z, lo.z);
                 tc_split(acc.w, hi.w, lo.w);
-                // row r of the K-major 128-byte-swizzle layout: 16-byte piece sl sits at sl ^ (r & 7)
-                unsigned char* dst = sbuf + (size_t)r * 128 + (size_t)((sl ^ (r & 7)) * 16);
-                *reinterpret_cast<uint4*>(dst) = hi;
-                *reinterpret_cast<uint4*>(dst + 128 * 128) = lo;
+                *reinterpret_cast<uint4*>(sbuf + da[p]) = hi;
+                *reinterpret_cast<uint4*>(sbuf + da[p] + 128 * 128) = lo;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // my stores -> visible to the tensor core
             __syncwarp();
@@ -437,33 +472,45 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
             return true;
         };
 
+        // ---- X term of the epilogue of stream s: feature = my lane, nodes GT_NODES_PER_SLOT*j ..
+        float xv[GT_NODES_PER_SLOT];
+        auto fetch_x = [&](int s) {
+            const int4* tag4 = reinterpret_cast<const int4*>(reinterpret_cast<const int*>(stream_base(s) + GT_ST_TAGS) + GT_NODES_PER_SLOT * j);
+            const float* xcol = W_in + 32 * q + lane;
+#pragma unroll
+            for (int i4 = 0; i4 < GT_NODES_PER_SLOT / 4; ++i4) {
+                const int4 t = tag4[i4];
+                xv[4 * i4 + 0] = __ldg(xcol + (int64_t)t.x * GT_D);
+                xv[4 * i4 + 1] = __ldg(xcol + (int64_t)t.y * GT_D);
+                xv[4 * i4 + 2] = __ldg(xcol + (int64_t)t.z * GT_D);
+                xv[4 * i4 + 3] = __ldg(xcol + (int64_t)t.w * GT_D);
+            }
+        };
         // ---- accumulator of the oldest open level-job (stream s) -> registers -> + X, ReLU -> the stream's H tile
         auto drain_epilogue = [&](int s) -> bool {
-            unsigned char* sb = stream_base(s);
-            const int* tag_s = reinterpret_cast<const int*>(sb + GT_ST_TAGS);
             float* Hs = reinterpret_cast<float*>(stream_h(s));
-            float xv[32];   // feature = my lane, nodes 32j .. 32j+31
-#pragma unroll
-            for (int i = 0; i < 32; ++i) xv[i] = __ldg(W_in + (int64_t)tag_s[32 * j + i] * GT_D + 32 * q + lane);
+            fetch_x(s);     // in flight across the wait below
             if (!tc_wait(bar(GB_ACC_FULL), drained & 1u, abort_flag, status, 31)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t acc_addr = tmem_base + lane_base + GT_TM_ACC + (uint32_t)(32 * j);
-            float z[32];
+            const uint32_t acc_addr = tmem_base + lane_base + GT_TM_ACC + (uint32_t)(GT_NODES_PER_SLOT * j);
+            float* hcol = Hs + (GT_NODES_PER_SLOT * j) * GT_D + 32 * q + lane;
+            float z[GT_NODES_PER_SLOT];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
+            for (int h = 0; h < GT_NODES_PER_SLOT / 16; ++h) {
                 uint32_t big[16], sml[16];
                 tc_ld_cols16(acc_addr + (uint32_t)(16 * h), big);
                 tc_ld_cols16(acc_addr + 128u + (uint32_t)(16 * h), sml);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < 16; ++i) z[16 * h + i] = __uint_as_float(big[i]) + __uint_as_float(sml[i]);
+                for (int i = 0; i < 16; ++i) z[16 * h + i] = (__uint_as_float(big[i]) + __uint_as_float(sml[i])) + xv[16 * h + i];
             }
+            // my block of the accumulator is in registers: hand the accumulator over to the next level-job's MMAs
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) tc_mbar_arrive(bar(GB_ACC_READ));   // the next level-job's MMAs may overwrite the accumulator
+            if (lane == 0) tc_mbar_arrive(bar(GB_ACC_READ));
             ++drained;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) Hs[(32 * j + i) * GT_D + 32 * q + lane] = relu_ref(z[i] + xv[i]);
+            for (int i = 0; i < GT_NODES_PER_SLOT; ++i) hcol[i * GT_D] = relu_ref(z[i]);
             return true;
         };
 
@@ -491,8 +538,8 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
             }
             if (embed_out) {
 #pragma unroll
-                for (int rr = 0; rr < 8; ++rr) {
-                    const int r = 8 * warp + rr;
+                for (int rr = 0; rr < GT_ROWS_PER_WARP; ++rr) {
+                    const int r = GT_ROWS_PER_WARP * warp + rr;
                     if (r < nrows) reinterpret_cast<float4*>(embed_out)[(int64_t)(node0 + r) * 32 + lane] = H4s[r * 32 + lane];
                 }
             }
@@ -509,6 +556,7 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
             const int s = k & 1;
             const bool have = (k >> 1) < (s == 0 ? n_lj0 : n_lj1);
             if (have) {
+                load_rows(s);
                 if (!gather_chunk(s, 0) || !gather_chunk(s, 1)) { alive = false; break; }
             }
             bool tile_finished = false;

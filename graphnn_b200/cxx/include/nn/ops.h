@@ -327,6 +327,90 @@ protected:
     }
 };
 
+// ---- edge-level matrices (src/nn/msg_pass.cpp:72-152): embeddings that live on edges (loopy BP style models)
+namespace detail
+{
+inline void edge_arrays(GraphStruct* graph, std::vector<int32_t>& src, std::vector<int32_t>& dst)
+{
+    src.resize(graph->num_edges);
+    dst.resize(graph->num_edges);
+    for (size_t e = 0; e < graph->edge_list.size(); ++e) {
+        src[e] = graph->edge_list[e].first;
+        dst[e] = graph->edge_list[e].second;
+    }
+}
+}  // namespace detail
+
+// [N x E]: row i = indices of the edges into node i, in the order they were added
+template <typename mode, typename Dtype>
+class Edge2NodeMsgPass : public IMsgPass<mode, Dtype>
+{
+public:
+    S2V_SPARSE_OUT("Edge2NodeMsgPass")
+    Edge2NodeMsgPass(std::string _name, bool _average = false) : IMsgPass<mode, Dtype>(_name, _average) {}
+
+protected:
+    void InitCPUWeight(GraphStruct* graph) override
+    {
+        auto& w = this->cpu_weight;
+        w.Reshape({graph->num_nodes, graph->num_edges});
+        w.ResizeSp(graph->num_edges, graph->num_nodes + 1);
+        detail::edge_arrays(graph, src_, dst_);
+        const int rc = s2v_build_e2n_csr_host(graph->num_nodes, graph->num_edges, src_.data(), dst_.data(), this->average,
+                                              w.data->row_ptr, w.data->col_idx, w.data->val);
+        ASSERT(rc == 0, "s2v_build_e2n_csr_host: " << s2v_status_str(rc));
+    }
+    std::vector<int32_t> src_, dst_;
+};
+
+// [E x N]: row e = the source node of edge e
+template <typename mode, typename Dtype>
+class Node2EdgeMsgPass : public IMsgPass<mode, Dtype>
+{
+public:
+    S2V_SPARSE_OUT("Node2EdgeMsgPass")
+    Node2EdgeMsgPass(std::string _name, bool _average = false) : IMsgPass<mode, Dtype>(_name, _average) {}
+
+protected:
+    void InitCPUWeight(GraphStruct* graph) override
+    {
+        auto& w = this->cpu_weight;
+        w.Reshape({graph->num_edges, graph->num_nodes});
+        w.ResizeSp(graph->num_edges, graph->num_edges + 1);
+        detail::edge_arrays(graph, src_, dst_);
+        const int rc = s2v_build_n2e_csr_host(graph->num_nodes, graph->num_edges, src_.data(), w.data->row_ptr, w.data->col_idx,
+                                              w.data->val);
+        ASSERT(rc == 0, "s2v_build_n2e_csr_host: " << s2v_status_str(rc));
+    }
+    std::vector<int32_t> src_, dst_;
+};
+
+// [E x E]: row e = (from -> to): the edges into `from` other than the ones coming back from `to`
+template <typename mode, typename Dtype>
+class Edge2EdgeMsgPass : public IMsgPass<mode, Dtype>
+{
+public:
+    S2V_SPARSE_OUT("Edge2EdgeMsgPass")
+    Edge2EdgeMsgPass(std::string _name, bool _average = false) : IMsgPass<mode, Dtype>(_name, _average) {}
+
+protected:
+    void InitCPUWeight(GraphStruct* graph) override
+    {
+        auto& w = this->cpu_weight;
+        detail::edge_arrays(graph, src_, dst_);
+        int64_t nnz = 0;
+        rp_.resize(graph->num_edges + 1);
+        int rc = s2v_build_e2e_csr_host(graph->num_nodes, graph->num_edges, src_.data(), dst_.data(), rp_.data(), nullptr, nullptr, 0, &nnz);
+        ASSERT(rc == 0, "s2v_build_e2e_csr_host (size query): " << s2v_status_str(rc));
+        w.Reshape({graph->num_edges, graph->num_edges});
+        w.ResizeSp((size_t)nnz, graph->num_edges + 1);
+        rc = s2v_build_e2e_csr_host(graph->num_nodes, graph->num_edges, src_.data(), dst_.data(), w.data->row_ptr, w.data->col_idx,
+                                    w.data->val, nnz, &nnz);
+        ASSERT(rc == 0, "s2v_build_e2e_csr_host: " << s2v_status_str(rc));
+    }
+    std::vector<int32_t> src_, dst_, rp_;
+};
+
 // ---- fused forms (no counterpart in the reference; registered through the same af<>) --------
 // operands {A (CSR), H, W, X}: out = ReLU((A*H)*W + X) in one kernel
 template <typename mode, typename Dtype>

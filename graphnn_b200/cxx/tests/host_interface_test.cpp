@@ -104,6 +104,22 @@ static int test_msg_pass_matrices()
     const int want_srp[] = {0, 3, 5}, want_sci[] = {0, 1, 2, 3, 4};
     CHECK(S.rows() == 2 && S.cols() == 5 && S.data->nnz == 5);
     CHECK(!memcmp(S.data->row_ptr, want_srp, sizeof(want_srp)) && !memcmp(S.data->col_idx, want_sci, sizeof(want_sci)));
+    // the edge-level matrices of the same graph (worked out by hand from the in-edge lists above)
+    auto e2n = af<Edge2NodeMsgPass<CPU, float>>(fg, {gv});
+    auto e2n_avg = af<Edge2NodeMsgPass<CPU, float>>(fg, {gv}, true);
+    auto n2e = af<Node2EdgeMsgPass<CPU, float>>(fg, {gv});
+    auto e2e = af<Edge2EdgeMsgPass<CPU, float>>(fg, {gv});
+    fg.FeedForward({e2n, e2n_avg, n2e, e2e}, feed, Phase::TEST);
+    const int want_e2n_ci[] = {1, 6, 0, 3, 2, 5, 4};
+    CHECK(e2n->value.rows() == 5 && e2n->value.cols() == 7 && e2n->value.data->nnz == 7);
+    CHECK(!memcmp(e2n->value.data->row_ptr, want_rp, sizeof(want_rp)) && !memcmp(e2n->value.data->col_idx, want_e2n_ci, sizeof(want_e2n_ci)));
+    CHECK(e2n_avg->value.data->val[1] == 0.5f && e2n_avg->value.data->val[6] == 1.0f);
+    const int want_n2e_ci[] = {0, 1, 1, 2, 3, 4, 2};
+    CHECK(n2e->value.rows() == 7 && n2e->value.cols() == 5 && !memcmp(n2e->value.data->col_idx, want_n2e_ci, sizeof(want_n2e_ci)));
+    CHECK(n2e->value.data->row_ptr[7] == 7 && n2e->value.data->row_ptr[3] == 3);
+    const int want_e2e_rp[] = {0, 1, 2, 3, 3, 3, 3, 4}, want_e2e_ci[] = {6, 3, 0, 2};
+    CHECK(e2e->value.rows() == 7 && e2e->value.cols() == 7 && e2e->value.data->nnz == 4);
+    CHECK(!memcmp(e2e->value.data->row_ptr, want_e2e_rp, sizeof(want_e2e_rp)) && !memcmp(e2e->value.data->col_idx, want_e2e_ci, sizeof(want_e2e_ci)));
     // a smaller batch through the same factors: the tensors shrink logically, capacity is kept
     g.Resize(1, 2);
     g.AddNode(0, 0);

@@ -72,8 +72,9 @@ typedef enum s2v_option {
                                         the environment variable S2V_VALIDATE_HOST=0 sets the default to 0) */
     S2V_OPT_LEVEL_TC = 2,            /* tcgen05 level kernel: 0 never, 1 automatic (default), 2 whenever the shape allows
                                         (default from S2V_LEVEL_TC) */
-    S2V_OPT_GRAPH_TILES = 3          /* whole-classifier tile kernel for batches of small graphs: 0 off, 1 automatic
-                                        (default; default from S2V_GRAPH_TILES) */
+    S2V_OPT_GRAPH_TILES = 3          /* whole-classifier tile kernel (s2v_graph_tiles_f32) inside s2v_forward_f32 for batches of
+                                        small graphs: 0 off (default: on the measured configurations the per-level kernels are
+                                        slightly faster), 1 whenever the batch allows (default from S2V_GRAPH_TILES) */
 } s2v_option;
 int s2v_ctx_set_option(s2v_ctx* ctx, int option, int value);
 /* Diagnostic, no counterpart in the reference: launches a two-warp kernel whose bounded barrier waits (the
@@ -239,9 +240,9 @@ typedef struct s2v_batch {
     const int32_t* tags;        /* [N] one-hot node types, or NULL when x_dense is given */
     const float* x_dense;       /* [N x F] or NULL */
     int32_t max_graph_nodes;    /* node count of the largest graph of the batch, or 0 if unknown.  Device entry
-                                   points cannot read graph_ptr on the host; with 1..128 here (and d = 128, tags)
-                                   s2v_forward_f32 runs the whole classifier as one tile kernel that keeps the
-                                   embeddings in shared memory.  A value that understates the truth is reported
+                                   points cannot read graph_ptr on the host; with 1..128 here (and d = 128, tags,
+                                   S2V_OPT_GRAPH_TILES on) s2v_forward_f32 runs the whole classifier as one tile kernel
+                                   that keeps the embeddings in shared memory.  A value that understates the truth is reported
                                    through the status word (S2V_ERR_UNSUPPORTED) and the oversized graphs are
                                    truncated.  s2v_infer_host_f32 computes it itself. */
 } s2v_batch;
@@ -279,6 +280,21 @@ int s2v_forward_static_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* mod
  * `average` != 0 writes 1/in-degree.  All pointers are HOST pointers. */
 int s2v_build_n2n_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* edge_src,
                            const int32_t* edge_dst, int average, int32_t* row_ptr, int32_t* col_idx, float* val);
+/* The other message-passing matrices of the reference (edge-level embeddings, e.g. loopy belief propagation),
+ * built from the same edge list (edge e = edge_src[e] -> edge_dst[e], in AddEdge order); HOST pointers.
+ *   edge-to-node [N x E]: row y lists the INDICES of the edges into y in insertion order, val 1 or 1/in-degree
+ *                         (Edge2NodeMsgPass::InitCPUWeight, src/nn/msg_pass.cpp:72-94);
+ *   node-to-edge [E x N]: row e has the single entry edge_src[e], val 1 (Node2EdgeMsgPass, msg_pass.cpp:98-116);
+ *   edge-to-edge [E x E]: row e = (from -> to) lists the indices of the edges into `from` except those coming
+ *                         from `to`, in insertion order, val 1 (Edge2EdgeMsgPass, msg_pass.cpp:120-152).
+ * The number of entries of the edge-to-edge matrix is not known in advance: call once with col_idx = NULL to get
+ * *nnz_out, then with arrays of that capacity (S2V_ERR_WORKSPACE if capacity is too small; *nnz_out is always set). */
+int s2v_build_e2n_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* edge_src, const int32_t* edge_dst,
+                           int average, int32_t* row_ptr, int32_t* col_idx, float* val);
+int s2v_build_n2e_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* edge_src, int32_t* row_ptr, int32_t* col_idx,
+                           float* val);
+int s2v_build_e2e_csr_host(int64_t num_nodes, int64_t num_edges, const int32_t* edge_src, const int32_t* edge_dst,
+                           int32_t* row_ptr, int32_t* col_idx, float* val, int64_t capacity, int64_t* nnz_out);
 /* Checks a host CSR: row_ptr[0]==0, monotone, row_ptr[m]==nnz, 0 <= col_idx < k. */
 int s2v_validate_csr_host(int64_t m, int64_t k, int64_t nnz, const int32_t* row_ptr, const int32_t* col_idx);
 

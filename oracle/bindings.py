@@ -92,6 +92,37 @@ def forward(batch, impl: str = "oracle", iters: int = 1, want_levels: bool = Tru
     return out
 
 
+def msgpass_matrix(batch, which: str, impl: str = "oracle", average: bool = False):
+    """One of the message-passing matrices of a batch: which in {"n2n", "e2n", "n2e", "e2e", "sub"}.  With
+    impl="reference" it is what the reference's own factor builds; with "oracle" the C restatement
+    (edge-level matrices only).  Returns (row_ptr, col_idx, val)."""
+    lib = _lib(impl)
+    code = {"n2n": 0, "e2n": 1, "n2e": 2, "e2e": 3, "sub": 4}[which]
+    G, N, E = batch.num_graphs, batch.num_nodes, batch.num_edges
+    rows = {"n2n": N, "e2n": N, "n2e": E, "e2e": E, "sub": G}[which]
+    npg = np.ascontiguousarray(batch.nodes_per_graph, np.int32)
+    es = np.ascontiguousarray(batch.edge_src, np.int32)
+    ed = np.ascontiguousarray(batch.edge_dst, np.int32)
+    rp = np.zeros(rows + 1, np.int32)
+    cap = 1
+    for _ in range(2):      # first call sizes the arrays
+        ci, val = np.zeros(cap, np.int32), np.zeros(cap, np.float32)
+        if impl == "oracle":
+            assert which in ("e2n", "n2e", "e2e")
+            lib.oracle_build_edge_csr.restype = C.c_int64
+            nnz = lib.oracle_build_edge_csr(C.c_int(code), C.c_int64(N), C.c_int64(E), _p(es, _i32p), _p(ed, _i32p), C.c_int(int(average)),
+                                            _p(rp, _i32p), _p(ci, _i32p), _p(val, _f32p), C.c_int64(cap))
+        else:
+            nnz = lib.ref_msgpass_matrix(C.c_int(code), C.c_int(int(average)), C.c_int(G), _p(npg, _i32p), C.c_int(E), _p(es, _i32p),
+                                         _p(ed, _i32p), _p(rp, _i32p), _p(ci, _i32p), _p(val, _f32p), C.c_int(cap))
+        if nnz < 0:
+            raise RuntimeError(f"{impl} msgpass_matrix failed with status {nnz}")
+        if nnz <= cap:
+            break
+        cap = int(nnz)
+    return rp, ci[:nnz], val[:nnz]
+
+
 def level(prob, impl: str = "oracle", iters: int = 1, rows: int | None = None):
     """One level; `rows` limits the computation to the first `rows` output rows (a bounded sample)."""
     lib = _lib(impl)

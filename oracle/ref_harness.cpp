@@ -17,6 +17,8 @@
  *                     MatMul(sparse A, H) -> MatMul(., W) -> ElewiseAdd(., X) -> ReLU
  *                     (kernel_mean_field.cpp:38-41) on caller-supplied CSR.
  *
+ *   ref_msgpass_matrix : any of the five message-passing matrices as the reference's own factor builds it.
+ *
  * Both return the per-iteration wall time of FeedForward so the same binary is
  * the timed CPU baseline.  The built library lives in oracle/_ref/ and is never
  * linked into, or loaded by, the product.
@@ -292,6 +294,51 @@ int ref_level_forward(int n_rows, int n_src, int nnz, const int* row_ptr, const 
     }
     copy_out(out, result->value);
     return 0;
+}
+
+/*
+ * The message-passing matrices of a graph as the reference's own factors build them
+ * (Node2Node / Edge2Node / Node2Edge / Edge2Edge / SubgraphMsgPass::InitCPUWeight, src/nn/msg_pass.cpp:46-177),
+ * with the factors' `average` flag.  which: 0 n2n, 1 e2n, 2 n2e, 3 e2e, 4 subgraph.  Returns nnz (or a negative
+ * value); row_ptr needs rows+1 entries, col_idx / val `capacity` entries (nothing beyond capacity is written).
+ */
+int ref_msgpass_matrix(int which, int average, int G, const int* nodes_per_graph, int E, const int* edge_src, const int* edge_dst,
+                       int* row_ptr, int* col_idx, float* val, int capacity)
+{
+    if (G <= 0) return -1;
+    size_t N = 0;
+    for (int g = 0; g < G; ++g) N += nodes_per_graph[g];
+    GraphStruct graph;
+    graph.Resize(G, N);
+    int node = 0;
+    for (int g = 0; g < G; ++g)
+        for (int j = 0; j < nodes_per_graph[g]; ++j) graph.AddNode(g, node++);
+    for (int e = 0; e < E; ++e) graph.AddEdge(e, edge_src[e], edge_dst[e]);
+
+    FactorGraph fg;
+    auto gvar = add_const<GraphVar>(fg, "graph", true);
+    std::shared_ptr<SpTensorVar<mode, Dtype>> out;
+    switch (which) {
+        case 0: out = af<Node2NodeMsgPass<mode, Dtype>>(fg, {gvar}, average != 0); break;
+        case 1: out = af<Edge2NodeMsgPass<mode, Dtype>>(fg, {gvar}, average != 0); break;
+        case 2: out = af<Node2EdgeMsgPass<mode, Dtype>>(fg, {gvar}, average != 0); break;
+        case 3: out = af<Edge2EdgeMsgPass<mode, Dtype>>(fg, {gvar}, average != 0); break;
+        case 4: out = af<SubgraphMsgPass<mode, Dtype>>(fg, {gvar}, average != 0); break;
+        default: return -1;
+    }
+    std::map<std::string, void*> feed;
+    feed["graph"] = &graph;
+    std::vector<std::shared_ptr<Variable>> targets;
+    targets.push_back(out);
+    fg.FeedForward(targets, feed, Phase::TEST);
+    auto& M = out->value;
+    const int nnz = (int)M.data->nnz;
+    const size_t rows = M.rows();
+    if (row_ptr) std::memcpy(row_ptr, M.data->row_ptr, sizeof(int) * (rows + 1));
+    const int n = nnz < capacity ? nnz : capacity;
+    if (col_idx) std::memcpy(col_idx, M.data->col_idx, sizeof(int) * n);
+    if (val) std::memcpy(val, M.data->val, sizeof(float) * n);
+    return nnz;
 }
 
 }  // extern "C"

@@ -66,6 +66,70 @@ int64_t oracle_build_n2n_csr(int64_t N, int64_t E, const int32_t* edge_src, cons
 }
 
 /*
+ * The edge-level message-passing matrices (src/nn/msg_pass.cpp:72-152), restated with per-node lists
+ * of (edge index, source) pairs kept in insertion order exactly like GraphStruct::in_edges
+ * (src/util/graph_struct.cpp:62-70).  which: 1 edge-to-node [N x E], 2 node-to-edge [E x N],
+ * 3 edge-to-edge [E x E].  Returns nnz; col_idx / val receive at most `capacity` entries.
+ */
+int64_t oracle_build_edge_csr(int which, int64_t N, int64_t E, const int32_t* edge_src, const int32_t* edge_dst, int average,
+                              int32_t* row_ptr, int32_t* col_idx, float* val, int64_t capacity)
+{
+    /* in_edges as linked lists: head/tail per node, next per edge */
+    int32_t* first = (int32_t*)malloc(sizeof(int32_t) * (size_t)(N > 0 ? N : 1));
+    int32_t* last = (int32_t*)malloc(sizeof(int32_t) * (size_t)(N > 0 ? N : 1));
+    int32_t* next = (int32_t*)malloc(sizeof(int32_t) * (size_t)(E > 0 ? E : 1));
+    int32_t* count = (int32_t*)calloc((size_t)(N > 0 ? N : 1), sizeof(int32_t));
+    for (int64_t i = 0; i < N; ++i) first[i] = last[i] = -1;
+    for (int64_t e = 0; e < E; ++e) {   /* AddEdge(e, x, y): in_edges[y].push_back({e, x}) */
+        const int32_t y = edge_dst[e];
+        next[e] = -1;
+        if (first[y] < 0) first[y] = (int32_t)e; else next[last[y]] = (int32_t)e;
+        last[y] = (int32_t)e;
+        count[y]++;
+    }
+    int64_t nnz = 0;
+    if (which == 1) {          /* Edge2NodeMsgPass: row i = indices of the edges into i */
+        for (int64_t i = 0; i < N; ++i) {
+            row_ptr[i] = (int32_t)nnz;
+            for (int32_t e = first[i]; e >= 0; e = next[e]) {
+                if (nnz < capacity) {
+                    val[nnz] = average ? (float)(1.0 / count[i]) : 1.0f;
+                    col_idx[nnz] = e;
+                }
+                nnz++;
+            }
+        }
+        row_ptr[N] = (int32_t)nnz;
+    } else if (which == 2) {   /* Node2EdgeMsgPass: row e = { source of edge e } */
+        for (int64_t e = 0; e < E; ++e) {
+            row_ptr[e] = (int32_t)nnz;
+            if (nnz < capacity) {
+                val[nnz] = 1.0f;
+                col_idx[nnz] = edge_src[e];
+            }
+            nnz++;
+        }
+        row_ptr[E] = (int32_t)nnz;
+    } else {                   /* Edge2EdgeMsgPass: row e = (from -> to): edges into `from` that do not come from `to` */
+        for (int64_t e = 0; e < E; ++e) {
+            row_ptr[e] = (int32_t)nnz;
+            const int32_t from = edge_src[e], to = edge_dst[e];
+            for (int32_t f = first[from]; f >= 0; f = next[f]) {
+                if (edge_src[f] == to) continue;
+                if (nnz < capacity) {
+                    val[nnz] = 1.0f;
+                    col_idx[nnz] = f;
+                }
+                nnz++;
+            }
+        }
+        row_ptr[E] = (int32_t)nnz;
+    }
+    free(first); free(last); free(next); free(count);
+    return nnz;
+}
+
+/*
  * CSR S [G x N] for graph pooling.
  * GetBatch (examples/graph_classification/include/nn_common.h:63-73) adds node
  * prefix[g]+j to subgraph g for j ascending; SubgraphMsgPass::InitCPUWeight

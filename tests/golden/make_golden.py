@@ -55,6 +55,14 @@ def main():
     ob._lib("reference").ref_save_model(os.path.join(HERE, "tiny_reference_saved.model").encode(), F, d, h, K,
                                         *[w[k].ctypes.data_as(f32p) for k in ("w_n2l", "p_node_conv", "h1_weight", "h2_weight")])
     np.savez(os.path.join(HERE, "tiny_reference_saved_weights.npz"), **w)
+    # 5. the message-passing matrices of the reference's own factors (sum and average forms) for the seed-0 batch
+    mats = {}
+    for which in ("n2n", "e2n", "n2e", "e2e", "sub"):
+        for avg in (False, True):
+            rp, ci, val = ob.msgpass_matrix(b, which, "reference", avg)
+            key = f"{which}_{'avg' if avg else 'sum'}"
+            mats[key + "_row_ptr"], mats[key + "_col_idx"], mats[key + "_val"] = rp, ci, val
+    np.savez_compressed(os.path.join(HERE, "msgpass_matrices_mutag_seed0.npz"), digest=b.digest(), **mats)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")

@@ -92,3 +92,40 @@ def test_validate_csr(lib):
     assert capi.validate_csr_host(3, 3, np.array([0, 2, 1, 3], np.int32), ci) == -4   # not monotone
     assert capi.validate_csr_host(3, 3, np.array([1, 2, 2, 3], np.int32), ci) == -4   # does not start at 0
     assert capi.validate_csr_host(3, 3, np.array([0, 2, 2, 2], np.int32), ci) == -4   # nnz mismatch
+
+
+@pytest.mark.parametrize("average", [False, True])
+def test_edge_level_msgpass_builders_match_reference_golden(lib, golden, average):
+    """Edge2Node / Node2Edge / Edge2Edge host builders against the matrices the reference's own factors built
+    (tests/golden/msgpass_matrices_mutag_seed0.npz), bit for bit; the n2n average form as well."""
+    g = golden("msgpass_matrices_mutag_seed0.npz")
+    b = synth.mutag_like(seed=0)
+    assert str(g["digest"]) == b.digest()
+    tag = "avg" if average else "sum"
+    mats = capi.build_edge_csrs_host(b.num_nodes, b.edge_src, b.edge_dst, average=average)
+    for which in ("e2n", "n2e", "e2e"):
+        rp, ci, val = mats[which]
+        assert np.array_equal(rp, g[f"{which}_{tag}_row_ptr"]), which
+        assert np.array_equal(ci, g[f"{which}_{tag}_col_idx"]), which
+        assert np.array_equal(val, g[f"{which}_{tag}_val"]), which
+    rp, ci, val = capi.build_n2n_csr_host(b.num_nodes, b.edge_src, b.edge_dst, average=average)
+    assert np.array_equal(rp, g[f"n2n_{tag}_row_ptr"]) and np.array_equal(ci, g[f"n2n_{tag}_col_idx"])
+    assert np.array_equal(val, g[f"n2n_{tag}_val"])
+
+
+def test_edge_level_builders_on_a_large_batch_and_bad_input(lib, oracle_lib):
+    b = synth.molecules_16k(seed=4, num_graphs=3000)        # large enough for the OpenMP path of the sort
+    mats = capi.build_edge_csrs_host(b.num_nodes, b.edge_src, b.edge_dst, average=True)
+    for which in ("e2n", "n2e", "e2e"):
+        want = oracle_lib.msgpass_matrix(b, which, "oracle", True)
+        assert all(np.array_equal(x, y) for x, y in zip(mats[which], want)), which
+    # a small directed graph worked out by hand: 0->1, 1->2, 2->0, 0->2.  Row e = (from -> to) keeps the edges
+    # into `from` that do not come from `to`: the last edge (0->2) loses its only candidate 2->0.
+    src = np.array([0, 1, 2, 0], np.int32)
+    dst = np.array([1, 2, 0, 2], np.int32)
+    m = capi.build_edge_csrs_host(3, src, dst)
+    assert m["e2e"][0].tolist() == [0, 1, 2, 3, 3] and m["e2e"][1].tolist() == [2, 0, 1]
+    assert m["e2n"][0].tolist() == [0, 1, 2, 4] and m["e2n"][1].tolist() == [2, 0, 1, 3]
+    assert m["n2e"][1].tolist() == [0, 1, 2, 0]
+    with pytest.raises(capi.S2VError):
+        capi.build_edge_csrs_host(3, np.array([0, 5], np.int32), np.array([1, 2], np.int32))

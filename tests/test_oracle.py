@@ -140,3 +140,22 @@ def test_loss_accuracy_tail(oracle_lib, golden):
         b = oracle_lib.loss_acc(lgs, lab, "reference")
         assert abs(a[0] - b[0]) <= 1e-5 * abs(b[0]) and a[1] == b[1]
         assert_close(a[2], b[2], "per-graph loss vs reference")
+
+
+@pytest.mark.parametrize("average", [False, True])
+def test_oracle_edge_matrices_match_golden_and_reference(oracle_lib, golden, average):
+    """The C restatement of Edge2Node / Node2Edge / Edge2Edge::InitCPUWeight against the committed output of the
+    reference's factors, and against the reference build itself when it is present."""
+    g = golden("msgpass_matrices_mutag_seed0.npz")
+    b = synth.mutag_like(seed=0)
+    tag = "avg" if average else "sum"
+    for which in ("e2n", "n2e", "e2e"):
+        rp, ci, val = oracle_lib.msgpass_matrix(b, which, "oracle", average)
+        assert np.array_equal(rp, g[f"{which}_{tag}_row_ptr"]) and np.array_equal(ci, g[f"{which}_{tag}_col_idx"])
+        assert np.array_equal(val, g[f"{which}_{tag}_val"])
+    if oracle_lib.have_reference():
+        b2 = synth.molecule_like(50, 1, 30, 5, 32, 2, 16, 2, 0.1, "uniform", seed=21)
+        for which in ("e2n", "n2e", "e2e"):
+            want = oracle_lib.msgpass_matrix(b2, which, "reference", average)
+            got = oracle_lib.msgpass_matrix(b2, which, "oracle", average)
+            assert all(np.array_equal(x, y) for x, y in zip(got, want)), which
