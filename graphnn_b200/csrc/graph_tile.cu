@@ -29,16 +29,16 @@
 //   * Epilogue: thread = output feature (tensor-memory lane), 32 node columns per worker:
 //     tcgen05.ld, large + small + W_in[tag], ReLU, back into the H tile (conflict-free 128-byte rows).
 //   * After a tile's last level the worker warps sum its graphs in node order and write Y.
-// A CTA keeps TWO tiles resident (two "streams", each with its own H tile and CSR slice) and the workers
-// run one software-pipelined program over the alternating sequence of their levels
-//     A.0  B.0  A.1  B.1 ...         step k:  gather chunks 0,1 of level-job k
-//                                             drain the accumulator of level-job k-1, its epilogue
-//                                             gather chunks 2,3 of level-job k
-//                                             (last level of a tile: pooling, then the stream's next tile)
-// so that the MMAs of one tile run while the other tile's epilogue and gathers are done: the tensor pipe,
-// not the serial chain gather -> MMA -> epilogue of one tile, bounds the time.  The single accumulator
-// (256 of the 512 tensor-memory columns; the other 256 hold W^T) is handed over by an "accumulator read"
-// barrier as soon as its values are in registers.
+// A CTA keeps TWO tiles resident (two "streams", each with its own H tile and CSR slice) and splits its sixteen
+// worker warps into two groups of eight, one per stream.  A group runs its tile through the levels on its own
+// (gather four chunks -> wait for the MMAs -> epilogue -> group barrier -> next level; pooling; next tile); the two
+// groups share the two operand buffers, the MMA-issue warp and the single accumulator (256 of the 512
+// tensor-memory columns; the other 256 hold W^T), which serve the level-jobs in the fixed order
+//     A.0  B.0  A.1  B.1 ...
+// While one group waits -- for its MMAs, for a barrier, for the global loads of its next tile -- the other group's
+// warps have work, and the tensor pipe runs one stream's MMAs during the other stream's epilogue and gathers.
+// The accumulator is handed over by an "accumulator read" barrier as soon as a group has drained it into its H
+// tile (raw sums); the X term and the ReLU are applied in a second, row-wise pass that is off the MMA's path.
 // Every wait is an mbarrier try_wait with a poll limit; on a time-out the kernel records
 // S2V_ERR_DEVICE_TIMEOUT, raises a CTA-wide flag, frees its tensor memory and returns.
 #include "common.cuh"
@@ -49,12 +49,12 @@ namespace
 
 constexpr int GT_NODES = 128;                    // node rows per tile
 constexpr int GT_D = 128;                        // latent dimension = MMA M
-constexpr int GT_WORKERS = 16;                   // worker warps: four per tensor-memory lane quarter (measured: 16 warps 0.83 ms, 8 warps
-                                                 // 1.01 ms per 16,384-graph batch: the kernel lives on warps that hide each other's waits)
+constexpr int GT_WORKERS = 16;                   // worker warps
+constexpr int GT_GROUP = 8;                      // worker warps per stream (two per tensor-memory lane quarter)
 constexpr int GT_THREADS = (GT_WORKERS + 1) * 32;
-constexpr int GT_ROWS_PER_WARP = GT_NODES / GT_WORKERS;          // gather rows of a worker: 16
-constexpr int GT_PASSES = GT_ROWS_PER_WARP / 4;                  // four rows side by side per pass
-constexpr int GT_NODES_PER_SLOT = GT_NODES / (GT_WORKERS / 4);   // epilogue node columns of a worker: 64
+constexpr int GT_ROWS_PER_WARP = GT_NODES / GT_GROUP;            // rows of a worker in the gather and the row-wise passes: 16
+constexpr int GT_PASSES = GT_ROWS_PER_WARP / 4;                  // gather: four rows side by side per pass
+constexpr int GT_NODES_PER_SLOT = GT_NODES / (GT_GROUP / 4);     // accumulator node columns drained by a worker: 64
 constexpr int GT_CHUNKS = 4;                     // K chunks of 32 features (one swizzle line per node row)
 constexpr int GT_SBUF = 2;                       // operand buffers
 constexpr int GT_LC_CAP = 1536;                  // non-zeros of a tile cached in shared memory
@@ -83,15 +83,18 @@ constexpr uint32_t GT_IDESC_BASE = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32
 constexpr uint32_t GT_IDESC_N256 = GT_IDESC_BASE | ((uint32_t)(256 >> 3) << 17);
 constexpr uint32_t GT_IDESC_N128 = GT_IDESC_BASE | ((uint32_t)(128 >> 3) << 17);
 
-// mbarriers
+// mbarriers.  An mbarrier wait names a phase by its parity only, so a waiter must never be two phases away from the
+// barrier; the two worker groups run independently, therefore every barrier a group WAITS on is the group's own and
+// sees exactly the phases that group waits for, in order.
 enum {
-    GB_FULL0 = 0,               // +b : operand buffer b holds a chunk (sixteen worker arrivals)
-    GB_EMPTY0 = GT_SBUF,        // +b : the MMAs that read operand buffer b are complete (tcgen05.commit)
-    GB_ACC_FULL = 2 * GT_SBUF,  // the MMAs of a level-job are complete
-    GB_ACC_READ,                // the accumulator is in the workers' registers (sixteen arrivals)
-    GB_WSYNC,                   // worker-wide barrier
-    GB_COUNT
+    GB_FULL0 = 0,               // +b      : operand buffer b holds a chunk (eight arrivals, the producing group's warps)
+    GB_EMPTY0 = 2,              // +2g + b : the MMAs that read operand buffer b are complete and group g uses it next (tcgen05.commit)
+    GB_ACC_FULL0 = 6,           // +g      : the MMAs of a level-job of group g are complete (tcgen05.commit)
+    GB_ACC_READ = 8,            // the accumulator has been drained (eight arrivals, the draining group's warps)
+    GB_GSYNC0 = 9,              // +g      : barrier of the eight worker warps of group g
+    GB_COUNT = 11
 };
+static_assert(GT_SBUF == 2, "barrier numbering assumes two operand buffers");
 
 // ------------------------------------------------------------------ tile planning
 constexpr int PLAN_SEG = 8192;      // graphs handled per pass of the single planning CTA
@@ -220,13 +223,13 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
     const uint32_t s_addr0 = smem_u32(smem + GT_OFF_S);
 
     if (threadIdx.x == 0) {
-        for (int b = 0; b < GT_SBUF; ++b) {
-            tc_mbar_init(bar(GB_FULL0 + b), GT_WORKERS);
-            tc_mbar_init(bar(GB_EMPTY0 + b), 1);
-        }
-        tc_mbar_init(bar(GB_ACC_FULL), 1);
-        tc_mbar_init(bar(GB_ACC_READ), GT_WORKERS);
-        tc_mbar_init(bar(GB_WSYNC), GT_WORKERS);
+        for (int b = 0; b < GT_SBUF; ++b) tc_mbar_init(bar(GB_FULL0 + b), GT_GROUP);
+        for (int e = 0; e < 4; ++e) tc_mbar_init(bar(GB_EMPTY0 + e), 1);
+        tc_mbar_init(bar(GB_ACC_FULL0), 1);
+        tc_mbar_init(bar(GB_ACC_FULL0 + 1), 1);
+        tc_mbar_init(bar(GB_ACC_READ), GT_GROUP);
+        tc_mbar_init(bar(GB_GSYNC0), GT_GROUP);
+        tc_mbar_init(bar(GB_GSYNC0 + 1), GT_GROUP);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -241,29 +244,26 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    const int q = warp & 3, j = (warp >> 2) % (GT_WORKERS / 4);   // tensor-memory lane quarter, slot within it
+    const int q = warp & 3;                                  // tensor-memory lane quarter of this warp
     const uint32_t lane_base = (uint32_t)(32 * q) << 16;
     if (warp < GT_WORKERS) {
         // W^T into tensor memory: lane m = output feature, column k = input feature; A[m][k] = W[k][m].
-        // Worker (q, j): features 32q..32q+31, a block of GT_NODES_PER_SLOT values of k.  Loads are coalesced across the lanes.
+        // Warp w: features 32q..32q+31, k in [32*(w/4), 32*(w/4)+32).  Loads are coalesced across the lanes.
         const int m = 32 * q + lane;
-#pragma unroll 1
-        for (int kb = 0; kb < GT_NODES_PER_SLOT / 32; ++kb) {
-            const int k0 = GT_NODES_PER_SLOT * j + 32 * kb;
-            float wv[32];
+        const int k0 = 32 * (warp >> 2);
+        float wv[32];
 #pragma unroll
-            for (int kk = 0; kk < 32; ++kk) wv[kk] = __ldg(W + (int64_t)(k0 + kk) * GT_D + m);
+        for (int kk = 0; kk < 32; ++kk) wv[kk] = __ldg(W + (int64_t)(k0 + kk) * GT_D + m);
 #pragma unroll
-            for (int h = 0; h < 4; ++h) {
-                uint32_t hi[8], lo[8];
+        for (int h = 0; h < 4; ++h) {
+            uint32_t hi[8], lo[8];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    hi[c] = tf32_rn(wv[8 * h + c]);
-                    lo[c] = tf32_rn(wv[8 * h + c] - __uint_as_float(hi[c]));
-                }
-                tc_st_cols8(tmem_base + lane_base + GT_TM_WHI + (uint32_t)(k0 + 8 * h), hi);
-                tc_st_cols8(tmem_base + lane_base + GT_TM_WLO + (uint32_t)(k0 + 8 * h), lo);
+            for (int c = 0; c < 8; ++c) {
+                hi[c] = tf32_rn(wv[8 * h + c]);
+                lo[c] = tf32_rn(wv[8 * h + c] - __uint_as_float(hi[c]));
             }
+            tc_st_cols8(tmem_base + lane_base + GT_TM_WHI + (uint32_t)(k0 + 8 * h), hi);
+            tc_st_cols8(tmem_base + lane_base + GT_TM_WLO + (uint32_t)(k0 + 8 * h), lo);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     }
@@ -277,36 +277,46 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
     const int n_steps = 2 * (n_lj0 > n_lj1 ? n_lj0 : n_lj1);
 
     if (warp < GT_WORKERS) {
-        // =========================== worker warps ===========================
-        const int tix = threadIdx.x;                 // 0 .. 32 * GT_WORKERS - 1
+        // =========================== worker warps: group s serves stream s ===========================
+        const int s = warp / GT_GROUP, gw = warp % GT_GROUP;       // my stream, my place in its group
+        const int j = gw >> 2;                                      // which half of the node columns I drain
+        const int gtix = threadIdx.x - s * (GT_GROUP * 32);        // 0 .. 255 within the group
         const int g4 = lane >> 3, sl = lane & 7;     // gather: row within a pass of four, 16-byte piece of the 128-byte line
         const float4* __restrict__ Win4 = reinterpret_cast<const float4*>(W_in);
-        uint32_t ws_phase = 0;                       // completed phases of the worker-wide barrier
-        uint32_t jobs = 0;                           // chunk jobs produced so far (operand buffer = jobs & 1)
-        uint32_t drained = 0;                        // level-jobs whose accumulator has been read
+        unsigned char* const sb = smem + GT_OFF_ST + (size_t)s * GT_ST_BYTES;
+        unsigned char* const hbase = smem + GT_OFF_H + (size_t)s * GT_H_BYTES;
+        float* const lval = reinterpret_cast<float*>(sb + GT_ST_LVAL);
+        uint4* const rec = reinterpret_cast<uint4*>(sb + GT_ST_REC);
+        int* const lrp = reinterpret_cast<int*>(sb + GT_ST_LRP);
+        int* const tag_s = reinterpret_cast<int*>(sb + GT_ST_TAGS);
+        int* const goff = reinterpret_cast<int*>(sb + GT_ST_GOFF);
+        int* const info = reinterpret_cast<int*>(sb + GT_ST_INFO);
+        unsigned char* const lcol = sb + GT_ST_LCOL;
+        float* const Hs = reinterpret_cast<float*>(hbase);
+        float4* const H4s = reinterpret_cast<float4*>(hbase);
+        uint32_t gs_phase = 0;                       // completed phases of my group's barrier
         bool alive = true;
-        auto stream_base = [&](int s) { return smem + GT_OFF_ST + (size_t)s * GT_ST_BYTES; };
-        auto stream_h = [&](int s) { return smem + GT_OFF_H + (size_t)s * GT_H_BYTES; };
-        // arrive at the worker-wide barrier and wait for the other fifteen warps (bounded)
-        auto wsync = [&](int site) -> bool {
+        // arrive at the group barrier and wait for the other seven warps (bounded)
+        auto gsync = [&](int site) -> bool {
             __syncwarp();
-            if (lane == 0) tc_mbar_arrive(bar(GB_WSYNC));
-            const bool ok = tc_wait(bar(GB_WSYNC), ws_phase & 1u, abort_flag, status, site);
-            ++ws_phase;
+            if (lane == 0) tc_mbar_arrive(bar(GB_GSYNC0 + s));
+            const bool ok = tc_wait(bar(GB_GSYNC0 + s), gs_phase & 1u, abort_flag, status, site);
+            ++gs_phase;
             return ok;
         };
+        // level-jobs are served in the order A.0 B.0 A.1 B.1 ...: my k-th level-job is step 2k + s, and the number of
+        // level-jobs served before step t is what both groups and the MMA warp derive buffer indices and parities from
+        auto jobs_before = [&](int t) -> uint32_t {
+            const int a0 = (t + 1) >> 1, a1 = t >> 1;
+            return (uint32_t)((a0 < n_lj0 ? a0 : n_lj0) + (a1 < n_lj1 ? a1 : n_lj1));
+        };
+        const int my_tile_count = s == 0 ? (my_tiles + 1) >> 1 : my_tiles >> 1;
+        int my_lj = 0;                               // level-jobs this group has started
+        uint32_t empty_seen[2] = {0u, 0u};           // phases of my "buffer b free for me" barriers already waited for
 
-        // ---- a tile enters stream s: its CSR slice, tags, graph offsets, H0, and the per-row gather records
-        auto prologue = [&](int s, int tile) -> bool {
-            unsigned char* sb = stream_base(s);
-            float* lval = reinterpret_cast<float*>(sb + GT_ST_LVAL);
-            uint4* rec = reinterpret_cast<uint4*>(sb + GT_ST_REC);
-            int* lrp = reinterpret_cast<int*>(sb + GT_ST_LRP);
-            int* tag_s = reinterpret_cast<int*>(sb + GT_ST_TAGS);
-            int* goff = reinterpret_cast<int*>(sb + GT_ST_GOFF);
-            int* info = reinterpret_cast<int*>(sb + GT_ST_INFO);
-            unsigned char* lcol = sb + GT_ST_LCOL;
-            float4* H4s = reinterpret_cast<float4*>(stream_h(s));
+        for (int ti = 0; ti < my_tile_count && alive; ++ti) {
+            // ---- the tile enters the stream: its CSR slice, tags, graph offsets, H0, and the per-row gather records
+            const int tile = (int)blockIdx.x + (2 * ti + s) * (int)gridDim.x;
             const int2 tr = tile_range[tile];
             const int node0 = __ldg(graph_ptr + tr.x);
             int nrows = __ldg(graph_ptr + tr.y) - node0;
@@ -317,21 +327,21 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
             const int32_t base = __ldg(row_ptr + node0);
             int nnz = __ldg(row_ptr + node0 + nrows) - base;
             if (nnz < 0) nnz = 0;
-            const bool cached = nnz <= GT_LC_CAP;      // uniform over the CTA
-            if (tix == 0) {
+            const bool cached = nnz <= GT_LC_CAP;      // uniform over the group
+            if (gtix == 0) {
                 info[0] = node0; info[1] = nrows; info[2] = ngr; info[3] = tr.x; info[4] = base; info[5] = nnz;
             }
-            if (tix <= GT_NODES) {
-                int v = __ldg(row_ptr + node0 + (tix < nrows ? tix : nrows)) - base;
-                lrp[tix] = v < 0 ? 0 : (v > nnz ? nnz : v);
+            if (gtix <= GT_NODES) {
+                int v = __ldg(row_ptr + node0 + (gtix < nrows ? gtix : nrows)) - base;
+                lrp[gtix] = v < 0 ? 0 : (v > nnz ? nnz : v);
             }
-            if (tix < GT_NODES) tag_s[tix] = tix < nrows ? tc_table_row(__ldg(tags + node0 + tix), num_tags, status) : 0;
-            if (tix <= ngr) {
-                int v = __ldg(graph_ptr + tr.x + tix) - node0;
-                goff[tix] = v < 0 ? 0 : (v > nrows ? nrows : v);
+            if (gtix < GT_NODES) tag_s[gtix] = gtix < nrows ? tc_table_row(__ldg(tags + node0 + gtix), num_tags, status) : 0;
+            if (gtix <= ngr) {
+                int v = __ldg(graph_ptr + tr.x + gtix) - node0;
+                goff[gtix] = v < 0 ? 0 : (v > nrows ? nrows : v);
             }
             if (cached) {
-                for (int e = tix; e < nnz; e += GT_WORKERS * 32) {
+                for (int e = gtix; e < nnz; e += GT_GROUP * 32) {
                     int c = __ldg(col_idx + base + e) - node0;
                     if ((unsigned)c >= (unsigned)nrows) {   // an edge that leaves the tile: not a batch of separate graphs
                         status->code = S2V_ERR_BAD_CSR;
@@ -344,16 +354,16 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
             }
 #pragma unroll 4
             for (int rr = 0; rr < GT_ROWS_PER_WARP; ++rr) {
-                const int r = GT_ROWS_PER_WARP * warp + rr;
+                const int r = GT_ROWS_PER_WARP * gw + rr;
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (r < nrows) v = relu4(__ldg(Win4 + (int64_t)tc_table_row(__ldg(tags + node0 + r), num_tags, status) * 32 + lane));
                 H4s[r * 32 + lane] = v;
             }
-            if (!wsync(30)) return false;
+            if (!gsync(30)) { alive = false; break; }
             // gather record of row r: offsets (from the shared-memory base) of the rows of its first four neighbours;
             // unused slots point at the row of zeros, so the gather needs no test per slot
-            if (tix < GT_NODES) {
-                const int beg = lrp[tix], deg = lrp[tix + 1] - beg;
+            if (gtix < GT_NODES) {
+                const int beg = lrp[gtix], deg = lrp[gtix + 1] - beg;
                 uint32_t off[4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
@@ -372,156 +382,140 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
                         off[u] = (uint32_t)(GT_OFF_H + (size_t)s * GT_H_BYTES) + (uint32_t)c * 512u;
                     }
                 }
-                rec[tix] = make_uint4(off[0], off[1], off[2], off[3]);
+                rec[gtix] = make_uint4(off[0], off[1], off[2], off[3]);
             }
-            return wsync(35);
-        };
+            if (!gsync(35)) { alive = false; break; }
 
-        // ---- my gather rows of stream s (rows GT_ROWS_PER_WARP*warp + 4p + g4): neighbour offsets, store offset, extent
-        uint32_t na[GT_PASSES][4], da[GT_PASSES];
-        int gbeg[GT_PASSES], gdeg[GT_PASSES];
-        bool long_rows = false;        // warp-uniform: some row of mine has more than four neighbours
-        auto load_rows = [&](int s) {
-            unsigned char* sb = stream_base(s);
-            const uint4* rec = reinterpret_cast<const uint4*>(sb + GT_ST_REC);
-            const int* lrp = reinterpret_cast<const int*>(sb + GT_ST_LRP);
+            // ---- my gather rows (GT_ROWS_PER_WARP*gw + 4p + g4): neighbour offsets and store offset, kept for the whole tile
+            uint32_t na[GT_PASSES][4], da[GT_PASSES];
             bool lng = false;
 #pragma unroll
             for (int p = 0; p < GT_PASSES; ++p) {
-                const int r = GT_ROWS_PER_WARP * warp + 4 * p + g4;
+                const int r = GT_ROWS_PER_WARP * gw + 4 * p + g4;
                 const uint4 rc = rec[r];
                 na[p][0] = rc.x + (uint32_t)sl * 16u; na[p][1] = rc.y + (uint32_t)sl * 16u;
                 na[p][2] = rc.z + (uint32_t)sl * 16u; na[p][3] = rc.w + (uint32_t)sl * 16u;
                 // row r of the K-major 128-byte-swizzle layout: 16-byte piece sl sits at sl ^ (r & 7)
                 da[p] = (uint32_t)GT_OFF_S + (uint32_t)r * 128u + (uint32_t)((sl ^ (r & 7)) * 16);
-                gbeg[p] = lrp[r];
-                gdeg[p] = lrp[r + 1] - gbeg[p];
-                lng |= gdeg[p] > 4;
+                lng |= (lrp[r + 1] - lrp[r]) > 4;
             }
-            long_rows = __any_sync(0xffffffffu, lng);
-        };
+            const bool long_rows = __any_sync(0xffffffffu, lng);   // warp-uniform: some row of mine has more than four neighbours
 
-        // ---- one chunk (32 features) of S = A * H of stream s's tile: gather, split, store as MMA operand
-        auto gather_chunk = [&](int s, int c) -> bool {
-            const uint32_t b = jobs & 1u;
-            if (jobs >= (uint32_t)GT_SBUF &&
-                !tc_wait(bar(GB_EMPTY0 + b), ((jobs >> 1) - 1u) & 1u, abort_flag, status, 36))
-                return false;
-            const unsigned char* hb = smem + (size_t)c * 128;
-            unsigned char* sbuf = smem + (size_t)b * GT_S_BYTES;
-#pragma unroll
-            for (int p = 0; p < GT_PASSES; ++p) {
-                const float4 v0 = *reinterpret_cast<const float4*>(hb + na[p][0]);
-                const float4 v1 = *reinterpret_cast<const float4*>(hb + na[p][1]);
-                const float4 v2 = *reinterpret_cast<const float4*>(hb + na[p][2]);
-                const float4 v3 = *reinterpret_cast<const float4*>(hb + na[p][3]);
-                float4 acc;
-                if (HAS_VAL) {
-                    unsigned char* sb = stream_base(s);
-                    const int* info = reinterpret_cast<const int*>(sb + GT_ST_INFO);
-                    const bool cached = info[5] <= GT_LC_CAP;
-                    const float* lv = reinterpret_cast<const float*>(sb + GT_ST_LVAL) + gbeg[p];
-                    const float* gv = val + info[4] + gbeg[p];
-                    float a[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) a[u] = u < gdeg[p] ? (cached ? lv[u] : __ldg(gv + u)) : 0.f;
-                    acc = make_float4(a[0] * v0.x, a[0] * v0.y, a[0] * v0.z, a[0] * v0.w);
-                    acc.x = fmaf(a[1], v1.x, acc.x); acc.y = fmaf(a[1], v1.y, acc.y); acc.z = fmaf(a[1], v1.z, acc.z); acc.w = fmaf(a[1], v1.w, acc.w);
-                    acc.x = fmaf(a[2], v2.x, acc.x); acc.y = fmaf(a[2], v2.y, acc.y); acc.z = fmaf(a[2], v2.z, acc.z); acc.w = fmaf(a[2], v2.w, acc.w);
-                    acc.x = fmaf(a[3], v3.x, acc.x); acc.y = fmaf(a[3], v3.y, acc.y); acc.z = fmaf(a[3], v3.z, acc.z); acc.w = fmaf(a[3], v3.w, acc.w);
-                } else {   // adds in CSR order; an unused slot adds the row of zeros
-                    acc = make_float4((((v0.x + v1.x) + v2.x) + v3.x), (((v0.y + v1.y) + v2.y) + v3.y),
-                                      (((v0.z + v1.z) + v2.z) + v3.z), (((v0.w + v1.w) + v2.w) + v3.w));
-                }
-                if (long_rows && gdeg[p] > 4) {   // rows with more than four neighbours
-                    unsigned char* sb = stream_base(s);
-                    const int* info = reinterpret_cast<const int*>(sb + GT_ST_INFO);
-                    const int node0 = info[0], nrows = info[1], base = info[4];
-                    const bool cached = info[5] <= GT_LC_CAP;
-                    const unsigned char* lcol = sb + GT_ST_LCOL;
-                    const unsigned char* hrow = stream_h(s) + (size_t)c * 128 + (size_t)sl * 16;
-                    for (int t = 4; t < gdeg[p]; ++t) {
-                        int n;
-                        if (cached) n = lcol[gbeg[p] + t];
-                        else {
-                            n = __ldg(col_idx + base + gbeg[p] + t) - node0;
-                            if ((unsigned)n >= (unsigned)nrows) n = 0;
-                        }
-                        const float4 vv = *reinterpret_cast<const float4*>(hrow + (size_t)n * 512);
-                        if (HAS_VAL) {
-                            const float a = cached ? reinterpret_cast<const float*>(sb + GT_ST_LVAL)[gbeg[p] + t] : __ldg(val + base + gbeg[p] + t);
-                            acc.x = fmaf(a, vv.x, acc.x); acc.y = fmaf(a, vv.y, acc.y);
-                            acc.z = fmaf(a, vv.z, acc.z); acc.w = fmaf(a, vv.w, acc.w);
-                        } else {
-                            acc.x += vv.x; acc.y += vv.y; acc.z += vv.z; acc.w += vv.w;
+            for (int lv = 0; lv < levels; ++lv) {
+                const uint32_t lj = jobs_before(2 * my_lj + s);      // level-jobs served before mine
+                ++my_lj;
+                // -------------------------------- gather: S = A * H, split, into the operand buffers --------------------------------
+#pragma unroll 1
+                for (int c = 0; c < GT_CHUNKS; ++c) {
+                    const uint32_t job = 4u * lj + (uint32_t)c;
+                    const uint32_t b = job & 1u;
+                    if (job >= (uint32_t)GT_SBUF) {   // the buffer was used before (by either group): wait until its MMAs are done
+                        const uint32_t par = (b == 0u ? empty_seen[0]++ : empty_seen[1]++) & 1u;
+                        if (!tc_wait(bar(GB_EMPTY0 + 2 * s + (int)b), par, abort_flag, status, 36)) {
+                            alive = false;
+                            break;
                         }
                     }
+                    const unsigned char* hb = smem + (size_t)c * 128;
+                    unsigned char* sbuf = smem + (size_t)b * GT_S_BYTES;
+#pragma unroll
+                    for (int p = 0; p < GT_PASSES; ++p) {
+                        const float4 v0 = *reinterpret_cast<const float4*>(hb + na[p][0]);
+                        const float4 v1 = *reinterpret_cast<const float4*>(hb + na[p][1]);
+                        const float4 v2 = *reinterpret_cast<const float4*>(hb + na[p][2]);
+                        const float4 v3 = *reinterpret_cast<const float4*>(hb + na[p][3]);
+                        float4 acc;
+                        const int r = GT_ROWS_PER_WARP * gw + 4 * p + g4;
+                        if (HAS_VAL) {
+                            const int gb = lrp[r], gd = lrp[r + 1] - gb;
+                            float a[4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) a[u] = u < gd ? (cached ? lval[gb + u] : __ldg(val + base + gb + u)) : 0.f;
+                            acc = make_float4(a[0] * v0.x, a[0] * v0.y, a[0] * v0.z, a[0] * v0.w);
+                            acc.x = fmaf(a[1], v1.x, acc.x); acc.y = fmaf(a[1], v1.y, acc.y); acc.z = fmaf(a[1], v1.z, acc.z); acc.w = fmaf(a[1], v1.w, acc.w);
+                            acc.x = fmaf(a[2], v2.x, acc.x); acc.y = fmaf(a[2], v2.y, acc.y); acc.z = fmaf(a[2], v2.z, acc.z); acc.w = fmaf(a[2], v2.w, acc.w);
+                            acc.x = fmaf(a[3], v3.x, acc.x); acc.y = fmaf(a[3], v3.y, acc.y); acc.z = fmaf(a[3], v3.z, acc.z); acc.w = fmaf(a[3], v3.w, acc.w);
+                        } else {   // adds in CSR order; an unused slot adds the row of zeros
+                            acc = make_float4((((v0.x + v1.x) + v2.x) + v3.x), (((v0.y + v1.y) + v2.y) + v3.y),
+                                              (((v0.z + v1.z) + v2.z) + v3.z), (((v0.w + v1.w) + v2.w) + v3.w));
+                        }
+                        if (long_rows) {   // rows with more than four neighbours
+                            const int gb = lrp[r], gd = lrp[r + 1] - gb;
+                            const unsigned char* hrow = hbase + (size_t)c * 128 + (size_t)sl * 16;
+                            for (int t = 4; t < gd; ++t) {
+                                int n;
+                                if (cached) n = lcol[gb + t];
+                                else {
+                                    n = __ldg(col_idx + base + gb + t) - node0;
+                                    if ((unsigned)n >= (unsigned)nrows) n = 0;
+                                }
+                                const float4 vv = *reinterpret_cast<const float4*>(hrow + (size_t)n * 512);
+                                if (HAS_VAL) {
+                                    const float a = cached ? lval[gb + t] : __ldg(val + base + gb + t);
+                                    acc.x = fmaf(a, vv.x, acc.x); acc.y = fmaf(a, vv.y, acc.y);
+                                    acc.z = fmaf(a, vv.z, acc.z); acc.w = fmaf(a, vv.w, acc.w);
+                                } else {
+                                    acc.x += vv.x; acc.y += vv.y; acc.z += vv.z; acc.w += vv.w;
+                                }
+                            }
+                        }
+                        uint4 hi, lo;
+                        tc_split(acc.x, hi.x, lo.x);
+                        tc_split(acc.y, hi.y, lo.y);
+                        tc_split(acc.z, hi.z, lo.z);
+                        tc_split(acc.w, hi.w, lo.w);
+                        *reinterpret_cast<uint4*>(sbuf + da[p]) = hi;
+                        *reinterpret_cast<uint4*>(sbuf + da[p] + 128 * 128) = lo;
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // my stores -> visible to the tensor core
+                    __syncwarp();
+                    if (lane == 0) tc_mbar_arrive(bar(GB_FULL0 + b));
                 }
-                uint4 hi, lo;
-                tc_split(acc.x, hi.x, lo.x);
-                tc_split(acc.y, hi.y, lo.y);
-                tc_split(acc.z, hi.z, lo.z);
-                tc_split(acc.w, hi.w, lo.w);
-                *reinterpret_cast<uint4*>(sbuf + da[p]) = hi;
-                *reinterpret_cast<uint4*>(sbuf + da[p] + 128 * 128) = lo;
+                if (!alive) break;
+                // -------------------------------- drain: accumulator -> raw sums in the H tile --------------------------------
+                // X rows of my first row-wise rows are fetched now and stay in flight across the wait
+                float4 xr[8];
+#pragma unroll
+                for (int rr = 0; rr < 8; ++rr) xr[rr] = __ldg(Win4 + (int64_t)tag_s[GT_ROWS_PER_WARP * gw + rr] * 32 + lane);
+                if (!tc_wait(bar(GB_ACC_FULL0 + s), (uint32_t)(my_lj - 1) & 1u, abort_flag, status, 31)) { alive = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                {   // feature = my lane (32q + lane), node columns GT_NODES_PER_SLOT*j ..
+                    const uint32_t acc_addr = tmem_base + lane_base + GT_TM_ACC + (uint32_t)(GT_NODES_PER_SLOT * j);
+                    float* hcol = Hs + (GT_NODES_PER_SLOT * j) * GT_D + 32 * q + lane;
+#pragma unroll
+                    for (int h = 0; h < GT_NODES_PER_SLOT / 16; ++h) {
+                        uint32_t big[16], sml[16];
+                        tc_ld_cols16(acc_addr + (uint32_t)(16 * h), big);
+                        tc_ld_cols16(acc_addr + 128u + (uint32_t)(16 * h), sml);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (h == GT_NODES_PER_SLOT / 16 - 1) {
+                            // my block of the accumulator is in registers: the next level-job's MMAs may overwrite it
+                            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                            __syncwarp();
+                            if (lane == 0) tc_mbar_arrive(bar(GB_ACC_READ));
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) hcol[(16 * h + i) * GT_D] = __uint_as_float(big[i]) + __uint_as_float(sml[i]);
+                    }
+                }
+                if (!gsync(32)) { alive = false; break; }
+                // -------------------------------- row-wise pass: H = ReLU(raw + X), lanes across the features --------------------------------
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                    for (int rr = 0; rr < 8; ++rr) {
+                        const int r = GT_ROWS_PER_WARP * gw + 8 * half + rr;
+                        const float4 z = H4s[r * 32 + lane];
+                        const float4 x = xr[rr];
+                        H4s[r * 32 + lane] = make_float4(relu_ref(z.x + x.x), relu_ref(z.y + x.y), relu_ref(z.z + x.z), relu_ref(z.w + x.w));
+                        if (half == 0) xr[rr] = __ldg(Win4 + (int64_t)tag_s[GT_ROWS_PER_WARP * gw + 8 + rr] * 32 + lane);
+                    }
+                }
+                if (!gsync(33)) { alive = false; break; }           // H complete for the next level's gather / the pooling
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // my stores -> visible to the tensor core
-            __syncwarp();
-            if (lane == 0) tc_mbar_arrive(bar(GB_FULL0 + b));
-            ++jobs;
-            return true;
-        };
-
-        // ---- X term of the epilogue of stream s: feature = my lane, nodes GT_NODES_PER_SLOT*j ..
-        float xv[GT_NODES_PER_SLOT];
-        auto fetch_x = [&](int s) {
-            const int4* tag4 = reinterpret_cast<const int4*>(reinterpret_cast<const int*>(stream_base(s) + GT_ST_TAGS) + GT_NODES_PER_SLOT * j);
-            const float* xcol = W_in + 32 * q + lane;
-#pragma unroll
-            for (int i4 = 0; i4 < GT_NODES_PER_SLOT / 4; ++i4) {
-                const int4 t = tag4[i4];
-                xv[4 * i4 + 0] = __ldg(xcol + (int64_t)t.x * GT_D);
-                xv[4 * i4 + 1] = __ldg(xcol + (int64_t)t.y * GT_D);
-                xv[4 * i4 + 2] = __ldg(xcol + (int64_t)t.z * GT_D);
-                xv[4 * i4 + 3] = __ldg(xcol + (int64_t)t.w * GT_D);
-            }
-        };
-        // ---- accumulator of the oldest open level-job (stream s) -> registers -> + X, ReLU -> the stream's H tile
-        auto drain_epilogue = [&](int s) -> bool {
-            float* Hs = reinterpret_cast<float*>(stream_h(s));
-            fetch_x(s);     // in flight across the wait below
-            if (!tc_wait(bar(GB_ACC_FULL), drained & 1u, abort_flag, status, 31)) return false;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t acc_addr = tmem_base + lane_base + GT_TM_ACC + (uint32_t)(GT_NODES_PER_SLOT * j);
-            float* hcol = Hs + (GT_NODES_PER_SLOT * j) * GT_D + 32 * q + lane;
-            float z[GT_NODES_PER_SLOT];
-#pragma unroll
-            for (int h = 0; h < GT_NODES_PER_SLOT / 16; ++h) {
-                uint32_t big[16], sml[16];
-                tc_ld_cols16(acc_addr + (uint32_t)(16 * h), big);
-                tc_ld_cols16(acc_addr + 128u + (uint32_t)(16 * h), sml);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int i = 0; i < 16; ++i) z[16 * h + i] = (__uint_as_float(big[i]) + __uint_as_float(sml[i])) + xv[16 * h + i];
-            }
-            // my block of the accumulator is in registers: hand the accumulator over to the next level-job's MMAs
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) tc_mbar_arrive(bar(GB_ACC_READ));
-            ++drained;
-#pragma unroll
-            for (int i = 0; i < GT_NODES_PER_SLOT; ++i) hcol[i * GT_D] = relu_ref(z[i]);
-            return true;
-        };
-
-        // ---- graph sums of stream s's finished tile (node order), optional node embeddings
-        auto pool = [&](int s) {
-            unsigned char* sb = stream_base(s);
-            const int* goff = reinterpret_cast<const int*>(sb + GT_ST_GOFF);
-            const int* info = reinterpret_cast<const int*>(sb + GT_ST_INFO);
-            const float4* H4s = reinterpret_cast<const float4*>(stream_h(s));
-            const int node0 = info[0], nrows = info[1], ngr = info[2], g0 = info[3];
-            for (int k = warp; k < ngr; k += GT_WORKERS) {
+            if (!alive) break;
+            // -------------------------------- pooling and (optionally) the node embeddings --------------------------------
+            for (int k = gw; k < ngr; k += GT_GROUP) {
                 const int nb = goff[k], ne = goff[k + 1];
                 const float inv = pool_average ? (float)(1.0 / (double)(ne - nb)) : 1.0f;
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -534,60 +528,33 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
                         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
                     }
                 }
-                reinterpret_cast<float4*>(Y)[(int64_t)(g0 + k) * 32 + lane] = acc;
+                reinterpret_cast<float4*>(Y)[(int64_t)(tr.x + k) * 32 + lane] = acc;
             }
             if (embed_out) {
-#pragma unroll
+#pragma unroll 4
                 for (int rr = 0; rr < GT_ROWS_PER_WARP; ++rr) {
-                    const int r = GT_ROWS_PER_WARP * warp + rr;
+                    const int r = GT_ROWS_PER_WARP * gw + rr;
                     if (r < nrows) reinterpret_cast<float4*>(embed_out)[(int64_t)(node0 + r) * 32 + lane] = H4s[r * 32 + lane];
                 }
             }
-        };
-
-        // the first tile of each stream
-        alive = prologue(0, (int)blockIdx.x);
-        if (alive && my_tiles > 1) alive = prologue(1, (int)blockIdx.x + (int)gridDim.x);
-        int pending = -1;                      // stream whose level-job awaits its epilogue
-        int lv_of[2] = {0, 0};                 // level the stream's tile is at
-        int tiles_done[2] = {0, 0};            // tiles the stream has finished
-        // step k: level-job (k >> 1) of stream (k & 1), if that stream still has one
-        for (int k = 0; k <= n_steps && alive; ++k) {
-            const int s = k & 1;
-            const bool have = (k >> 1) < (s == 0 ? n_lj0 : n_lj1);
-            if (have) {
-                load_rows(s);
-                if (!gather_chunk(s, 0) || !gather_chunk(s, 1)) { alive = false; break; }
-            }
-            bool tile_finished = false;
-            if (pending >= 0) {
-                if (!drain_epilogue(pending)) { alive = false; break; }
-                tile_finished = ++lv_of[pending] == levels;
-            }
-            if (have) {
-                if (!gather_chunk(s, 2) || !gather_chunk(s, 3)) { alive = false; break; }
-            }
-            if (!wsync(32)) { alive = false; break; }           // H of the drained level complete for every warp
-            if (tile_finished) {
-                pool(pending);
-                lv_of[pending] = 0;
-                const int next_i = 2 * (++tiles_done[pending]) + pending;   // the stream's next tile among this CTA's
-                if (!wsync(33)) { alive = false; break; }       // pooling has read H before the next tile overwrites it
-                if (next_i < my_tiles && !prologue(pending, (int)blockIdx.x + next_i * (int)gridDim.x)) { alive = false; break; }
-            }
-            pending = have ? s : -1;
+            if (!gsync(34)) { alive = false; break; }       // the tile's shared arrays are rewritten by the next prologue
         }
     } else {
         // =========================== MMA-issue warp ===========================
         uint32_t jobs = 0, lj = 0;
         bool alive = true;
+        auto has_job = [&](int k) { return (k >> 1) < ((k & 1) == 0 ? n_lj0 : n_lj1); };
         for (int k = 0; k < n_steps && alive; ++k) {
-            if ((k >> 1) >= ((k & 1) == 0 ? n_lj0 : n_lj1)) continue;
+            if (!has_job(k)) continue;
+            const int g = k & 1;                       // the group this level-job belongs to
+            int k2 = k + 1;                            // the next level-job and its group (-1: none)
+            while (k2 < n_steps && !has_job(k2)) ++k2;
+            const int g_next = k2 < n_steps ? (k2 & 1) : -1;
 #pragma unroll 1
             for (int c = 0; c < GT_CHUNKS; ++c) {
                 const uint32_t b = jobs & 1u;
                 if (!tc_wait(bar(GB_FULL0 + b), (jobs >> 1) & 1u, abort_flag, status, 34)) { alive = false; break; }
-                // the previous level-job's accumulator must be in the workers' registers before it is overwritten
+                // the previous level-job's accumulator must be in the workers' hands before it is overwritten
                 if (c == 0 && lj > 0 && !tc_wait(bar(GB_ACC_READ), (lj - 1u) & 1u, abort_flag, status, 37)) { alive = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (lane == 0) {
@@ -601,10 +568,14 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
                         // W_lo * S_hi onto the small-term half
                         tc_mma(tmem_base + GT_TM_ACC + 128u, tmem_base + GT_TM_WLO + 8u * ks, bd, GT_IDESC_N128, 1u);
                     }
-                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar(GB_EMPTY0 + b))
-                                 : "memory");
+                    // this buffer is used next by the chunk two jobs on: the same group's (c < 2) or the next level-job's
+                    const int g_user = c < 2 ? g : g_next;
+                    if (g_user >= 0)
+                        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                         bar(GB_EMPTY0 + 2 * g_user + (int)b))
+                                     : "memory");
                     if (c == GT_CHUNKS - 1)
-                        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar(GB_ACC_FULL))
+                        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar(GB_ACC_FULL0 + g))
                                      : "memory");
                 }
                 __syncwarp();
