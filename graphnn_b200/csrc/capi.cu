@@ -223,6 +223,9 @@ int s2v_level_lookup_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_
     int rc = check_level_args(ctx, n_rows, n_src, d, row_ptr, col_idx, H, W, table, out);
     if (rc != S2V_OK || n_rows == 0) return rc;
     if (!table || !x_index || n_table <= 0) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level_lookup: NULL table or index");
+    // the level kernel clamps the indices it uses; this launch finds and reports the ones outside the table
+    rc = s2v_launch_index_check(ctx, s2v_pick_stream(ctx, stream), n_rows, x_index, n_table);
+    if (rc != S2V_OK) return rc;
     return s2v_launch_level(ctx, s2v_pick_stream(ctx, stream), n_rows, n_src, d, row_ptr, false, col_idx, val, H, W,
                             nullptr, table, x_index, n_table, out);
 }
@@ -238,8 +241,10 @@ int s2v_level_first_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n, int d, const
         return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level_first: W, table, out must be 16-byte aligned");
     if (!s2v_use_tc(ctx, d, n))
         return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "level_first: only the tcgen05 kernel (d = 64 or 128, large batch) has this form; materialise H0 instead");
-    const int rc = s2v_launch_level_tc(ctx, s2v_pick_stream(ctx, stream), n, d, row_ptr, col_idx, val, nullptr, W, nullptr, table,
-                                       tags, n_table, out);
+    int rc = s2v_launch_index_check(ctx, s2v_pick_stream(ctx, stream), n, tags, n_table);
+    if (rc != S2V_OK) return rc;
+    rc = s2v_launch_level_tc(ctx, s2v_pick_stream(ctx, stream), n, d, row_ptr, col_idx, val, nullptr, W, nullptr, table,
+                             tags, n_table, out);
     if (rc == S2V_ERR_UNSUPPORTED) return s2v_fail(ctx, rc, "level_first: shape not supported by the tcgen05 kernel");
     return rc;
 }
@@ -328,10 +333,16 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
     const bool onehot = batch->tags != nullptr && d % 4 == 0;
     // first level straight from the tags (no H0 in memory) when the tcgen05 kernel takes this shape
     bool first_fused = false;
+    if (onehot) {   // the tags are range-checked once per batch; the level kernels only clamp them
+        if (!s2v_aligned16(model->w_n2l) || !s2v_aligned16(model->p_node_conv) || (embed_out && !s2v_aligned16(embed_out)))
+            return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "forward: weights and embed_out must be 16-byte aligned");
+        rc = s2v_launch_index_check(ctx, st, N, batch->tags, model->num_feat);
+        if (rc != S2V_OK) return rc;
+    }
     if (onehot && L >= 1 && s2v_use_tc(ctx, d, N)) {
         float* dst = (L == 1 && embed_out) ? embed_out : ha;
-        rc = s2v_level_first_f32(ctx, st, N, d, batch->n2n_row_ptr, batch->n2n_col_idx, batch->n2n_val, model->p_node_conv,
-                                 model->w_n2l, model->num_feat, batch->tags, dst);
+        rc = s2v_launch_level_tc(ctx, st, N, d, batch->n2n_row_ptr, batch->n2n_col_idx, batch->n2n_val, nullptr, model->p_node_conv,
+                                 nullptr, model->w_n2l, batch->tags, model->num_feat, dst);
         if (rc == S2V_OK) first_fused = true;
         else if (rc != S2V_ERR_UNSUPPORTED) return rc;
     }
@@ -350,8 +361,10 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
     for (int lv = first_fused ? 1 : 0; lv < L; ++lv) {
         float* dst = (lv == L - 1 && embed_out) ? embed_out : nxt;
         if (onehot)
-            rc = s2v_level_lookup_f32(ctx, st, N, N, d, batch->n2n_row_ptr, batch->n2n_col_idx, batch->n2n_val, cur,
-                                      model->p_node_conv, model->w_n2l, model->num_feat, batch->tags, dst);
+            rc = (d == 32 || d == 64 || d == 128)
+                     ? s2v_launch_level(ctx, st, N, N, d, batch->n2n_row_ptr, false, batch->n2n_col_idx, batch->n2n_val, cur,
+                                        model->p_node_conv, nullptr, model->w_n2l, batch->tags, model->num_feat, dst)
+                     : s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "fused level kernel supports d in {32, 64, 128}");
         else
             rc = s2v_level_f32(ctx, st, N, N, d, batch->n2n_row_ptr, batch->n2n_col_idx, batch->n2n_val, cur,
                                model->p_node_conv, msg, dst);

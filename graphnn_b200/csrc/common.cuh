@@ -139,6 +139,8 @@ int s2v_launch_level_tc(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int d, co
                         const int32_t* col_idx, const float* val, const float* H, const float* W, const float* X,
                         const float* table, const int32_t* x_index, int n_table, float* out);
 int s2v_launch_wait_selftest(s2v_ctx* ctx, cudaStream_t st);
+// records S2V_ERR_INVALID_ARG in the status word if any idx[i] lies outside [0, limit)
+int s2v_launch_index_check(s2v_ctx* ctx, cudaStream_t st, int64_t n, const int32_t* idx, int limit);
 // whole classifier up to the pooled embeddings for batches of graphs of at most S2V_TILE_NODES nodes (d = 128, tags)
 constexpr int S2V_TILE_NODES = 128;
 size_t s2v_graph_tiles_plan_bytes(int64_t num_graphs);

@@ -195,6 +195,14 @@ __global__ void __launch_bounds__(PLAN_THREADS) gt_plan_kernel(int64_t G, const 
 }
 
 // ------------------------------------------------------------------ the tile kernel
+// a node tag outside [0, n) is replaced by 0 and remembered; the kernel reports it once, when it ends
+__device__ __forceinline__ int gt_checked_tag(int v, int n, int& bad)
+{
+    const bool out = (unsigned)v >= (unsigned)n;
+    bad |= out ? 1 : 0;
+    return out ? 0 : v;
+}
+
 __device__ __forceinline__ float4 relu4(float4 v)
 {
     return make_float4(relu_ref(v.x), relu_ref(v.y), relu_ref(v.z), relu_ref(v.w));
@@ -220,6 +228,7 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    int bad_index = 0;   // a tag outside the table was met (reported once, at the end)
     const uint32_t s_addr0 = smem_u32(smem + GT_OFF_S);
 
     if (threadIdx.x == 0) {
@@ -335,7 +344,7 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
                 int v = __ldg(row_ptr + node0 + (gtix < nrows ? gtix : nrows)) - base;
                 lrp[gtix] = v < 0 ? 0 : (v > nnz ? nnz : v);
             }
-            if (gtix < GT_NODES) tag_s[gtix] = gtix < nrows ? tc_table_row(__ldg(tags + node0 + gtix), num_tags, status) : 0;
+            if (gtix < GT_NODES) tag_s[gtix] = gtix < nrows ? gt_checked_tag(__ldg(tags + node0 + gtix), num_tags, bad_index) : 0;
             if (gtix <= ngr) {
                 int v = __ldg(graph_ptr + tr.x + gtix) - node0;
                 goff[gtix] = v < 0 ? 0 : (v > nrows ? nrows : v);
@@ -356,7 +365,7 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
             for (int rr = 0; rr < GT_ROWS_PER_WARP; ++rr) {
                 const int r = GT_ROWS_PER_WARP * gw + rr;
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (r < nrows) v = relu4(__ldg(Win4 + (int64_t)tc_table_row(__ldg(tags + node0 + r), num_tags, status) * 32 + lane));
+                if (r < nrows) v = relu4(__ldg(Win4 + (int64_t)gt_checked_tag(__ldg(tags + node0 + r), num_tags, bad_index) * 32 + lane));
                 H4s[r * 32 + lane] = v;
             }
             if (!gsync(30)) { alive = false; break; }
@@ -586,6 +595,10 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
     }
 
     // ---- teardown: everyone is done with tensor memory before it is released
+    if (bad_index) {
+        status->code = S2V_ERR_INVALID_ARG;
+        status->where = 3;
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

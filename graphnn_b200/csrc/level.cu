@@ -345,13 +345,9 @@ s2v_level_kernel(int64_t n_rows, int64_t num_tiles, const RpT* __restrict__ row_
                 float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (XMODE == 1) x = ld_stream_f4(reinterpret_cast<const float4*>(X) + row * LPR + sl);
                 if (XMODE == 2) {
-                    // the index is caller data (a node tag): outside [0, n_table) it is recorded and row 0 is used
-                    int xi = __ldg(x_index + row);
-                    if ((unsigned)xi >= (unsigned)n_table) {
-                        status->code = S2V_ERR_INVALID_ARG;
-                        status->where = 3;
-                        xi = 0;
-                    }
+                    // the index is caller data (a node tag): clamped into the table here; a bad index is detected and
+                    // reported by index_range_check_kernel, which the host entry point launches beside this kernel
+                    const int xi = (int)min((unsigned)__ldg(x_index + row), (unsigned)(n_table - 1));
                     x = ld_nc_f4(reinterpret_cast<const float4*>(X) + (int64_t)xi * LPR + sl);
                 }
                 float4 r;

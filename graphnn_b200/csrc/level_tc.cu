@@ -191,7 +191,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
         // X row index of "my" epilogue row (lane = row within the quarter)
         auto load_xi = [&](int it) -> int {
             const int64_t mr = ((int64_t)blockIdx.x + (int64_t)it * gridDim.x) * TC_TILE + 32 * q + lane;
-            return (XMODE == 2 && it < my_tiles && mr < n_rows) ? tc_table_row(tc_ld_early(x_index + mr), n_table, status) : 0;
+            return (XMODE == 2 && it < my_tiles && mr < n_rows) ? tc_ld_early(x_index + mr) : 0;   // range-checked where it is used, a tile later
         };
         constexpr int G = 32 / LPR;        // lane groups per warp (1 at d = 128, 2 at d = 64)
         constexpr int WSZ = IDX_CAP / G;   // index window per lane group: 64 entries
@@ -217,7 +217,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
             for (int jj = 0; jj < IPL; ++jj)
             {
                 const int c_ = window_index(jj, __shfl_sync(0xffffffffu, rel, RPG), __shfl_sync(0xffffffffu, rel, TC_ROWS_PER_GW), base, 0);
-                idx_base[lane + 32 * jj] = HSRC_TABLE ? tc_table_row(__ldg(x_index + c_), n_table, status) : c_;
+                idx_base[lane + 32 * jj] = HSRC_TABLE ? tc_table_row(__ldg(x_index + c_), n_table) : c_;
             }
             rp_next = rp_next2;
         }
@@ -293,7 +293,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                         }
                         // table form: the window holds the neighbour's table row, looked up here, a tile ahead
                         // (issued now, stored after the stream: see tag_pref below)
-                        if (HSRC_TABLE) tag_pref[jj] = tc_table_row(__ldg(x_index + idx_pref[jj]), n_table, status);
+                        if (HSRC_TABLE) tag_pref[jj] = __ldg(x_index + idx_pref[jj]);   // range-checked when it is stored, after the stream
                         else nb[lane + 32 * jj] = idx_pref[jj];
                     }
                     if (lane <= TC_ROWS_PER_GW) nb[IDX_CAP + lane] = rel1;
@@ -341,7 +341,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
 #pragma unroll
                         for (int jj = 0; jj < IPL; ++jj) {
                             const int c_ = window_index(jj, r_mid, r_end, base, k);
-                            idx_s[lane + 32 * jj] = HSRC_TABLE ? tc_table_row(__ldg(x_index + c_), n_table, status) : c_;
+                            idx_s[lane + 32 * jj] = HSRC_TABLE ? tc_table_row(__ldg(x_index + c_), n_table) : c_;
                         }
                         __syncwarp();
                     }
@@ -381,7 +381,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                 if (HSRC_TABLE) {
                     int* nb = idx_base + ((it + 1) & 1) * IDX_BUF;
 #pragma unroll
-                    for (int jj = 0; jj < IPL; ++jj) nb[lane + 32 * jj] = tag_pref[jj];
+                    for (int jj = 0; jj < IPL; ++jj) nb[lane + 32 * jj] = tc_table_row(tag_pref[jj], n_table);
                 }
                 base = base1;
                 rp_next = rp_next2;
@@ -398,7 +398,7 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                 x[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (XMODE == 1 && rl < rows_left) x[rr] = ld_stream_f4(X4 + (prow0 + rl) * (D / 4) + C4 * j + ec4);
                 if (XMODE == 2) {
-                    const int xi = __shfl_sync(0xffffffffu, xi_prev, rl);
+                    const int xi = tc_table_row(__shfl_sync(0xffffffffu, xi_prev, rl), n_table);
                     if (rl < rows_left) x[rr] = ld_nc_f4(X4 + xi * (D / 4) + C4 * j + ec4);
                 }
             }

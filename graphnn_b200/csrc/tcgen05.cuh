@@ -53,16 +53,13 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
     }
     return __all_sync(0xffffffffu, ok);
 }
-// A table row index that came from the caller's data (a node tag): anything outside [0, n_table) is
-// recorded as S2V_ERR_INVALID_ARG in the status word and replaced by row 0, so no lookup leaves the table.
-__device__ __forceinline__ int tc_table_row(int v, int n_table, s2v_device_status* status)
+// A table row index that came from the caller's data (a node tag) is clamped into [0, n_table) where it is used:
+// one instruction, so no lookup can leave the table whatever the data holds.  DETECTING a bad index is not done in
+// the level kernels (a compare-and-record there cost 6 % of the level's time): the host entry points launch
+// index_range_check_kernel over the index array beside the level, which records S2V_ERR_INVALID_ARG.
+__device__ __forceinline__ int tc_table_row(int v, int n_table)
 {
-    if ((unsigned)v >= (unsigned)n_table) {
-        status->code = S2V_ERR_INVALID_ARG;
-        status->where = 3;
-        return 0;
-    }
-    return v;
+    return (int)min((unsigned)v, (unsigned)(n_table - 1));
 }
 // TF32 head rounded to nearest (add half an ulp of TF32 to the bit pattern, then cut: integer pipe only,
 // no conversion-unit instruction), tail = v - head (exact) cut to TF32.  head + tail differs from v by

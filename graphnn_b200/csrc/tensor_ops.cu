@@ -203,6 +203,20 @@ inline unsigned grid_for(s2v_ctx* ctx, int64_t work_items, int per_block)
     return (unsigned)(b < 1 ? 1 : b);
 }
 
+// Any index outside [0, limit) records S2V_ERR_INVALID_ARG (site 3) in the status word.  Run beside the level kernels,
+// which only clamp the indices they use.
+__global__ void __launch_bounds__(256) index_range_check_kernel(int64_t n, const int32_t* __restrict__ idx, int limit,
+                                                                s2v_device_status* status)
+{
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    bool bad = false;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) bad |= (unsigned)idx[i] >= (unsigned)limit;
+    if (bad) {
+        status->code = S2V_ERR_INVALID_ARG;
+        status->where = 3;
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -297,3 +311,13 @@ int s2v_argmax_f32(s2v_ctx* ctx, s2v_stream stream, int64_t rows, int cols, cons
 }
 
 }  // extern "C"
+
+int s2v_launch_index_check(s2v_ctx* ctx, cudaStream_t st, int64_t n, const int32_t* idx, int limit)
+{
+    if (n <= 0) return S2V_OK;
+    int64_t blocks = (n + 2047) / 2048;
+    if (blocks > (int64_t)ctx->sm_count * 4) blocks = (int64_t)ctx->sm_count * 4;
+    index_range_check_kernel<<<(unsigned)blocks, 256, 0, st>>>(n, idx, limit, ctx->dstatus_dev);
+    S2V_CHECK_LAUNCH(ctx, "index_range_check_kernel");
+    return S2V_OK;
+}

@@ -110,7 +110,9 @@ int s2v_level_rp64_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_t 
 /* Level whose X term is a table lookup: X[i,:] = table[x_index[i],:]; this is
  * X = onehot(tags) * W_in without materialising the product (the reference's
  * node_input * w_n2l, kernel_mean_field.cpp:31, with the one-hot X GetBatch builds,
- * nn_common.h:57-70).  table : [n_table x d], x_index : int32 [n_rows]. */
+ * nn_common.h:57-70).  table : [n_table x d], x_index : int32 [n_rows].  An index outside [0, n_table) never
+ * leaves the table (the kernel clamps it) and is reported through the status word by a small checking launch
+ * that accompanies the level (S2V_ERR_INVALID_ARG); the level's result is then meaningless. */
 int s2v_level_lookup_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_t n_src, int d,
                          const int32_t* row_ptr, const int32_t* col_idx, const float* val, const float* H,
                          const float* W, const float* table, int n_table, const int32_t* x_index, float* out);
