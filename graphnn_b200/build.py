@@ -71,12 +71,13 @@ def build_cxx(force: bool = False) -> dict:
     out = {}
     for name, src in (("s2v_mean_field", os.path.join(CXX_DIR, "examples", "s2v_mean_field.cpp")),
                       ("s2v_classify", os.path.join(CXX_DIR, "examples", "s2v_classify.cpp")),
+                      ("s2v_multi_gpu", os.path.join(CXX_DIR, "examples", "s2v_multi_gpu.cpp")),
                       ("host_interface_test", os.path.join(CXX_DIR, "tests", "host_interface_test.cpp"))):
         exe = os.path.join(CXX_BIN, name)
         if force or _stale(exe, [src, LIB] + headers):
             cmd = ["g++", "-std=c++14", "-O2", "-Wall", "-I", os.path.join(REPO, "include"), "-I",
                    os.path.join(CXX_DIR, "include"), "-I", os.path.join(cuda, "include"), src, "-o", exe,
-                   "-L", PKG, "-ls2v_b200", "-L", os.path.join(cuda, "lib64"), "-lcudart",
+                   "-L", PKG, "-ls2v_b200", "-L", os.path.join(cuda, "lib64"), "-lcudart", "-pthread",
                    "-Wl,-rpath,$ORIGIN/../..", "-Wl,-rpath," + PKG, "-Wl,-rpath," + os.path.join(cuda, "lib64")]
             r = subprocess.run(cmd, capture_output=True, text=True)
             if r.returncode != 0:

@@ -1,6 +1,7 @@
 // Graph pooling (segmented sum), fused readout MLP + softmax + argmax, and the
 // input projection of the structure2vec classifier, for sm_100a.
 #include "common.cuh"
+#include "mma_tf32.cuh"
 
 namespace
 {
@@ -273,6 +274,100 @@ __global__ void __launch_bounds__(256) readout_v4_kernel(int64_t G, int d, int h
     }
 }
 
+// Tensor-core form of the first readout layer for d % 8 == 0 and hidden % 32 == 0: a CTA of eight warps takes 32
+// graphs; warp (gh, hq) computes graphs 16*gh .. +15 x hidden units hq*hidden/4 .. as 3xTF32 mma.sync.m16n8k8 tiles
+// (Y fragments from shared memory split head/tail with rounding, W1 fragments straight from L1/L2 split by
+// truncation, small terms first, fp32 accumulate), then ReLU into the shared hidden tile.  The second layer
+// (hidden x C, C small) and softmax / argmax follow as in the register-tiled form: one warp per graph.
+template <int NT /* 8-column MMA tiles per warp = hidden / 32 */>
+__global__ void __launch_bounds__(256) readout_mma_kernel(int64_t G, int d, int C, const float* __restrict__ Y,
+                                                          const float* __restrict__ W1, const float* __restrict__ W2,
+                                                          float* __restrict__ logits, float* __restrict__ probs,
+                                                          int32_t* __restrict__ pred)
+{
+    extern __shared__ __align__(16) float smm[];
+    constexpr int hidden = NT * 32;
+    const int ys = d + 4, hs = hidden + 4;   // A fragments (rows g, g+8; cols tig, tig+4) hit 32 distinct banks
+    float* Ys = smm;                  // [32][d + 4]
+    float* Hs = Ys + TG4 * ys;        // [32][hidden + 4]
+    float* Ls = Hs + TG4 * hs;        // [32][C]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, tig = lane & 3;        // MMA fragment coordinates
+    const int gh = warp & 1, hq = warp >> 1;
+    const int d4 = d >> 2;
+    for (int64_t g0 = (int64_t)blockIdx.x * TG4; g0 < G; g0 += (int64_t)gridDim.x * TG4) {
+        const int ng = (int)((G - g0) < TG4 ? (G - g0) : TG4);
+        for (int e = threadIdx.x; e < TG4 * d4; e += blockDim.x) {
+            const int gg = e / d4, c = e - gg * d4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (gg < ng) v = __ldcs(reinterpret_cast<const float4*>(Y + (g0 + gg) * d) + c);
+            *reinterpret_cast<float4*>(Ys + gg * ys + 4 * c) = v;
+        }
+        __syncthreads();
+        float c[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
+        const float* ya = Ys + (16 * gh + g) * ys + tig;
+        const float* wb = W1 + (int64_t)tig * hidden + hq * (NT * 8) + g;
+#pragma unroll 2
+        for (int ks = 0; ks < d / 8; ++ks) {
+            uint32_t ah[4], al[4];
+            tf32_split_rn(ya[ks * 8], ah[0], al[0]);
+            tf32_split_rn(ya[8 * ys + ks * 8], ah[1], al[1]);
+            tf32_split_rn(ya[ks * 8 + 4], ah[2], al[2]);
+            tf32_split_rn(ya[8 * ys + ks * 8 + 4], ah[3], al[3]);
+            const float* w = wb + (int64_t)(ks * 8) * hidden;
+            float w0[NT], w1[NT];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                w0[nt] = __ldg(w + nt * 8);
+                w1[nt] = __ldg(w + (int64_t)4 * hidden + nt * 8);
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                uint32_t bh0, bl0, bh1, bl1;
+                tf32_split_trunc(w0[nt], bh0, bl0);
+                tf32_split_trunc(w1[nt], bh1, bl1);
+                mma_tf32(c[nt], al, bh0, bh1);   // small terms first
+                mma_tf32(c[nt], ah, bl0, bl1);
+                mma_tf32(c[nt], ah, bh0, bh1);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            float* h0 = Hs + (16 * gh + g) * hs + hq * (NT * 8) + nt * 8 + 2 * tig;
+            *reinterpret_cast<float2*>(h0) = make_float2(relu_ref(c[nt][0]), relu_ref(c[nt][1]));
+            *reinterpret_cast<float2*>(h0 + 8 * hs) = make_float2(relu_ref(c[nt][2]), relu_ref(c[nt][3]));
+        }
+        __syncthreads();
+        for (int gg = warp; gg < ng; gg += (blockDim.x >> 5)) {
+            for (int cc = 0; cc < C; ++cc) {
+                float acc = 0.f;
+                for (int h = lane; h < hidden; h += 32) acc = fmaf(Hs[gg * hs + h], __ldg(W2 + (int64_t)h * C + cc), acc);
+#pragma unroll
+                for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (lane == 0) Ls[gg * C + cc] = acc;
+            }
+            __syncwarp();
+            if (lane == 0) {
+                const float* l = Ls + gg * C;
+                float mx = l[0];
+                int best = 0;
+                for (int cc = 1; cc < C; ++cc)
+                    if (l[cc] > mx) { mx = l[cc]; best = cc; }
+                float sum = 0.f;
+                for (int cc = 0; cc < C; ++cc) sum += expf(l[cc] - mx);
+                for (int cc = 0; cc < C; ++cc) {
+                    logits[(g0 + gg) * C + cc] = l[cc];
+                    if (probs) probs[(g0 + gg) * C + cc] = expf(l[cc] - mx) / sum;
+                }
+                if (pred) pred[g0 + gg] = best;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 inline unsigned grid_cap(s2v_ctx* ctx, int64_t blocks, int per_sm)
 {
     const int64_t cap = (int64_t)ctx->sm_count * per_sm;
@@ -356,6 +451,19 @@ int s2v_readout_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int d, 
     if (num_graphs == 0) return S2V_OK;
     if (!Y || !W1 || !W2 || !logits) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "readout: NULL pointer");
     const size_t smem4 = sizeof(float) * (size_t)TG4 * ((size_t)d + 4 + hidden + 4 + num_class);
+    if (d % 8 == 0 && (hidden == 256 || hidden == 128) && smem4 <= 96 * 1024 && s2v_aligned16(Y) && num_graphs >= 256) {
+        // batches of hundreds of graphs and the two hidden sizes of the path: first layer on the tensor cores
+        const unsigned grid = grid_cap(ctx, (num_graphs + TG4 - 1) / TG4, 3);
+        if (hidden == 256) {
+            S2V_CUDA_OK(ctx, cudaFuncSetAttribute(readout_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4));
+            readout_mma_kernel<8><<<grid, 256, smem4, s2v_pick_stream(ctx, stream)>>>(num_graphs, d, num_class, Y, W1, W2, logits, probs, pred);
+        } else {
+            S2V_CUDA_OK(ctx, cudaFuncSetAttribute(readout_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4));
+            readout_mma_kernel<4><<<grid, 256, smem4, s2v_pick_stream(ctx, stream)>>>(num_graphs, d, num_class, Y, W1, W2, logits, probs, pred);
+        }
+        S2V_CHECK_LAUNCH(ctx, "readout_mma_kernel");
+        return S2V_OK;
+    }
     if (d % 4 == 0 && hidden % 4 == 0 && smem4 <= 96 * 1024 && s2v_aligned16(Y) && s2v_aligned16(W1)) {
         S2V_CUDA_OK(ctx, cudaFuncSetAttribute(readout_v4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4));
         readout_v4_kernel<<<grid_cap(ctx, (num_graphs + TG4 - 1) / TG4, 2), 256, smem4, s2v_pick_stream(ctx, stream)>>>(

@@ -203,26 +203,17 @@ class GiantGraphLevels:
         self.blocks = [(edges[k], edges[k + 1]) for k in range(self.chunks) if edges[k + 1] > edges[k]]
         # position of global row (r * rows + i) in the block-major layout
         self._edges = torch.tensor([lo for lo, _ in self.blocks] + [rows], dtype=torch.int64, device=dev)
-        col = shard.col_idx.to(torch.int64)
-        real = col < self.n                                   # hub rows (>= n) keep their place behind the blocks
-        r = torch.div(col, rows, rounding_mode="floor")
-        i = col - r * rows
-        k = torch.bucketize(i, self._edges[1:], right=True)
-        lo_k = self._edges[k.clamp(max=len(self.blocks) - 1)]
-        rk = self._edges[(k + 1).clamp(max=len(self.blocks))] - lo_k
-        pos = world * lo_k + r * rk + (i - lo_k)
-        new_col = torch.where(real, pos, col).to(torch.int32)
+        new_col = torch.empty_like(shard.col_idx)
+        piece = 1 << 27                                        # renumber in slices: the int64 temporaries stay small
+        for lo in range(0, shard.nnz, piece):
+            col = shard.col_idx[lo:lo + piece].to(torch.int64)
+            real = col < self.n                                # hub rows (>= n) keep their place behind the blocks
+            new_col[lo:lo + piece] = torch.where(real, self.position_of(col.clamp(max=self.n - 1)), col).to(torch.int32)
+            del col, real
         self.shard = CsrShard(shard.row_lo, shard.row_hi, shard.n_cols, shard.row_ptr, new_col)
-        del col, real, r, i, k, lo_k, rk, pos
         extra = hub_plan.n_hub if hub_plan is not None else 0       # rank-private source rows N .. N+n_hub
         if hub_plan is not None:                                    # the hubs' own column lists use the same layout
-            hc = hub_plan.sub_col_idx.to(torch.int64)
-            r = torch.div(hc, rows, rounding_mode="floor")
-            i = hc - r * rows
-            k = torch.bucketize(i, self._edges[1:], right=True).clamp(max=len(self.blocks) - 1)
-            lo_k = self._edges[k]
-            rk = self._edges[k + 1] - lo_k
-            self.hub_cols = (world * lo_k + r * rk + (i - lo_k)).to(torch.int32)
+            self.hub_cols = self.position_of(hub_plan.sub_col_idx.to(torch.int64)).to(torch.int32)
         # full[0] holds the input H0 and is never written by run(); the levels alternate between full[1] and full[2]
         self.full = [torch.empty((self.n + extra, d), dtype=torch.float32, device=dev) for _ in range(3)]
         self.partial = torch.empty((hub_plan.n_sub, d), dtype=torch.float32, device=dev) if hub_plan is not None else None

@@ -164,3 +164,53 @@ def test_serving_driver_on_text_dataset_and_checkpoint(cxx_bins, oracle_lib, tmp
     want_loss, want_acc, _ = oracle_lib.loss_acc(o["logits"], labels, "oracle")
     words = r.stdout.split()
     assert abs(float(words[2]) - want_loss) <= 1e-5 * max(1.0, want_loss) and abs(float(words[4]) - want_acc) < 1e-6
+
+
+def _gpus_for_test():
+    import torch
+    return max(1, min(2, torch.cuda.device_count()))
+
+
+@pytest.mark.gpu
+def test_multi_gpu_host_program_shard_by_graph(cxx_bins, oracle_lib, tmp_path):
+    """The C++ host that uses only include/s2v_b200.h: graphs sharded over the GPUs present (two if there are two),
+    one host thread per GPU, logits gathered with s2v_gather_logits; against the CPU oracle on the whole batch."""
+    b = synth.molecules_16k(seed=5, num_graphs=1200)
+    write_batch(tmp_path / "batch.bin", b)
+    P = _gpus_for_test()
+    r = subprocess.run([cxx_bins["s2v_multi_gpu"], "shard", str(tmp_path / "batch.bin"), str(tmp_path / "out.bin"), "--gpus", str(P), "--iters", "2"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert f"shard gpus {P} ms_per_iter" in r.stdout
+    raw = open(tmp_path / "out.bin", "rb").read()
+    G, C = b.num_graphs, b.num_class
+    logits = np.frombuffer(raw, np.float32, G * C, 0).reshape(G, C)
+    pred = np.frombuffer(raw, np.int32, G, 4 * G * C)
+    o = oracle_lib.forward(b, "oracle", want_levels=False)
+    assert_close(logits, o["logits"], "sharded logits", scale=max(1.0, float(np.abs(o["logits"]).max())))
+    margin = np.sort(o["logits"], axis=1)
+    safe = (margin[:, -1] - margin[:, -2]) > 1e-4 * np.abs(o["logits"]).max()
+    assert np.array_equal(pred[safe], o["argmax"][safe]) and safe.mean() > 0.9
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("d,chunks", [(64, 3), (128, 1)])
+def test_multi_gpu_host_program_giant_graph(cxx_bins, oracle_lib, tmp_path, d, chunks):
+    """Row-partitioned single graph from the same C++ host: block-major H, one in-place all-gather per block and level."""
+    from graphnn_b200.synth import LevelProblem
+    p = synth.rmat_level(scale=12, edge_factor=8, d=d, seed=4)
+    with open(tmp_path / "graph.bin", "wb") as f:
+        f.write(struct.pack("3q", p.n_rows, p.nnz, d))
+        f.write(np.ascontiguousarray(p.row_ptr, np.int64).tobytes())
+        f.write(np.ascontiguousarray(p.col_idx, np.int32).tobytes())
+        f.write(np.ascontiguousarray(p.H, np.float32).tobytes())
+        f.write(np.ascontiguousarray(p.W, np.float32).tobytes())
+    P = _gpus_for_test()
+    r = subprocess.run([cxx_bins["s2v_multi_gpu"], "giant", str(tmp_path / "graph.bin"), str(tmp_path / "out.bin"), "--gpus", str(P),
+                        "--levels", "2", "--chunks", str(chunks), "--iters", "2"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    got = np.fromfile(tmp_path / "out.bin", np.float32).reshape(p.n_rows, d)
+    H = p.H
+    for _ in range(2):
+        H, _ = oracle_lib.level(LevelProblem(p.n_rows, p.n_src, p.row_ptr, p.col_idx, H, p.W, None), "oracle")
+    assert_close(got, H, f"giant graph on {P} GPU(s)", scale=max(1.0, float(np.abs(H).max())))
