@@ -104,6 +104,7 @@ def load_library():
         "s2v_comm_last_error": (C.c_char_p, [vp]),
         "s2v_allgather_rows_f32": (i32, [vp, vp, i64, i32, vp, vp]),
         "s2v_gather_logits": (i32, [vp, vp, vp, i32, vp, vp, vp, vp]),
+        "s2v_exchange_rows_f32": (i32, [vp, vp, i32, vp, vp, vp, vp, vp]),
         "s2v_infer_edges_host_f32": (i32, [vp, C.POINTER(Model), i64, i64, i64, vp, vp, vp, vp, vp, vp]),
         "s2v_build_n2n_csr_scratch_bytes": (C.c_size_t, [i64, i64]),
         "s2v_build_n2n_csr_f32": (i32, [vp, vp, i64, i64, vp, vp, i32, vp, C.c_size_t, vp, vp, vp]),
@@ -214,6 +215,17 @@ class Comm:
         rows, d = slab.shape
         self.check(self.lib.s2v_allgather_rows_f32(self.h, stream, rows, d, _ptr(slab), _ptr(full)))
 
+    def exchange_rows(self, send, send_offsets, recv, recv_offsets, recv_rows, stream):
+        """Pairwise exchange of rows: rows [send_offsets[p], send_offsets[p+1]) of `send` go to rank p, recv_rows[p]
+        rows from rank p land at row recv_offsets[p] of `recv` (host arrays of counts); asynchronous on `stream`."""
+        so = np.ascontiguousarray(send_offsets, np.int64)
+        ro = np.ascontiguousarray(recv_offsets, np.int64)
+        rr = np.ascontiguousarray(recv_rows, np.int64)
+        assert so.shape[0] == self.world + 1 and ro.shape[0] == self.world and rr.shape[0] == self.world
+        d = int(recv.shape[1] if recv is not None else send.shape[1])
+        self.check(self.lib.s2v_exchange_rows_f32(self.h, stream, d, _ptr(send), so.ctypes.data, _ptr(recv), ro.ctypes.data,
+                                                  rr.ctypes.data))
+
     def gather_logits(self, graphs_per_rank, logits_local, pred_local, logits_all, pred_all, stream):
         counts = np.ascontiguousarray(graphs_per_rank, np.int64)
         num_class = logits_all.shape[1] if logits_all is not None else 1
@@ -275,7 +287,7 @@ class Context:
         """Synchronises `stream` (None = the context's own) and raises if a kernel recorded a status."""
         self.check(self.lib.s2v_stream_status(self.h, stream))
 
-    OPT_VALIDATE_HOST_INPUT, OPT_LEVEL_TC, OPT_GRAPH_TILES = 1, 2, 3
+    OPT_VALIDATE_HOST_INPUT, OPT_LEVEL_TC, OPT_GRAPH_TILES, OPT_RESERVED_SMS = 1, 2, 3, 4
 
     def set_option(self, option: int, value: int):
         self.check(self.lib.s2v_ctx_set_option(self.h, int(option), int(value)))

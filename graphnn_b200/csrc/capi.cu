@@ -104,7 +104,7 @@ int s2v_ctx_create(int device, s2v_ctx** out)
         delete ctx;
         return S2V_ERR_NO_DEVICE;
     }
-    ctx->sm_count = prop.multiProcessorCount;
+    ctx->sm_count = ctx->sm_count_hw = prop.multiProcessorCount;
     ctx->smem_optin = prop.sharedMemPerBlockOptin;
     bool ok = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) == cudaSuccess &&
               cudaHostAlloc((void**)&ctx->dstatus_host, sizeof(s2v_device_status), cudaHostAllocMapped) == cudaSuccess &&
@@ -159,6 +159,10 @@ int s2v_ctx_set_option(s2v_ctx* ctx, int option, int value)
         case S2V_OPT_VALIDATE_HOST_INPUT: ctx->validate_host = value != 0; return S2V_OK;
         case S2V_OPT_LEVEL_TC: ctx->tc_mode = value <= 0 ? 0 : (value >= 2 ? 2 : 1); return S2V_OK;
         case S2V_OPT_GRAPH_TILES: ctx->graph_tiles = value != 0; return S2V_OK;
+        case S2V_OPT_RESERVED_SMS:
+            if (value < 0 || value >= ctx->sm_count_hw) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "set_option: reserved SMs outside [0, SM count)");
+            ctx->sm_count = ctx->sm_count_hw - value;
+            return S2V_OK;
         default: return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "set_option: unknown option");
     }
 }

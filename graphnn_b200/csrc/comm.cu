@@ -3,7 +3,9 @@
 // The inference path needs exactly two exchanges and no reduction:
 //   * shard-by-graph batches: one final gather of the per-rank logits / predictions (ragged: ranks own
 //     different numbers of graphs), done as a group of broadcasts, one rooted at every rank;
-//   * a row-partitioned giant graph: one all-gather of the [rows x d] embedding slabs per level.
+//   * a row-partitioned giant graph: per level either one all-gather of the [rows x d] embedding slabs, or --
+//     when a rank references only a fraction of the remote rows -- a pairwise exchange of exactly those rows
+//     (a group of sends and receives with per-peer counts).
 // NCCL is opened at run time (dlopen of libnccl.so.2, or of the library named by S2V_NCCL_LIBRARY), so the
 // single-GPU product does not depend on it and a process that already has an NCCL loaded -- a torch process
 // -- shares that copy.  Every NCCL status other than success becomes S2V_ERR_COMM with NCCL's own message
@@ -37,6 +39,8 @@ struct nccl_api {
     nccl_result_t (*CommDestroy)(nccl_comm_t) = nullptr;
     nccl_result_t (*AllGather)(const void*, void*, size_t, int, nccl_comm_t, cudaStream_t) = nullptr;
     nccl_result_t (*Broadcast)(const void*, void*, size_t, int, int, nccl_comm_t, cudaStream_t) = nullptr;
+    nccl_result_t (*Send)(const void*, size_t, int, int, nccl_comm_t, cudaStream_t) = nullptr;
+    nccl_result_t (*Recv)(void*, size_t, int, int, nccl_comm_t, cudaStream_t) = nullptr;
     nccl_result_t (*GroupStart)() = nullptr;
     nccl_result_t (*GroupEnd)() = nullptr;
     const char* (*GetErrorString)(nccl_result_t) = nullptr;
@@ -74,6 +78,8 @@ const nccl_api* api()
     g_api.CommDestroy = reinterpret_cast<decltype(g_api.CommDestroy)>(sym("ncclCommDestroy"));
     g_api.AllGather = reinterpret_cast<decltype(g_api.AllGather)>(sym("ncclAllGather"));
     g_api.Broadcast = reinterpret_cast<decltype(g_api.Broadcast)>(sym("ncclBroadcast"));
+    g_api.Send = reinterpret_cast<decltype(g_api.Send)>(sym("ncclSend"));
+    g_api.Recv = reinterpret_cast<decltype(g_api.Recv)>(sym("ncclRecv"));
     g_api.GroupStart = reinterpret_cast<decltype(g_api.GroupStart)>(sym("ncclGroupStart"));
     g_api.GroupEnd = reinterpret_cast<decltype(g_api.GroupEnd)>(sym("ncclGroupEnd"));
     g_api.GetErrorString = reinterpret_cast<decltype(g_api.GetErrorString)>(sym("ncclGetErrorString"));
@@ -243,6 +249,54 @@ int s2v_allgather_rows_f32(s2v_comm* comm, s2v_stream stream, int64_t rows, int 
     if (!guard.ok) return S2V_ERR_CUDA;
     const nccl_result_t r = a->AllGather(slab, full, (size_t)rows * (size_t)d, NCCL_FLOAT32, comm->nccl, static_cast<cudaStream_t>(stream));
     if (r != 0) return comm_fail(comm, nccl_text(a, "ncclAllGather", r));
+    return S2V_OK;
+}
+
+int s2v_exchange_rows_f32(s2v_comm* comm, s2v_stream stream, int d, const float* send, const int64_t* send_offsets,
+                          float* recv, const int64_t* recv_offsets, const int64_t* recv_rows)
+{
+    if (!comm) return S2V_ERR_INVALID_ARG;
+    if (d <= 0 || !send_offsets || !recv_offsets || !recv_rows) {
+        comm_fail(comm, "exchange_rows: bad width or NULL count array");
+        return S2V_ERR_INVALID_ARG;
+    }
+    int64_t n_send = 0, n_recv = 0;
+    for (int p = 0; p < comm->world; ++p) {
+        if (send_offsets[p + 1] < send_offsets[p] || send_offsets[p] < 0 || recv_rows[p] < 0 || recv_offsets[p] < 0) {
+            comm_fail(comm, "exchange_rows: offsets not monotone or a negative count");
+            return S2V_ERR_INVALID_ARG;
+        }
+        n_send += send_offsets[p + 1] - send_offsets[p];
+        n_recv += recv_rows[p];
+    }
+    if ((n_send > 0 && !send) || (n_recv > 0 && !recv)) {
+        comm_fail(comm, "exchange_rows: NULL buffer");
+        return S2V_ERR_INVALID_ARG;
+    }
+    if (n_send == 0 && n_recv == 0) return S2V_OK;
+    const nccl_api* a = api();
+    if (!a) return comm_fail(comm, g_api.load_error);
+    comm_device_guard guard(comm->device);
+    if (!guard.ok) return S2V_ERR_CUDA;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    nccl_result_t r = a->GroupStart();
+    if (r != 0) return comm_fail(comm, nccl_text(a, "ncclGroupStart", r));
+    nccl_result_t first_bad = 0;
+    const char* bad_call = nullptr;
+    for (int p = 0; p < comm->world; ++p) {
+        const int64_t ns = send_offsets[p + 1] - send_offsets[p];
+        if (ns > 0) {
+            r = a->Send(send + send_offsets[p] * d, (size_t)ns * (size_t)d, NCCL_FLOAT32, p, comm->nccl, st);
+            if (r != 0 && !first_bad) { first_bad = r; bad_call = "ncclSend"; }
+        }
+        if (recv_rows[p] > 0) {
+            r = a->Recv(recv + recv_offsets[p] * d, (size_t)recv_rows[p] * (size_t)d, NCCL_FLOAT32, p, comm->nccl, st);
+            if (r != 0 && !first_bad) { first_bad = r; bad_call = "ncclRecv"; }
+        }
+    }
+    r = a->GroupEnd();   // always closed, so that the communicator is not left inside an open group
+    if (first_bad) return comm_fail(comm, nccl_text(a, bad_call, first_bad));
+    if (r != 0) return comm_fail(comm, nccl_text(a, "ncclGroupEnd", r));
     return S2V_OK;
 }
 

@@ -28,7 +28,8 @@ struct s2v_staging {  // grow-only buffers owned by a context (host-buffer entry
 
 struct s2v_ctx {
     int device = 0;
-    int sm_count = 0;
+    int sm_count = 0;      // SMs the persistent kernels size their grids for (hardware count minus S2V_OPT_RESERVED_SMS)
+    int sm_count_hw = 0;
     size_t smem_optin = 0;
     cudaStream_t stream = nullptr;       // the context's own non-blocking stream
     s2v_device_status* dstatus_host = nullptr;  // pinned + mapped

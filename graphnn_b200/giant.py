@@ -270,9 +270,11 @@ class GiantGraphLevels:
         rk = self._edges[k + 1] - lo_k
         return self.world * lo_k + r * rk + (i - lo_k)
 
-    def run(self, W: torch.Tensor, levels: int, X_slab: torch.Tensor | None = None, timed: bool = False) -> torch.Tensor:
+    def run(self, W: torch.Tensor, levels: int, X_slab: torch.Tensor | None = None, timed: bool = False,
+            return_copy: bool = True) -> torch.Tensor | None:
         """Runs `levels` levels from the input set by set_input (which stays intact, so run() can be repeated);
-        returns the local slab of H_L in row order (a copy)."""
+        returns the local slab of H_L in row order (a copy; None with return_copy=False: the result stays in the
+        layout's buffer, see local_slab / level_buffers)."""
         cuda = self.comm_stream is not None
         self.timing = [] if timed and cuda else None
         self.cur = 0
@@ -321,7 +323,7 @@ class GiantGraphLevels:
                 t_end.record(torch.cuda.current_stream())
                 self.timing.append((t_begin, t_compute, t_end, marks))
             self.cur = nxt
-        return self.local_slab()
+        return self.local_slab() if return_copy else None
 
     def level_buffers(self, level: int):
         """(input, output) buffers of level `level` (1-based) of the last run()."""
@@ -337,6 +339,248 @@ class GiantGraphLevels:
             out.append({"compute_ms": t_begin.elapsed_time(t_compute), "exposed_exchange_ms": t_compute.elapsed_time(t_end),
                         "exchange_ms_sum": float(sum(a.elapsed_time(b) for a, b in marks))})
         return out
+
+
+def _exchange_lists(lists, rank: int, world: int, group=None):
+    """lists[p] (1-D int32 tensors) go to rank p; returns what every rank sent to this one.  Set-up plumbing on
+    torch.distributed point-to-point calls (both gloo and nccl have them)."""
+    dev = lists[0].device
+    counts = torch.tensor([int(l.numel()) for l in lists], dtype=torch.int64, device=dev)
+    all_counts = [torch.zeros(world, dtype=torch.int64, device=dev) for _ in range(world)]
+    dist.all_gather(all_counts, counts, group=group)
+    got = [torch.empty(int(all_counts[p][rank]), dtype=lists[0].dtype, device=dev) for p in range(world)]
+    ops = []
+    for p in range(world):
+        if p == rank:
+            got[p] = lists[p].clone()
+            continue
+        if lists[p].numel():
+            ops.append(dist.P2POp(dist.isend, lists[p].contiguous(), p, group))
+        if got[p].numel():
+            ops.append(dist.P2POp(dist.irecv, got[p], p, group))
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+    return got
+
+
+class GiantGraphReferenced:
+    """The same L levels on a row-partitioned graph, but every rank fetches only the rows of H that its own
+    rows reference instead of all of H.  On a power-law graph cut into P slabs a rank references a
+    fraction of the remote rows that shrinks with P (a quarter at P = 8 on R-MAT scale 26), so the exchange
+    volume and the gather table shrink with it.
+
+    Table of a rank:  [own rows 0 .. rows) | referenced remote rows in ascending global order | hub rows].
+    At construction every rank tells each owner which of its rows it needs; per level and row block k the
+    owner packs, for every peer, the requested rows of block k (one row-lookup launch) and one group of
+    sends / receives moves them straight into place in the peers' tables (`exchange_rows`), while block k+1
+    is still being computed.  Column indices are renumbered once to positions in the table.
+
+    `pack_fn(idx, table, out)` : out[i, :] = table[idx[i], :]   (the library's row-lookup kernel on the GPU)
+    `exchange_rows(send, send_offsets, table, recv_offsets, recv_rows)` : the pairwise exchange
+    (s2v_exchange_rows_f32 on the GPU; torch.distributed point-to-point on CPU ranks)."""
+
+    def __init__(self, shard: CsrShard, d: int, rank: int, world: int, level_fn, pack_fn=None, chunks: int = 8, group=None,
+                 hub_plan: HubPlan | None = None, spmm_fn=None, segsum_fn=None, exchange_rows=None):
+        self.hub = hub_plan
+        self.spmm_fn, self.segsum_fn = spmm_fn, segsum_fn
+        if hub_plan is not None:
+            assert spmm_fn is not None and segsum_fn is not None
+            shard = hub_plan.light
+        self.d, self.rank, self.world, self.level_fn, self.group = d, rank, world, level_fn, group
+        dev = shard.col_idx.device
+        self.device = dev
+        rows = shard.rows
+        self.rows, self.n = rows, shard.n_cols
+        assert self.n == rows * world, "equal row slabs: the number of columns must be world * rows"
+        self.row_lo = rank * rows
+        self.chunks = max(1, min(chunks, rows))
+        edges = [rows * k // self.chunks for k in range(self.chunks + 1)]
+        self.blocks = [(edges[k], edges[k + 1]) for k in range(self.chunks) if edges[k + 1] > edges[k]]
+        cuts = torch.tensor([lo for lo, _ in self.blocks] + [rows], dtype=torch.int64, device=dev)
+        piece = 1 << 27
+        # which remote rows do my rows (and my hubs' sub-rows) reference?
+        mask = torch.zeros(self.n, dtype=torch.bool, device=dev)
+        sources = [shard.col_idx] + ([hub_plan.sub_col_idx] if hub_plan is not None else [])
+        for src_cols in sources:
+            for lo in range(0, int(src_cols.numel()), piece):
+                col = src_cols[lo:lo + piece].to(torch.int64)
+                mask[col[col < self.n]] = True
+                del col
+        self.rows_referenced = int(mask.sum())            # own + remote, for the record
+        mask[self.row_lo:self.row_lo + rows] = False
+        self.need = torch.nonzero(mask).flatten()         # int64 global ids, ascending
+        del mask
+        self.n_need = int(self.need.numel())
+        self.n_table = rows + self.n_need
+        # renumber the columns to table positions (hub rows, >= n, move behind the table)
+        new_col = torch.empty_like(shard.col_idx)
+        for lo in range(0, shard.nnz, piece):
+            col = shard.col_idx[lo:lo + piece].to(torch.int64)
+            real = col < self.n
+            new_col[lo:lo + piece] = torch.where(real, self.position_of(col.clamp(max=self.n - 1)), col - self.n + self.n_table).to(torch.int32)
+            del col, real
+        self.shard = CsrShard(shard.row_lo, shard.row_hi, shard.n_cols, shard.row_ptr, new_col)
+        extra = hub_plan.n_hub if hub_plan is not None else 0
+        if hub_plan is not None:
+            self.hub_cols = self.position_of(hub_plan.sub_col_idx.to(torch.int64)).to(torch.int32)
+        # receive side: rows needed from owner s in block k are need[nb[s][k] : nb[s][k+1]]
+        owner_cut = (torch.arange(world, device=dev, dtype=torch.int64) * rows)[:, None] + cuts[None, :]
+        nb = torch.searchsorted(self.need, owner_cut.flatten()).reshape(world, len(self.blocks) + 1).cpu().numpy()
+        self._recv_rows = [[int(nb[s][k + 1] - nb[s][k]) for s in range(world)] for k in range(len(self.blocks))]
+        self._recv_offsets = [[rows + int(nb[s][k]) for s in range(world)] for k in range(len(self.blocks))]
+        # send side: every owner learns which of its rows each peer needs
+        requests = [(self.need[int(nb[s][0]):int(nb[s][-1])] - s * rows).to(torch.int32) for s in range(world)]
+        give = _exchange_lists(requests, rank, world, group) if world > 1 else [requests[0]]
+        self._send_idx, self._send_offsets = [], []
+        for k in range(len(self.blocks)):
+            parts, offs = [], [0]
+            for t in range(world):
+                if t == rank or give[t].numel() == 0:
+                    offs.append(offs[-1])
+                    continue
+                a, b = torch.searchsorted(give[t], cuts[k:k + 2].to(give[t].dtype)).tolist()
+                parts.append(give[t][a:b])
+                offs.append(offs[-1] + (b - a))
+            self._send_idx.append(torch.cat(parts).contiguous() if parts else torch.empty(0, dtype=torch.int32, device=dev))
+            self._send_offsets.append(offs)
+        self.rows_sent_per_level = sum(o[-1] for o in self._send_offsets)
+        max_send = max((o[-1] for o in self._send_offsets), default=0)
+        self.sendbuf = torch.empty((max(max_send, 1), d), dtype=torch.float32, device=dev)
+        # full[0] holds the input H0 and is never written by run(); the levels alternate between full[1] and full[2]
+        self.full = [torch.empty((self.n_table + extra, d), dtype=torch.float32, device=dev) for _ in range(3)]
+        self.partial = torch.empty((hub_plan.n_sub, d), dtype=torch.float32, device=dev) if hub_plan is not None else None
+        self.comm_stream = torch.cuda.Stream(device=dev) if dev.type == "cuda" else None
+        self.pack_fn = pack_fn if pack_fn is not None else (lambda idx, table, out: torch.index_select(table, 0, idx.to(torch.int64), out=out))
+        self.exchange_rows = exchange_rows if exchange_rows is not None else self._exchange_rows_torch
+        rp = self.shard.row_ptr
+        self._block_rp = []
+        for lo, hi in self.blocks:
+            seg = rp[lo:hi + 1]
+            self._block_rp.append((seg - seg[0]).contiguous())
+        self._block_base = [int(rp[lo]) for lo, _ in self.blocks]
+        self._block_nnz = [int(rp[hi]) - int(rp[lo]) for lo, hi in self.blocks]
+        self.timing = None
+
+    def exchange_bytes_per_level(self) -> int:
+        """Bytes this rank receives per level."""
+        return self.n_need * self.d * 4
+
+    def position_of(self, global_rows: torch.Tensor) -> torch.Tensor:
+        """Row index inside the table of the given global node ids (own rows, or remote rows this rank references)."""
+        own = (global_rows >= self.row_lo) & (global_rows < self.row_lo + self.rows)
+        far = torch.searchsorted(self.need, global_rows).clamp(max=max(self.n_need - 1, 0))
+        return torch.where(own, global_rows - self.row_lo, self.rows + far)
+
+    def _exchange_rows_torch(self, send, send_offsets, table, recv_offsets, recv_rows):
+        ops = []
+        for p in range(self.world):
+            ns = send_offsets[p + 1] - send_offsets[p]
+            if p == self.rank:
+                continue
+            if ns > 0:
+                ops.append(dist.P2POp(dist.isend, send[send_offsets[p]:send_offsets[p + 1]].contiguous(), p, self.group))
+            if recv_rows[p] > 0:
+                ops.append(dist.P2POp(dist.irecv, table[recv_offsets[p]:recv_offsets[p] + recv_rows[p]], p, self.group))
+        if ops:
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
+
+    def _ship_block(self, table: torch.Tensor, k: int):
+        """Pack the rows of block k that the peers asked for and exchange them into place."""
+        n_send = self._send_offsets[k][-1]
+        send = self.sendbuf[:max(n_send, 1)]
+        if n_send > 0:
+            self.pack_fn(self._send_idx[k], table[:self.rows], send[:n_send])
+        self.exchange_rows(send, self._send_offsets[k], table, self._recv_offsets[k], self._recv_rows[k])
+
+    def set_input(self, slab: torch.Tensor):
+        """Local slab of H0 -> this rank's table of H0 (own rows + the referenced remote rows)."""
+        self.full[0][:self.rows].copy_(slab)
+        if self.world > 1:
+            for k in range(len(self.blocks)):
+                self._ship_block(self.full[0], k)
+        self.cur = 0
+
+    def local_slab(self) -> torch.Tensor:
+        return self.full[self.cur][:self.rows].clone()
+
+    def run(self, W: torch.Tensor, levels: int, X_slab: torch.Tensor | None = None, timed: bool = False,
+            return_copy: bool = True) -> torch.Tensor | None:
+        """Runs `levels` levels from the input set by set_input (which stays intact); returns the local slab of H_L
+        (a copy; None with return_copy=False: the result stays in rows 0 .. rows of the current table)."""
+        cuda = self.comm_stream is not None
+        self.timing = [] if timed and cuda else None
+        self.cur = 0
+        for _ in range(levels):
+            nxt = 1 if self.cur != 1 else 2
+            src, dst = self.full[self.cur], self.full[nxt]
+            events, marks = [], []
+            if timed and cuda:
+                t_begin = torch.cuda.Event(enable_timing=True)
+                t_begin.record(torch.cuda.current_stream())
+            if self.hub is not None:   # hub sums of this level -> the extra source rows of `src`
+                nt = self.n_table
+                self.spmm_fn(self.hub.sub_row_ptr, self.hub_cols, src[:nt], self.partial)
+                self.segsum_fn(self.hub.hub_seg_ptr, self.partial, src[nt:])
+            for k, (lo, hi) in enumerate(self.blocks):
+                base, nnz = self._block_base[k], self._block_nnz[k]
+                self.level_fn(self._block_rp[k], self.shard.col_idx[base:base + nnz], src, W,
+                              None if X_slab is None else X_slab[lo:hi], dst[lo:hi])
+                if self.world > 1:
+                    if cuda:
+                        ev = torch.cuda.Event()
+                        ev.record(torch.cuda.current_stream())
+                        with torch.cuda.stream(self.comm_stream):
+                            self.comm_stream.wait_event(ev)
+                            if timed:
+                                x0 = torch.cuda.Event(enable_timing=True)
+                                x0.record(self.comm_stream)
+                            self._ship_block(dst, k)
+                            done = torch.cuda.Event(enable_timing=timed)
+                            done.record(self.comm_stream)
+                            if timed:
+                                marks.append((x0, done))
+                        events.append(done)
+                    else:
+                        self._ship_block(dst, k)
+            if timed and cuda:
+                t_compute = torch.cuda.Event(enable_timing=True)
+                t_compute.record(torch.cuda.current_stream())
+            for ev in events:          # the next level reads the whole table
+                torch.cuda.current_stream().wait_event(ev)
+            if timed and cuda:
+                t_end = torch.cuda.Event(enable_timing=True)
+                t_end.record(torch.cuda.current_stream())
+                self.timing.append((t_begin, t_compute, t_end, marks))
+            self.cur = nxt
+        return self.local_slab() if return_copy else None
+
+    level_buffers = GiantGraphLevels.level_buffers
+    timing_summary = GiantGraphLevels.timing_summary
+
+
+def make_comm_exchange_rows(comm):
+    """exchange_rows() for GiantGraphReferenced on the library's NCCL entry point (s2v_exchange_rows_f32), on
+    torch's current stream."""
+
+    def exchange_rows(send, send_offsets, table, recv_offsets, recv_rows):
+        st = torch.cuda.current_stream().cuda_stream
+        comm.exchange_rows(send, send_offsets, table, recv_offsets, recv_rows, st)
+
+    return exchange_rows
+
+
+def make_gpu_pack_fn(ctx):
+    """pack_fn() for GiantGraphReferenced: out[i, :] = table[idx[i], :] with the library's row-lookup kernel
+    (s2v_input_proj_onehot_f32 without the ReLU output), on torch's current stream."""
+
+    def pack(idx, table, out):
+        st = torch.cuda.current_stream().cuda_stream
+        assert st != 0
+        ctx.input_proj_onehot(idx, table, out, None, stream=st)
+
+    return pack
 
 
 def make_comm_exchange(comm, stream_getter=None):

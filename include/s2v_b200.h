@@ -72,9 +72,12 @@ typedef enum s2v_option {
                                         the environment variable S2V_VALIDATE_HOST=0 sets the default to 0) */
     S2V_OPT_LEVEL_TC = 2,            /* tcgen05 level kernel: 0 never, 1 automatic (default), 2 whenever the shape allows
                                         (default from S2V_LEVEL_TC) */
-    S2V_OPT_GRAPH_TILES = 3          /* whole-classifier tile kernel (s2v_graph_tiles_f32) inside s2v_forward_f32 for batches of
+    S2V_OPT_GRAPH_TILES = 3,         /* whole-classifier tile kernel (s2v_graph_tiles_f32) inside s2v_forward_f32 for batches of
                                         small graphs: 0 off (default: on the measured configurations the per-level kernels are
                                         slightly faster), 1 whenever the batch allows (default from S2V_GRAPH_TILES) */
+    S2V_OPT_RESERVED_SMS = 4         /* the persistent kernels size their grids for (SM count - value) SMs, leaving the rest to
+                                        kernels of another stream -- a communication library's, which cannot start while
+                                        one-CTA-per-SM kernels hold every SM (default 0; 0 <= value < SM count) */
 } s2v_option;
 int s2v_ctx_set_option(s2v_ctx* ctx, int option, int value);
 /* Diagnostic, no counterpart in the reference: launches a two-warp kernel whose bounded barrier waits (the
@@ -354,6 +357,14 @@ const char* s2v_comm_last_error(const s2v_comm* comm);
 /* full[r*rows*d ..] = slab of rank r, for equal slabs of rows x d floats (in place if slab already sits at
  * full + rank*rows*d): the per-level exchange of a row-partitioned graph. */
 int s2v_allgather_rows_f32(s2v_comm* comm, s2v_stream stream, int64_t rows, int d, const float* slab, float* full);
+/* Pairwise exchange of rows of d floats with per-peer counts (an all-to-all-v): this rank sends rows
+ * [send_offsets[p], send_offsets[p+1]) of `send` to rank p and receives recv_rows[p] rows from rank p at
+ * recv + recv_offsets[p]*d.  send_offsets (world+1 entries), recv_offsets and recv_rows (world entries) are
+ * HOST arrays; a count of zero skips the peer; rows addressed to the calling rank itself are exchanged like any
+ * other.  One group of ncclSend / ncclRecv.  This is the per-level exchange of a row-partitioned graph when
+ * every rank fetches only the rows of H its own rows reference instead of all of H. */
+int s2v_exchange_rows_f32(s2v_comm* comm, s2v_stream stream, int d, const float* send, const int64_t* send_offsets,
+                          float* recv, const int64_t* recv_offsets, const int64_t* recv_rows);
 /* Gather of the results of a batch sharded by graph: rank r holds graphs_per_rank[r] rows (a HOST array of
  * `world` counts, the same on every rank); logits_all [sum x C] and pred_all [sum] receive all ranks' rows in
  * rank order on EVERY rank.  Either pair (logits / pred) may be NULL. */

@@ -124,8 +124,9 @@ def msgpass_matrix(batch, which: str, impl: str = "oracle", average: bool = Fals
 
 
 def level(prob, impl: str = "oracle", iters: int = 1, rows: int | None = None):
-    """One level; `rows` limits the computation to the first `rows` output rows (a bounded sample)."""
-    lib = _lib(impl)
+    """One level; `rows` limits the computation to the first `rows` output rows (a bounded sample).
+    impl: "oracle", "reference", or "oracle_f64" (oracle_level_f64: all sums in double)."""
+    lib = _lib("oracle" if impl == "oracle_f64" else impl)
     n_rows = prob.n_rows if rows is None else min(int(rows), prob.n_rows)
     d = prob.d
     rp = np.ascontiguousarray(prob.row_ptr[: n_rows + 1], np.int32)
@@ -135,6 +136,12 @@ def level(prob, impl: str = "oracle", iters: int = 1, rows: int | None = None):
     W = np.ascontiguousarray(prob.W, np.float32)
     X = None if prob.X is None else np.ascontiguousarray(prob.X[:n_rows], np.float32)
     out = np.zeros((n_rows, d), np.float32)
+    if impl == "oracle_f64":   # every sum in double: the yardstick for very long rows
+        lib = _lib("oracle")
+        lib.oracle_level_f64.restype = None
+        lib.oracle_level_f64(C.c_int64(n_rows), C.c_int64(d), _p(rp, _i32p), _p(ci, _i32p), None, _p(H, _f32p),
+                             _p(W, _f32p), _p(X, _f32p), _p(out, _f32p))
+        return out, np.zeros(1)
     if impl == "oracle":
         import time
         scratch = np.zeros((2, n_rows, d), np.float32)

@@ -260,6 +260,37 @@ void oracle_level(int64_t n_rows, int64_t d, const int32_t* row_ptr, const int32
 }
 
 /*
+ * The same level with every sum carried in double (row sums and the product with W), rounded to float once at
+ * the end.  Not a restatement of the reference (which accumulates in float in an order its BLAS chooses): it is
+ * the order-independent yardstick for rows so long that two float summation orders differ by more than the
+ * parity bar (a row of a million entries summed sequentially in float carries ~1e-4 relative error itself).
+ * No scratch needed.
+ */
+void oracle_level_f64(int64_t n_rows, int64_t d, const int32_t* row_ptr, const int32_t* col_idx, const float* val,
+                      const float* H, const float* W, const float* X, float* out)
+{
+#pragma omp parallel for num_threads(g_threads) if (g_threads > 1) schedule(dynamic, 16)
+    for (int64_t i = 0; i < n_rows; ++i) {
+        double* s = (double*)calloc((size_t)(2 * d), sizeof(double));
+        double* y = s + d;
+        for (int32_t t = row_ptr[i]; t < row_ptr[i + 1]; ++t) {
+            const double v = val ? (double)val[t] : 1.0;
+            const float* b = H + (int64_t)col_idx[t] * d;
+            for (int64_t j = 0; j < d; ++j) s[j] += v * (double)b[j];
+        }
+        for (int64_t p = 0; p < d; ++p) {
+            const float* w = W + p * d;
+            for (int64_t j = 0; j < d; ++j) y[j] += s[p] * (double)w[j];
+        }
+        for (int64_t j = 0; j < d; ++j) {
+            double r = y[j] + (X ? (double)X[i * d + j] : 0.0);
+            out[i * d + j] = (float)(r < 0.0 ? 0.0 : r);
+        }
+        free(s);
+    }
+}
+
+/*
  * The whole classifier, same argument list as the harness around the reference
  * (ref_s2v_forward): model wiring of kernel_mean_field.cpp:28-47.
  */

@@ -58,6 +58,18 @@ def test_gather_and_allgather_through_the_c_abi(fake_nccl):
         c.allgather_rows(slab, full, None)
         assert np.array_equal(full, slab)
         c.allgather_rows(full, full, None)                           # in place
+        # pairwise exchange with per-peer counts: with one rank, rows 1..2 of `slab` come back at row 1 of `got`
+        got = np.zeros((4, 4), np.float32)
+        c.exchange_rows(slab[1:], [0, 2], got, [1], [2], None)
+        assert np.array_equal(got[1:3], slab[1:3]) and not got[0].any() and not got[3].any()
+        c.exchange_rows(slab, [0, 0], got, [0], [0], None)           # nothing to exchange: no NCCL call
+        for bad in (lambda: c.exchange_rows(slab, [2, 0], got, [0], [0], None),
+                    lambda: c.exchange_rows(slab, [0, 1], got, [0], [-1], None),
+                    lambda: c.exchange_rows(None, [0, 1], got, [0], [1], None)):
+            try:
+                bad(); raise SystemExit("no error raised")
+            except capi.S2VError as e:
+                assert e.status == -1, e
         # argument errors are reported before NCCL is reached
         for bad in (lambda: c.gather_logits([-1], logits, pred, la, pa, None),
                     lambda: c.gather_logits([5], logits, pred, None, None, None)):
@@ -77,6 +89,8 @@ def test_gather_and_allgather_through_the_c_abi(fake_nccl):
     ("ncclCommInitRank", 3, "internal error"),
     ("ncclAllGather", 5, "invalid usage"),
     ("ncclBroadcast", 6, "remote process exited"),
+    ("ncclSend", 3, "internal error"),
+    ("ncclRecv", 2, "unhandled system error"),
     ("ncclGroupEnd", 1, "unhandled cuda error"),
 ])
 def test_failing_nccl_calls_become_comm_errors(fake_nccl, call, code, needle):
@@ -103,6 +117,10 @@ def test_failing_nccl_calls_become_comm_errors(fake_nccl, call, code, needle):
                 p = np.ones(4, np.int32); q = np.zeros(4, np.int32)
                 if fail == "ncclAllGather":
                     hit = expect(lambda: c.allgather_rows(x, y, None))
+                elif fail in ("ncclSend", "ncclRecv"):
+                    hit = expect(lambda: c.exchange_rows(x, [0, 4], y, [0], [4], None))
+                    fake = ctypes.CDLL(os.environ["S2V_NCCL_LIBRARY"])
+                    assert fake.fake_nccl_group_depth() == 0
                 else:
                     hit = expect(lambda: c.gather_logits([4], x, p, y, q, None))
                     # the group was closed although a call inside it failed

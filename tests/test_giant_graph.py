@@ -30,7 +30,7 @@ def _free_port():
     return port
 
 
-def _cpu_rank(rank, world, port, scale, d, levels, chunks, out_dir):
+def _cpu_rank(rank, world, port, scale, d, levels, chunks, out_dir, referenced=False):
     sys.path.insert(0, REPO)
     sys.path.insert(0, os.path.join(REPO, "tests"))
     from oracle import bindings as ob
@@ -58,7 +58,16 @@ def _cpu_rank(rank, world, port, scale, d, levels, chunks, out_dir):
 
     plan = giant.plan_hubs(shard, threshold=40, piece=16)      # low threshold: several hubs at this scale
     assert plan is not None and plan.n_hub > 0
-    g = giant.GiantGraphLevels(shard, d, rank, world, level_fn, chunks=chunks, hub_plan=plan, spmm_fn=spmm_fn, segsum_fn=segsum_fn)
+    if referenced:
+        g = giant.GiantGraphReferenced(shard, d, rank, world, level_fn, chunks=chunks, hub_plan=plan, spmm_fn=spmm_fn, segsum_fn=segsum_fn)
+        # the table holds my rows plus exactly the remote rows my columns name, and fewer than all of them
+        cols = np.unique(np.concatenate([shard.col_idx.numpy()]))
+        lo_, hi_ = giant.row_range(p.n_rows, rank, world)
+        far = cols[(cols < lo_) | (cols >= hi_)]
+        assert g.n_need == len(far) and np.array_equal(g.need.numpy(), far) and g.n_need < p.n_rows - shard.rows
+        assert g.exchange_bytes_per_level() == len(far) * d * 4
+    else:
+        g = giant.GiantGraphLevels(shard, d, rank, world, level_fn, chunks=chunks, hub_plan=plan, spmm_fn=spmm_fn, segsum_fn=segsum_fn)
     lo, hi = giant.row_range(p.n_rows, rank, world)
     g.set_input(torch.from_numpy(p.H[lo:hi]))
     slab = g.run(torch.from_numpy(p.W), levels)
@@ -75,6 +84,18 @@ def test_row_partition_with_allgather_two_cpu_ranks(oracle_lib, tmp_path):
     want = oracle_levels(oracle_lib, p, levels)
     got = np.concatenate([np.load(tmp_path / "slab0.npy"), np.load(tmp_path / "slab1.npy")])
     assert_close(got, want, "two ranks, hub rows split", scale=max(1.0, float(np.abs(want).max())))
+
+
+@pytest.mark.parametrize("world,chunks", [(2, 3), (4, 2)])
+def test_row_partition_exchanging_only_referenced_rows_cpu_ranks(oracle_lib, tmp_path, world, chunks):
+    """Same graph, same levels, but every rank fetches only the rows its columns name (pairwise exchange with
+    per-peer counts): the result must equal the single-process oracle, as the all-gather form does."""
+    scale, d, levels = 9, 32, 2
+    mp.spawn(_cpu_rank, args=(world, _free_port(), scale, d, levels, chunks, str(tmp_path), True), nprocs=world, join=True)
+    p = synth.rmat_level(scale=scale, edge_factor=8, d=d, seed=3)
+    want = oracle_levels(oracle_lib, p, levels)
+    got = np.concatenate([np.load(tmp_path / f"slab{r}.npy") for r in range(world)])
+    assert_close(got, want, f"{world} ranks, referenced rows only", scale=max(1.0, float(np.abs(want).max())))
 
 
 def test_partition_helpers():
@@ -109,6 +130,21 @@ def test_giant_graph_levels_one_gpu(gpu_ctx, oracle_lib, scale, d):
         got = slab.cpu().numpy()
     want = oracle_levels(oracle_lib, p, 2)
     assert_close(got, want, f"rmat scale {scale} d {d}", scale=max(1.0, float(np.abs(want).max())))
+    # the referenced-rows driver on one rank (no exchange; exercises the table layout and the renumbering)
+    with torch.cuda.stream(stream):
+        g2 = giant.GiantGraphReferenced(shard, d, 0, 1, giant.make_gpu_level_fn(gpu_ctx), pack_fn=giant.make_gpu_pack_fn(gpu_ctx), chunks=3,
+                                        hub_plan=plan, spmm_fn=spmm_fn, segsum_fn=segsum_fn)
+        assert g2.n_need == 0
+        g2.set_input(torch.from_numpy(p.H).to(dev))
+        got2 = g2.run(torch.from_numpy(p.W).to(dev), 2)
+        # the pack step is the library's row lookup
+        idx = torch.tensor([5, 0, 5, shard.rows - 1], dtype=torch.int32, device=dev)
+        packed = torch.empty((4, d), dtype=torch.float32, device=dev)
+        giant.make_gpu_pack_fn(gpu_ctx)(idx, got2, packed)
+        stream.synchronize()
+        assert torch.equal(packed, got2[idx.long()])
+    # (not bit-equal to `got`: three blocks instead of two fall below the row count at which the library switches kernels)
+    assert_close(got2.cpu().numpy(), want, f"referenced-rows driver, rmat scale {scale} d {d}", scale=max(1.0, float(np.abs(want).max())))
     # generated-on-device shard: symmetric, deduplicated, sorted rows
     sh = giant.rmat_shard_on_device(10, 8 << 10, 0, 1, dev, seed=5)
     rp, ci = sh.row_ptr.cpu().numpy().astype(np.int64), sh.col_idx.cpu().numpy()

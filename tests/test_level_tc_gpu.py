@@ -173,3 +173,21 @@ def test_bounded_wait_reports_and_context_survives(gpu_ctx, oracle_lib):
     gpu_ctx.synchronize()                                           # the status was cleared
     p = synth.erdos_renyi_level(n=20000, nnz=90000, d=128, seed=3)  # large enough for the tcgen05 kernel
     assert_close(run_level(gpu_ctx, p), oracle_level(oracle_lib, p), "level after a reported time-out")
+
+
+def test_reserved_sms_change_the_grid_not_the_result(tc_ctx):
+    """S2V_OPT_RESERVED_SMS shrinks the persistent grid (SMs left to a communication library's kernels); the tiles
+    are only dealt differently over the CTAs, so the output is bit-identical."""
+    from graphnn_b200 import capi
+    p = synth.erdos_renyi_level(n=148 * 128 * 3 + 5, nnz=400000, d=128, seed=5)
+    a = run_level(tc_ctx, p)
+    tc_ctx.set_option(tc_ctx.OPT_RESERVED_SMS, 20)
+    try:
+        b = run_level(tc_ctx, p)
+        with pytest.raises(capi.S2VError):
+            tc_ctx.set_option(tc_ctx.OPT_RESERVED_SMS, 100000)
+        with pytest.raises(capi.S2VError):
+            tc_ctx.set_option(tc_ctx.OPT_RESERVED_SMS, -1)
+    finally:
+        tc_ctx.set_option(tc_ctx.OPT_RESERVED_SMS, 0)
+    assert np.array_equal(a, b)

@@ -83,6 +83,25 @@ def test_float64_restatement_agrees(oracle_lib):
     assert_close(o["logits"], n["logits"], "logits")
 
 
+def test_level_in_double_agrees_on_short_rows_and_wins_on_long_ones(oracle_lib):
+    """oracle_level_f64 (every sum in double) is the yardstick for very long rows: on ordinary rows it agrees with
+    the float oracle to the parity bar; on one 300,000-entry row of equal positive values the float sequential sum
+    is visibly off while the double one is exact."""
+    prob = synth.erdos_renyi_level(n=600, nnz=4800, d=64, seed=3)
+    a, _ = oracle_lib.level(prob, "oracle")
+    b, _ = oracle_lib.level(prob, "oracle_f64")
+    assert_close(a, b, "level f32 vs f64")
+    d, n = 8, 300_000
+    H = np.full((1, d), 0.1, np.float32)
+    W = np.eye(d, dtype=np.float32)
+    long_row = synth.LevelProblem(1, 1, np.array([0, n], np.int32), np.zeros(n, np.int32), H, W, None)
+    f32, _ = oracle_lib.level(long_row, "oracle")
+    f64, _ = oracle_lib.level(long_row, "oracle_f64")
+    exact = n * float(np.float32(0.1))
+    assert abs(float(f64[0, 0]) - exact) <= 1e-6 * exact
+    assert abs(float(f32[0, 0]) - exact) > 1e-5 * exact
+
+
 def test_generators_shapes():
     b = synth.mutag_like(seed=0)
     assert b.num_graphs == 64 and b.nodes_per_graph.min() >= 10 and b.nodes_per_graph.max() <= 28
