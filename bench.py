@@ -250,14 +250,19 @@ class ClassifierStep:
     device buffers, followed -- on several GPUs -- by the gather of the logits; `profile()` runs the same kernels
     composed from the library's operators so that each launch can be bracketed by CUDA events on its stream."""
 
-    def __init__(self, torch, eng, batch, stream, gather=None, use_tiles=False):
+    TILE_AUTO_MAX_NODES = 160000     # the library's automatic mode takes the tile kernel up to this many nodes
+
+    def __init__(self, torch, eng, batch, stream, gather=None, use_tiles=2):
         from graphnn_b200 import engine
         self.torch, self.eng, self.ctx, self.b, self.stream, self.gather = torch, eng, eng.ctx, batch, stream, gather
         dev = eng.device
         self.hb = engine.build_host_batch(batch)
         self.db = eng.to_device(self.hb)
         G, N, d, C = batch.num_graphs, batch.num_nodes, batch.d, batch.num_class
-        self.tiles = bool(use_tiles) and d == 128 and int(batch.nodes_per_graph.max()) <= 128
+        # use_tiles is the value of S2V_OPT_GRAPH_TILES: 0 never, 1 whenever the batch allows, 2 automatic (the library's default)
+        self.mode = int(use_tiles)
+        self.tiles = (d == 128 and int(batch.nodes_per_graph.max()) <= 128 and
+                      (self.mode == 1 or (self.mode == 2 and N <= self.TILE_AUTO_MAX_NODES)))
         self.Y = torch.empty((G, d), device=dev)
         self.logits = torch.empty((G, C), device=dev)
         self.pred = torch.empty((G,), dtype=torch.int32, device=dev)
@@ -274,7 +279,7 @@ class ClassifierStep:
 
     def __call__(self, timed: bool = False):
         st = self.stream.cuda_stream
-        self.ctx.set_option(self.ctx.OPT_GRAPH_TILES, int(self.tiles))
+        self.ctx.set_option(self.ctx.OPT_GRAPH_TILES, self.mode)
         self.ctx.forward(self.eng.model, self.cb, self.ws_fwd, self.logits, None, self.pred, None, stream=st)
         if self.gather is not None:
             self.gather(self.logits, self.pred, st)       # the final gather of the logits (NCCL through the C ABI)
@@ -576,9 +581,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                               "checked_by": f"the reference build (kind={kind}) on the whole batch, against the logits the e2e entry point returned"}
             if not args.skip_level:
                 line["level_cfg2"] = level_cfg2(ctx, torch, peaks)
-            if not args.tiles and d == 128 and int(full.nodes_per_graph.max()) <= 128:
+            if not step.tiles and d == 128 and int(full.nodes_per_graph.max()) <= 128:
                 # the opt-in whole-classifier tile kernel on the same batch, device-timed, checked against the default path
-                tstep = ClassifierStep(torch, eng, full, stream, None, use_tiles=True)
+                tstep = ClassifierStep(torch, eng, full, stream, None, use_tiles=1)
                 t_ms, _ = device_timed(torch, dist, 1, stream, tstep, min(args.steps, 20), 3, local_rank)
                 ctx.stream_status(stream.cuda_stream)
                 tstep.profile(10)
@@ -860,8 +865,9 @@ def main():
                     help="giant graph on several GPUs: SMs the level kernel leaves to NCCL's kernels (S2V_OPT_RESERVED_SMS)")
     ap.add_argument("--giant-chunks", type=int, default=0, help="giant graph: row blocks per rank (0: 8 for referenced, 4 for allgather)")
     ap.add_argument("--skip-level", action="store_true", help="leave out the 1M-node fused-level measurement")
-    ap.add_argument("--tiles", type=int, default=0, choices=[0, 1],
-                    help="1: run the classifier through the whole-classifier tile kernel (S2V_OPT_GRAPH_TILES) instead of the per-level kernels")
+    ap.add_argument("--tiles", type=int, default=2, choices=[0, 1, 2],
+                    help="S2V_OPT_GRAPH_TILES: 0 per-level kernels only, 1 whole-classifier tile kernel whenever the batch allows, "
+                         "2 the library's default (tile kernel for batches of at most 160,000 nodes)")
     ap.add_argument("--case", default=None, choices=["er_d64", "er_d64_full", "mol_d128", "prot_d64", "mol_tiles", "mol_tiles_small"],
                     help="run one small launch case (for profiler captures) instead of the benchmark")
     ap.add_argument("--launches", type=int, default=3)

@@ -39,7 +39,7 @@ struct s2v_ctx {
     std::mutex mu;
     s2v_staging staging;
     int tc_mode = 1;  // tcgen05 level kernel: 0 never, 1 when the batch is large enough, 2 whenever the shape allows
-    int graph_tiles = 0;    // whole-classifier tile kernel for batches of small graphs: 0 off (default), 1 whenever the batch allows
+    int graph_tiles = 2;    // whole-classifier tile kernel for batches of small graphs: 0 off, 1 whenever the batch allows, 2 automatic
     int validate_host = 1;  // s2v_infer_host_f32 scans its host arrays before launching
 };
 
@@ -144,6 +144,7 @@ int s2v_launch_wait_selftest(s2v_ctx* ctx, cudaStream_t st);
 int s2v_launch_index_check(s2v_ctx* ctx, cudaStream_t st, int64_t n, const int32_t* idx, int limit);
 // whole classifier up to the pooled embeddings for batches of graphs of at most S2V_TILE_NODES nodes (d = 128, tags)
 constexpr int S2V_TILE_NODES = 128;
+constexpr int64_t S2V_TILE_AUTO_MAX_NODES = 160000;   // automatic mode: batches up to this many nodes take the tile kernel
 size_t s2v_graph_tiles_plan_bytes(int64_t num_graphs);
 int s2v_launch_graph_tiles(s2v_ctx* ctx, cudaStream_t st, int64_t G, const int32_t* row_ptr, const int32_t* col_idx,
                            const float* val, const int32_t* graph_ptr, const int32_t* tags, int num_tags,

@@ -73,8 +73,9 @@ typedef enum s2v_option {
     S2V_OPT_LEVEL_TC = 2,            /* tcgen05 level kernel: 0 never, 1 automatic (default), 2 whenever the shape allows
                                         (default from S2V_LEVEL_TC) */
     S2V_OPT_GRAPH_TILES = 3,         /* whole-classifier tile kernel (s2v_graph_tiles_f32) inside s2v_forward_f32 for batches of
-                                        small graphs: 0 off (default: on the measured configurations the per-level kernels are
-                                        slightly faster), 1 whenever the batch allows (default from S2V_GRAPH_TILES) */
+                                        small graphs: 0 never, 1 whenever the batch allows, 2 automatic (default: batches of at
+                                        most 160,000 nodes, where one launch beats the per-level kernels by 1.1x - 2.2x; larger
+                                        batches stream better through the per-level kernels).  Default from S2V_GRAPH_TILES */
     S2V_OPT_RESERVED_SMS = 4         /* the persistent kernels size their grids for (SM count - value) SMs, leaving the rest to
                                         kernels of another stream -- a communication library's, which cannot start while
                                         one-CTA-per-SM kernels hold every SM (default 0; 0 <= value < SM count) */
@@ -319,24 +320,27 @@ int s2v_build_n2n_csr_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_nodes, in
  * `model` weights are DEVICE pointers (parameters live on the device in the
  * reference too).  Writes logits_host [G x C] and pred_host [G] (either may be NULL)
  * and returns after they are valid.  Staging buffers are owned by ctx and only grow.
- * Before anything is launched the host arrays are scanned (unless S2V_OPT_VALIDATE_HOST_INPUT is 0): row_ptr and
- * graph_ptr monotone with the right ends, 0 <= col_idx < N, 0 <= tags < F; a violation returns S2V_ERR_BAD_CSR
- * (or S2V_ERR_INVALID_ARG for a tag) with nothing copied or launched. */
+ * The host arrays are scanned (unless S2V_OPT_VALIDATE_HOST_INPUT is 0): row_ptr and graph_ptr monotone with the
+ * right ends, 0 <= col_idx < N, 0 <= tags < F; a violation returns S2V_ERR_BAD_CSR (or S2V_ERR_INVALID_ARG for a
+ * tag) and no result is written.  Offsets and column indices are scanned before anything is copied or launched;
+ * tags, which the kernels clamp into the table themselves, are scanned while the device already works. */
 int s2v_infer_host_f32(s2v_ctx* ctx, const s2v_model* model, const s2v_batch* batch_host, float* logits_host,
                        int32_t* pred_host);
 
 /* The same from a raw directed edge list in AddEdge order (what GraphStruct::edge_list holds after GetBatch,
  * src/util/graph_struct.cpp:62-70, nn_common.h:76-90): the edge list is uploaded and the node-to-node CSR is
  * built on the device by s2v_build_n2n_csr_f32, so the host does no sorting at all.  All array arguments are HOST
- * pointers (pinned memory makes the copies asynchronous); validation as for s2v_infer_host_f32. */
+ * pointers (pinned memory makes the copies asynchronous).  graph_ptr is checked before anything is launched; edge
+ * endpoints and tags are scanned on the host while the device already works (the device-side builder drops and
+ * reports an edge outside [0, N), the kernels clamp a tag), with the same return codes as s2v_infer_host_f32. */
 int s2v_infer_edges_host_f32(s2v_ctx* ctx, const s2v_model* model, int64_t num_graphs, int64_t num_nodes, int64_t num_edges,
                              const int32_t* edge_src_host, const int32_t* edge_dst_host, const int32_t* graph_ptr_host,
                              const int32_t* tags_host, float* logits_host, int32_t* pred_host);
 
 /* ---- several GPUs (no counterpart in the reference, which drives one GPU: src/tensor/gpu_handle.cu:17-44).
  * The path needs two exchanges and no reduction: the final gather of the logits when a batch is sharded by
- * graph, and one all-gather of the embedding slabs per level when a single giant graph is partitioned by rows.
- * Both go straight to NCCL, which is opened at run time (libnccl.so.2, or the library named by the environment
+ * graph, and one exchange of embedding rows per level when a single giant graph is partitioned by rows (all
+ * slabs to everyone, or to every rank only the rows it references).  All go straight to NCCL, which is opened at run time (libnccl.so.2, or the library named by the environment
  * variable S2V_NCCL_LIBRARY); a process that already has an NCCL loaded shares it.  Any NCCL failure is returned
  * as S2V_ERR_COMM with NCCL's message in s2v_comm_last_error (pass NULL for failures before a communicator
  * exists).  Calls are asynchronous on `stream`, which belongs to the communicator's device. */

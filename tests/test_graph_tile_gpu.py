@@ -194,14 +194,17 @@ def test_host_entry_validates_before_launching():
     logits, pred = eng.infer_host(hb)                   # a good batch first (staging allocated)
     n0 = eng.ctx.launches
 
-    def expect(status, mutate):
+    def expect(status, mutate, before_launch=True):
+        nonlocal n0
         rp, ci, gp, tg = (t.clone() for t in (hb.row_ptr, hb.col_idx, hb.graph_ptr, hb.tags))
         mutate(rp, ci, gp, tg)
         bad = engine.HostBatch(hb.num_graphs, hb.num_nodes, rp, ci, gp, tg, hb.max_graph_nodes)
         with pytest.raises(capi.S2VError) as e:
             eng.infer_host(bad)
         assert e.value.status == status
-        assert eng.ctx.launches == n0                   # nothing was launched
+        if before_launch:
+            assert eng.ctx.launches == n0               # nothing was launched
+        n0 = eng.ctx.launches
 
     def set_(t, i, v):
         t[i] = v
@@ -209,7 +212,11 @@ def test_host_entry_validates_before_launching():
     expect(-4, lambda rp, ci, gp, tg: set_(ci, 0, -1))
     expect(-4, lambda rp, ci, gp, tg: set_(rp, 10, int(rp[11]) + 1))      # row offsets not monotone
     expect(-4, lambda rp, ci, gp, tg: set_(gp, 3, int(gp[4]) + 1))        # graph offsets not monotone
-    expect(-1, lambda rp, ci, gp, tg: set_(tg, 7, b.num_tags))            # tag == F
+    # a tag outside the table is clamped by the kernels, so its scan runs beside the device work: still an error, from the host scan
+    expect(-1, lambda rp, ci, gp, tg: set_(tg, 7, b.num_tags), before_launch=False)
+    assert "tag outside" in eng.ctx.lib.s2v_last_error(eng.ctx.h).decode()
+    l1, p1 = eng.infer_host(hb)                                          # and the context carries nothing over
+    assert np.array_equal(l1, logits) and np.array_equal(p1, pred)
     # with validation switched off the same good batch still runs
     eng.ctx.set_option(eng.ctx.OPT_VALIDATE_HOST_INPUT, 0)
     l2, p2 = eng.infer_host(hb)
