@@ -461,6 +461,29 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         torch.cuda.synchronize()
         return (time.perf_counter() - w0) * 1e3
 
+    # two batches in flight: every step still uploads its inputs and downloads its results, but step i+1 is
+    # submitted (s2v_infer_edges_host_submit, the other lane) before step i is waited for
+    pipe_out = [(np.empty((G, C), np.float32), np.empty((G,), np.int32)) for _ in range(2)]
+
+    def submit(i):
+        ctx.infer_edges_host_submit(i % 2, eng.model, G, N, es.numpy(), ed.numpy(), hb.graph_ptr.numpy(), hb.tags.numpy(), *pipe_out[i % 2])
+
+    def time_pipelined() -> float:
+        for rep in range(2):                                 # first pass: warm-up (the second lane's staging is allocated)
+            n = 4 if rep == 0 else e2e_steps
+            if rep == 1:
+                if world > 1:
+                    dist.barrier()
+                torch.cuda.synchronize()
+                w0 = time.perf_counter()
+            submit(0)
+            for i in range(n):
+                if i + 1 < n:
+                    submit(i + 1)
+                ctx.infer_host_wait(i % 2)
+        return (time.perf_counter() - w0) * 1e3
+
+    e2e_pipe_ms = time_pipelined()
     e2e_csr_ms = time_e2e(e2e_csr)
     e2e_sorted_ms = time_e2e(e2e_host_sorted)
     ctx.set_option(ctx.OPT_VALIDATE_HOST_INPUT, 0)
@@ -468,9 +491,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ctx.set_option(ctx.OPT_VALIDATE_HOST_INPUT, 1)
     e2e_edges_ms = time_e2e(e2e_edges)                   # last: logits_h / pred_h below come from this entry point
     assert np.array_equal(pred_h, step.pred.cpu().numpy()), "host-buffer path and device path disagree"
+    assert all(np.array_equal(p, pred_h) and np.array_equal(l, logits_h) for l, p in pipe_out), "lanes and synchronous entry disagree"
 
-    elapsed_ms, e2e_edges_ms, e2e_csr_ms, e2e_sorted_ms, e2e_edges_novalidate_ms = max_over_ranks(
-        torch, dist, world, dev, [elapsed_ms, e2e_edges_ms, e2e_csr_ms, e2e_sorted_ms, e2e_edges_novalidate_ms])
+    elapsed_ms, e2e_edges_ms, e2e_csr_ms, e2e_sorted_ms, e2e_edges_novalidate_ms, e2e_pipe_ms = max_over_ranks(
+        torch, dist, world, dev, [elapsed_ms, e2e_edges_ms, e2e_csr_ms, e2e_sorted_ms, e2e_edges_novalidate_ms, e2e_pipe_ms])
 
     # ---- the same with 16,384 graphs PER rank (weak scaling), device-timed only
     weak = None
@@ -506,6 +530,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     "steps": e2e_steps, "ms_per_step": e2e_edges_ms / e2e_steps,
                     "includes": "s2v_infer_edges_host_f32: host validation scan, upload of the raw edge list + tags + graph offsets, CSR built on "
                                 "the device, forward, download of logits and predictions (what one FeedForward of the reference covers)",
+                    "two_in_flight": {"value": total_graphs * e2e_steps / (e2e_pipe_ms * 1e-3), "ms_per_step": e2e_pipe_ms / e2e_steps,
+                                      "includes": "the same work per step (same uploads and downloads), but step i+1 is submitted on the "
+                                                  "context's other lane (s2v_infer_edges_host_submit) before step i is waited for "
+                                                  "(s2v_infer_host_wait): the transfers of one batch overlap the kernels of the other"},
                     "without_host_validation": {"value": total_graphs * e2e_steps / (e2e_edges_novalidate_ms * 1e-3),
                                                 "ms_per_step": e2e_edges_novalidate_ms / e2e_steps},
                     "from_host_csr": {"value": total_graphs * e2e_steps / (e2e_csr_ms * 1e-3), "ms_per_step": e2e_csr_ms / e2e_steps,
@@ -799,9 +827,36 @@ def run_case(args):
                 out are 134 MB each, above the 126 MB L2);  er_d64_full: the full problem
     mol_d128    per-level kernel on 16,384 molecule-like graphs, d=128, X looked up from W_in by tag
     prot_d64    per-level kernel on 2,048 protein-like graphs, d=64
-    mol_tiles   tile kernel (projection + 4 levels + pooling) on 16,384 molecule-like graphs;  mol_tiles_small: 4,096 graphs"""
+    mol_tiles   tile kernel (projection + 4 levels + pooling) on 16,384 molecule-like graphs;  mol_tiles_small: 4,096 graphs
+    mol_paths   whole forward pass (s2v_forward_f32) on 512 .. 16,384 molecule-like graphs through the per-level kernels
+                and through the tile kernel, one line per batch size"""
     import torch
     from graphnn_b200 import capi
+    if args.case == "mol_paths":
+        from graphnn_b200 import engine
+        stream = torch.cuda.Stream()
+        torch.cuda.set_stream(stream)
+        st = stream.cuda_stream
+        for G in (512, 1024, 2048, 4096, 8192, 16384):
+            b = synth.molecules_16k(seed=0, weight_seed=WEIGHT_SEED, num_graphs=G)
+            eng = engine.S2VInference(b.weights, b.levels)
+            db = eng.to_device(engine.build_host_batch(b))
+            ms = []
+            for mode in (0, 1):
+                eng.ctx.set_option(eng.ctx.OPT_GRAPH_TILES, mode)
+                for _ in range(5):
+                    eng.forward(db, stream=st)
+                torch.cuda.synchronize()
+                a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                for _ in range(50):
+                    eng.forward(db, stream=st)
+                e.record(stream)
+                torch.cuda.synchronize()
+                eng.ctx.stream_status(st)
+                ms.append(a.elapsed_time(e) / 50)
+            print(f"G={G} N={b.num_nodes} per-level kernels {ms[0]:.4f} ms  tile kernel {ms[1]:.4f} ms  ratio {ms[0] / ms[1]:.2f}", flush=True)
+        return
     ctx = capi.Context(0)
     dev = torch.device("cuda", 0)
     stream = torch.cuda.Stream(device=dev)
@@ -868,7 +923,7 @@ def main():
     ap.add_argument("--tiles", type=int, default=2, choices=[0, 1, 2],
                     help="S2V_OPT_GRAPH_TILES: 0 per-level kernels only, 1 whole-classifier tile kernel whenever the batch allows, "
                          "2 the library's default (tile kernel for batches of at most 160,000 nodes)")
-    ap.add_argument("--case", default=None, choices=["er_d64", "er_d64_full", "mol_d128", "prot_d64", "mol_tiles", "mol_tiles_small"],
+    ap.add_argument("--case", default=None, choices=["er_d64", "er_d64_full", "mol_d128", "prot_d64", "mol_tiles", "mol_tiles_small", "mol_paths"],
                     help="run one small launch case (for profiler captures) instead of the benchmark")
     ap.add_argument("--launches", type=int, default=3)
     args = ap.parse_args()

@@ -106,6 +106,8 @@ def load_library():
         "s2v_gather_logits": (i32, [vp, vp, vp, i32, vp, vp, vp, vp]),
         "s2v_exchange_rows_f32": (i32, [vp, vp, i32, vp, vp, vp, vp, vp]),
         "s2v_infer_edges_host_f32": (i32, [vp, C.POINTER(Model), i64, i64, i64, vp, vp, vp, vp, vp, vp]),
+        "s2v_infer_edges_host_submit": (i32, [vp, i32, C.POINTER(Model), i64, i64, i64, vp, vp, vp, vp, vp, vp]),
+        "s2v_infer_host_wait": (i32, [vp, i32]),
         "s2v_build_n2n_csr_scratch_bytes": (C.c_size_t, [i64, i64]),
         "s2v_build_n2n_csr_f32": (i32, [vp, vp, i64, i64, vp, vp, i32, vp, C.c_size_t, vp, vp, vp]),
     }
@@ -433,6 +435,17 @@ class Context:
                                                _ptr(edge_src), _ptr(edge_dst), _ptr(graph_ptr), _ptr(tags),
                                                _ptr(logits_host), _ptr(pred_host))
         self.check(rc)
+
+    def infer_edges_host_submit(self, lane: int, model: Model, num_graphs, num_nodes, edge_src, edge_dst, graph_ptr, tags,
+                                logits_host, pred_host):
+        """s2v_infer_edges_host_submit: the same batch put on lane 0 or 1 without waiting for it; the arrays must
+        stay alive and untouched until infer_host_wait(lane) returns."""
+        self.check(self.lib.s2v_infer_edges_host_submit(self.h, int(lane), C.byref(model), num_graphs, num_nodes,
+                                                        int(edge_src.shape[0]), _ptr(edge_src), _ptr(edge_dst), _ptr(graph_ptr),
+                                                        _ptr(tags), _ptr(logits_host), _ptr(pred_host)))
+
+    def infer_host_wait(self, lane: int):
+        self.check(self.lib.s2v_infer_host_wait(self.h, int(lane)))
 
     def infer_host(self, model: Model, batch_host: Batch, logits_host: np.ndarray | None,
                    pred_host: np.ndarray | None):

@@ -50,9 +50,8 @@ int check_level_args(s2v_ctx* ctx, int64_t n_rows, int64_t n_src, int d, const v
     return S2V_OK;
 }
 
-int ensure_staging(s2v_ctx* ctx, size_t dev_bytes, size_t pinned_bytes)
+int ensure_staging(s2v_ctx* ctx, s2v_staging& s, size_t dev_bytes, size_t pinned_bytes)
 {
-    s2v_staging& s = ctx->staging;
     if (dev_bytes > s.dev_bytes) {
         if (s.dev) cudaFree(s.dev);
         s.dev = nullptr;
@@ -130,8 +129,11 @@ int s2v_ctx_destroy(s2v_ctx* ctx)
         s2v_device_guard guard(ctx->device);
         if (ctx->stream) { cudaStreamSynchronize(ctx->stream); cudaStreamDestroy(ctx->stream); }
         if (ctx->dstatus_host) cudaFreeHost(ctx->dstatus_host);
-        if (ctx->staging.dev) cudaFree(ctx->staging.dev);
-        if (ctx->staging.pinned) cudaFreeHost(ctx->staging.pinned);
+        for (s2v_lane& lane : ctx->lanes) {
+            if (lane.stream && lane.stream != ctx->stream) { cudaStreamSynchronize(lane.stream); cudaStreamDestroy(lane.stream); }
+            if (lane.staging.dev) cudaFree(lane.staging.dev);
+            if (lane.staging.pinned) cudaFreeHost(lane.staging.pinned);
+        }
     }
     delete ctx;
     return S2V_OK;
@@ -590,6 +592,7 @@ int s2v_infer_host_f32(s2v_ctx* ctx, const s2v_model* model, const s2v_batch* hb
 {
     S2V_ENTER(ctx);
     if (!model || !hb) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_host: NULL model or batch");
+    if (ctx->lanes[0].busy) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_host: lane 0 holds a submitted batch; wait for it first");
     const int64_t N = hb->num_nodes, G = hb->num_graphs, E = hb->num_edges;
     const int d = model->d, C = model->num_class, F = model->num_feat;
     if (N < 0 || G < 0 || E < 0 || d <= 0 || C <= 0 || F <= 0)
@@ -652,9 +655,9 @@ int s2v_infer_host_f32(s2v_ctx* ctx, const s2v_model* model, const s2v_batch* hb
     const size_t o_pred = take(sizeof(int32_t) * (size_t)G);
     const size_t ws_bytes = s2v_forward_workspace_bytes(N, G, d);
     const size_t o_ws = take(ws_bytes);
-    int rc = ensure_staging(ctx, off, sizeof(float) * (size_t)G * C + sizeof(int32_t) * (size_t)G + 512);
+    int rc = ensure_staging(ctx, ctx->lanes[0].staging, off, sizeof(float) * (size_t)G * C + sizeof(int32_t) * (size_t)G + 512);
     if (rc != S2V_OK) return rc;
-    unsigned char* dev = static_cast<unsigned char*>(ctx->staging.dev);
+    unsigned char* dev = static_cast<unsigned char*>(ctx->lanes[0].staging.dev);
     cudaStream_t st = ctx->stream;
 
     S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_rp, hb->n2n_row_ptr, sizeof(int32_t) * (size_t)(N + 1), cudaMemcpyHostToDevice, st));
@@ -681,8 +684,8 @@ int s2v_infer_host_f32(s2v_ctx* ctx, const s2v_model* model, const s2v_batch* hb
     rc = s2v_forward_f32(ctx, st, model, &db, dev + o_ws, ws_bytes, d_logits, nullptr, d_pred, nullptr);
     if (rc != S2V_OK) return rc;
 
-    float* p_logits = static_cast<float*>(ctx->staging.pinned);
-    int32_t* p_pred = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(ctx->staging.pinned) +
+    float* p_logits = static_cast<float*>(ctx->lanes[0].staging.pinned);
+    int32_t* p_pred = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(ctx->lanes[0].staging.pinned) +
                                                  align_up(sizeof(float) * (size_t)G * C, 256));
     if (logits_host)
         S2V_CUDA_OK(ctx, cudaMemcpyAsync(p_logits, d_logits, sizeof(float) * (size_t)G * C, cudaMemcpyDeviceToHost, st));
@@ -698,16 +701,20 @@ int s2v_infer_host_f32(s2v_ctx* ctx, const s2v_model* model, const s2v_batch* hb
     return S2V_OK;
 }
 
-// Same from a raw edge list: the CSR is built on the device (s2v_build_n2n_csr_f32).
-int s2v_infer_edges_host_f32(s2v_ctx* ctx, const s2v_model* model, int64_t num_graphs, int64_t num_nodes, int64_t num_edges,
-                             const int32_t* edge_src_host, const int32_t* edge_dst_host, const int32_t* graph_ptr_host,
-                             const int32_t* tags_host, float* logits_host, int32_t* pred_host)
+// Same from a raw edge list: the CSR is built on the device (s2v_build_n2n_csr_f32).  Split in two halves so that
+// two batches can be in flight: edges_enqueue puts everything of one batch on a lane's stream (upload, CSR build,
+// forward, download into the lane's pinned buffer) and scans the host arrays while the device works; lane_finish
+// waits for the lane, reports, and hands the results to the caller.
+static int edges_enqueue(s2v_ctx* ctx, s2v_lane& lane, const s2v_model* model, int64_t num_graphs, int64_t num_nodes, int64_t num_edges,
+                         const int32_t* edge_src_host, const int32_t* edge_dst_host, const int32_t* graph_ptr_host,
+                         const int32_t* tags_host, float* logits_host, int32_t* pred_host)
 {
-    S2V_ENTER(ctx);
     if (!model) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_edges: NULL model");
     const int64_t N = num_nodes, G = num_graphs, E = num_edges;
     const int d = model->d, C = model->num_class, F = model->num_feat;
     if (N < 0 || G < 0 || E < 0 || d <= 0 || C <= 0 || F <= 0) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_edges: bad shape");
+    lane.G = 0;
+    lane.bad_edge = lane.bad_tag = 0;
     if (G == 0) return S2V_OK;
     if (!graph_ptr_host || !tags_host || (E > 0 && (!edge_src_host || !edge_dst_host)))
         return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_edges: NULL batch array");
@@ -727,19 +734,6 @@ int s2v_infer_edges_host_f32(s2v_ctx* ctx, const s2v_model* model, int64_t num_g
         }
         if (bad) return s2v_fail(ctx, S2V_ERR_BAD_CSR, "infer_edges: graph_ptr not monotone or an edge endpoint outside [0, N)");
     }
-    auto scan_indices = [&](int& bad_edge, int& bad_tag) {
-        int T = omp_get_max_threads();
-        if (T > 16) T = 16;
-        int be = 0, bt = 0;
-#pragma omp parallel for num_threads(T) schedule(static) reduction(| : bt) if (N >= (1 << 15))
-        for (int64_t i = 0; i < N; ++i)
-            if (tags_host[i] < 0 || tags_host[i] >= F) bt |= 1;
-#pragma omp parallel for num_threads(T) schedule(static) reduction(| : be) if (E >= (1 << 15))
-        for (int64_t e = 0; e < E; ++e)
-            if (edge_src_host[e] < 0 || edge_src_host[e] >= N || edge_dst_host[e] < 0 || edge_dst_host[e] >= N) be |= 1;
-        bad_edge = be;
-        bad_tag = bt;
-    };
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
     const size_t o_es = take(sizeof(int32_t) * (size_t)E);
@@ -754,16 +748,17 @@ int s2v_infer_edges_host_f32(s2v_ctx* ctx, const s2v_model* model, int64_t num_g
     const size_t o_sc = take(sc_bytes);
     const size_t ws_bytes = s2v_forward_workspace_bytes(N, G, d);
     const size_t o_ws = take(ws_bytes);
-    int rc = ensure_staging(ctx, off, sizeof(float) * (size_t)G * C + sizeof(int32_t) * (size_t)G + 512);
+    int rc = ensure_staging(ctx, lane.staging, off, sizeof(float) * (size_t)G * C + sizeof(int32_t) * (size_t)G + 512);
     if (rc != S2V_OK) return rc;
-    unsigned char* dev = static_cast<unsigned char*>(ctx->staging.dev);
-    cudaStream_t st = ctx->stream;
+    unsigned char* dev = static_cast<unsigned char*>(lane.staging.dev);
+    cudaStream_t st = lane.stream;
     if (E > 0) {
         S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_es, edge_src_host, sizeof(int32_t) * (size_t)E, cudaMemcpyHostToDevice, st));
         S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_ed, edge_dst_host, sizeof(int32_t) * (size_t)E, cudaMemcpyHostToDevice, st));
     }
     S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_gp, graph_ptr_host, sizeof(int32_t) * (size_t)(G + 1), cudaMemcpyHostToDevice, st));
     S2V_CUDA_OK(ctx, cudaMemcpyAsync(dev + o_tg, tags_host, sizeof(int32_t) * (size_t)N, cudaMemcpyHostToDevice, st));
+    lane.busy = true;   // from here on the lane's stream holds work that reads the caller's arrays
     rc = s2v_build_n2n_csr_f32(ctx, st, N, E, reinterpret_cast<const int32_t*>(dev + o_es), reinterpret_cast<const int32_t*>(dev + o_ed),
                                0, dev + o_sc, sc_bytes, reinterpret_cast<int32_t*>(dev + o_rp), reinterpret_cast<int32_t*>(dev + o_ci),
                                nullptr);
@@ -781,22 +776,101 @@ int s2v_infer_edges_host_f32(s2v_ctx* ctx, const s2v_model* model, int64_t num_g
     int32_t* d_pred = reinterpret_cast<int32_t*>(dev + o_pred);
     rc = s2v_forward_f32(ctx, st, model, &db, dev + o_ws, ws_bytes, d_logits, nullptr, d_pred, nullptr);
     if (rc != S2V_OK) return rc;
-    float* p_logits = static_cast<float*>(ctx->staging.pinned);
-    int32_t* p_pred = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(ctx->staging.pinned) +
+    float* p_logits = static_cast<float*>(lane.staging.pinned);
+    int32_t* p_pred = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(lane.staging.pinned) +
                                                  align_up(sizeof(float) * (size_t)G * C, 256));
     if (logits_host)
         S2V_CUDA_OK(ctx, cudaMemcpyAsync(p_logits, d_logits, sizeof(float) * (size_t)G * C, cudaMemcpyDeviceToHost, st));
     if (pred_host)
         S2V_CUDA_OK(ctx, cudaMemcpyAsync(p_pred, d_pred, sizeof(int32_t) * (size_t)G, cudaMemcpyDeviceToHost, st));
-    int bad_edge = 0, bad_tag = 0;
-    if (ctx->validate_host) scan_indices(bad_edge, bad_tag);   // on the host, while the device works
-    rc = s2v_ctx_synchronize(ctx);
-    if (bad_edge) return s2v_fail(ctx, S2V_ERR_BAD_CSR, "infer_edges: graph_ptr not monotone or an edge endpoint outside [0, N)");
-    if (bad_tag) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_edges: a node tag outside [0, num_feat)");
-    if (rc != S2V_OK) return rc;
-    if (logits_host) std::memcpy(logits_host, p_logits, sizeof(float) * (size_t)G * C);
-    if (pred_host) std::memcpy(pred_host, p_pred, sizeof(int32_t) * (size_t)G);
+    lane.G = G;
+    lane.C = C;
+    lane.logits_host = logits_host;
+    lane.pred_host = pred_host;
+    if (ctx->validate_host) {   // on the host, while the device works
+        int T = omp_get_max_threads();
+        if (T > 16) T = 16;
+        int be = 0, bt = 0;
+#pragma omp parallel for num_threads(T) schedule(static) reduction(| : bt) if (N >= (1 << 15))
+        for (int64_t i = 0; i < N; ++i)
+            if (tags_host[i] < 0 || tags_host[i] >= F) bt |= 1;
+#pragma omp parallel for num_threads(T) schedule(static) reduction(| : be) if (E >= (1 << 15))
+        for (int64_t e = 0; e < E; ++e)
+            if (edge_src_host[e] < 0 || edge_src_host[e] >= N || edge_dst_host[e] < 0 || edge_dst_host[e] >= N) be |= 1;
+        lane.bad_edge = be;
+        lane.bad_tag = bt;
+    }
     return S2V_OK;
+}
+
+static int lane_finish(s2v_ctx* ctx, s2v_lane& lane)
+{
+    if (!lane.busy) return S2V_OK;
+    lane.busy = false;
+    const int rc = s2v_stream_status(ctx, lane.stream);
+    if (lane.bad_edge) return s2v_fail(ctx, S2V_ERR_BAD_CSR, "infer_edges: graph_ptr not monotone or an edge endpoint outside [0, N)");
+    if (lane.bad_tag) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_edges: a node tag outside [0, num_feat)");
+    if (rc != S2V_OK) return rc;
+    const int64_t G = lane.G;
+    if (G > 0) {
+        const float* p_logits = static_cast<const float*>(lane.staging.pinned);
+        const int32_t* p_pred = reinterpret_cast<const int32_t*>(static_cast<const unsigned char*>(lane.staging.pinned) +
+                                                                 align_up(sizeof(float) * (size_t)G * lane.C, 256));
+        if (lane.logits_host) std::memcpy(lane.logits_host, p_logits, sizeof(float) * (size_t)G * lane.C);
+        if (lane.pred_host) std::memcpy(lane.pred_host, p_pred, sizeof(int32_t) * (size_t)G);
+    }
+    return S2V_OK;
+}
+
+static int lane_of(s2v_ctx* ctx, int index, s2v_lane** out)
+{
+    if (index < 0 || index > 1) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer: the lane is 0 or 1");
+    s2v_lane& lane = ctx->lanes[index];
+    if (!lane.stream) {
+        if (index == 0) lane.stream = ctx->stream;
+        else S2V_CUDA_OK(ctx, cudaStreamCreateWithFlags(&lane.stream, cudaStreamNonBlocking));
+    }
+    *out = &lane;
+    return S2V_OK;
+}
+
+int s2v_infer_edges_host_f32(s2v_ctx* ctx, const s2v_model* model, int64_t num_graphs, int64_t num_nodes, int64_t num_edges,
+                             const int32_t* edge_src_host, const int32_t* edge_dst_host, const int32_t* graph_ptr_host,
+                             const int32_t* tags_host, float* logits_host, int32_t* pred_host)
+{
+    S2V_ENTER(ctx);
+    s2v_lane* lane = nullptr;
+    int rc = lane_of(ctx, 0, &lane);
+    if (rc != S2V_OK) return rc;
+    if (lane->busy) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_edges: lane 0 holds a submitted batch; wait for it first");
+    rc = edges_enqueue(ctx, *lane, model, num_graphs, num_nodes, num_edges, edge_src_host, edge_dst_host, graph_ptr_host, tags_host,
+                       logits_host, pred_host);
+    const int rc2 = lane_finish(ctx, *lane);   // also drains the stream after a failed enqueue
+    return rc != S2V_OK ? rc : rc2;
+}
+
+int s2v_infer_edges_host_submit(s2v_ctx* ctx, int lane_index, const s2v_model* model, int64_t num_graphs, int64_t num_nodes,
+                                int64_t num_edges, const int32_t* edge_src_host, const int32_t* edge_dst_host,
+                                const int32_t* graph_ptr_host, const int32_t* tags_host, float* logits_host, int32_t* pred_host)
+{
+    S2V_ENTER(ctx);
+    s2v_lane* lane = nullptr;
+    int rc = lane_of(ctx, lane_index, &lane);
+    if (rc != S2V_OK) return rc;
+    if (lane->busy) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "infer_edges_submit: the lane holds a submitted batch; wait for it first");
+    rc = edges_enqueue(ctx, *lane, model, num_graphs, num_nodes, num_edges, edge_src_host, edge_dst_host, graph_ptr_host, tags_host,
+                       logits_host, pred_host);
+    if (rc != S2V_OK) lane_finish(ctx, *lane);   // drain what was enqueued; the enqueue error is the one reported
+    return rc;
+}
+
+int s2v_infer_host_wait(s2v_ctx* ctx, int lane_index)
+{
+    S2V_ENTER(ctx);
+    s2v_lane* lane = nullptr;
+    const int rc = lane_of(ctx, lane_index, &lane);
+    if (rc != S2V_OK) return rc;
+    return lane_finish(ctx, *lane);
 }
 
 }  // extern "C"

@@ -26,6 +26,19 @@ struct s2v_staging {  // grow-only buffers owned by a context (host-buffer entry
     size_t pinned_bytes = 0;
 };
 
+// One of the two lanes of the host-buffer entry points: its own stream and staging, and what a finished batch
+// still has to deliver.  Lane 0 is the context's own stream and serves the synchronous entry points.
+struct s2v_lane {
+    cudaStream_t stream = nullptr;
+    s2v_staging staging;
+    bool busy = false;
+    int64_t G = 0;
+    int C = 0;
+    float* logits_host = nullptr;
+    int32_t* pred_host = nullptr;
+    int bad_edge = 0, bad_tag = 0;   // outcome of the host scan that ran beside the device work
+};
+
 struct s2v_ctx {
     int device = 0;
     int sm_count = 0;      // SMs the persistent kernels size their grids for (hardware count minus S2V_OPT_RESERVED_SMS)
@@ -37,7 +50,7 @@ struct s2v_ctx {
     std::atomic<uint64_t> launches{0};
     std::string last_error;
     std::mutex mu;
-    s2v_staging staging;
+    s2v_lane lanes[2];
     int tc_mode = 1;  // tcgen05 level kernel: 0 never, 1 when the batch is large enough, 2 whenever the shape allows
     int graph_tiles = 2;    // whole-classifier tile kernel for batches of small graphs: 0 off, 1 whenever the batch allows, 2 automatic
     int validate_host = 1;  // s2v_infer_host_f32 scans its host arrays before launching

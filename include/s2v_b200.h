@@ -337,6 +337,21 @@ int s2v_infer_edges_host_f32(s2v_ctx* ctx, const s2v_model* model, int64_t num_g
                              const int32_t* edge_src_host, const int32_t* edge_dst_host, const int32_t* graph_ptr_host,
                              const int32_t* tags_host, float* logits_host, int32_t* pred_host);
 
+/* Two batches in flight (no counterpart in the reference, whose FeedForward is synchronous).  A context has two
+ * lanes, 0 and 1, each with its own stream and staging memory.  s2v_infer_edges_host_submit puts one batch on a
+ * lane -- upload, CSR build, forward, download, all asynchronous -- and returns after scanning the host arrays
+ * (which it does while the device already works); s2v_infer_host_wait blocks until that lane's batch is done,
+ * reports what the scan or a kernel found, and only then writes logits_host / pred_host.  A serving loop that
+ * submits batch i+1 on the other lane before it waits for batch i overlaps the PCIe transfers of one batch with
+ * the kernels of the other.  The caller's arrays (inputs and outputs) must stay valid and untouched from submit to
+ * wait; pinned input arrays keep the submit asynchronous.  Submitting to a lane that still holds a batch, or
+ * calling a synchronous host entry point (they use lane 0) while lane 0 holds one, returns S2V_ERR_INVALID_ARG;
+ * waiting on an idle lane returns S2V_OK. */
+int s2v_infer_edges_host_submit(s2v_ctx* ctx, int lane, const s2v_model* model, int64_t num_graphs, int64_t num_nodes,
+                                int64_t num_edges, const int32_t* edge_src_host, const int32_t* edge_dst_host,
+                                const int32_t* graph_ptr_host, const int32_t* tags_host, float* logits_host, int32_t* pred_host);
+int s2v_infer_host_wait(s2v_ctx* ctx, int lane);
+
 /* ---- several GPUs (no counterpart in the reference, which drives one GPU: src/tensor/gpu_handle.cu:17-44).
  * The path needs two exchanges and no reduction: the final gather of the logits when a batch is sharded by
  * graph, and one exchange of embedding rows per level when a single giant graph is partitioned by rows (all

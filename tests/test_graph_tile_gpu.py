@@ -283,3 +283,55 @@ def test_edge_list_host_entry_matches_csr_host_entry(oracle_lib):
             assert np.array_equal(l2, logits) and np.array_equal(p2, pred)
         o = oracle_lib.forward(b, "oracle", want_levels=False)
         assert_close(l2, o["logits"], "edge-list entry vs oracle", scale=max(1.0, float(np.abs(o["logits"]).max())))
+
+
+def test_two_batches_in_flight_give_the_synchronous_results():
+    """s2v_infer_edges_host_submit / s2v_infer_host_wait: six different batches through the two lanes, the next one
+    submitted before the previous one is waited for; every result equals the synchronous entry point's, results
+    appear only at the wait, and misuse of a lane is an argument error, not a fault."""
+    batches = [synth.molecules_16k(seed=40 + i, num_graphs=300 + 150 * i) for i in range(6)]
+    eng = engine.S2VInference(batches[0].weights, batches[0].levels)
+    ctx = eng.ctx
+    jobs = []
+    for b in batches:
+        hb = engine.build_host_batch(b)
+        es = torch.from_numpy(np.ascontiguousarray(b.edge_src, np.int32)).pin_memory()
+        ed = torch.from_numpy(np.ascontiguousarray(b.edge_dst, np.int32)).pin_memory()
+        gp, tg = hb.graph_ptr.pin_memory(), hb.tags.pin_memory()
+        want_l, want_p = np.empty((b.num_graphs, b.num_class), np.float32), np.empty(b.num_graphs, np.int32)
+        ctx.infer_edges_host(eng.model, b.num_graphs, b.num_nodes, es.numpy(), ed.numpy(), gp.numpy(), tg.numpy(), want_l, want_p)
+        jobs.append((b, es, ed, gp, tg, want_l, want_p, np.full_like(want_l, np.nan), np.full_like(want_p, -7)))
+
+    def submit(i):
+        b, es, ed, gp, tg, _, _, got_l, got_p = jobs[i]
+        ctx.infer_edges_host_submit(i % 2, eng.model, b.num_graphs, b.num_nodes, es.numpy(), ed.numpy(), gp.numpy(), tg.numpy(), got_l, got_p)
+
+    submit(0)
+    for i in range(len(jobs)):
+        if i + 1 < len(jobs):
+            submit(i + 1)                              # the other lane, before waiting for this one
+        assert np.isnan(jobs[i][7]).all()              # nothing is delivered before the wait
+        ctx.infer_host_wait(i % 2)
+        assert np.array_equal(jobs[i][7], jobs[i][5]) and np.array_equal(jobs[i][8], jobs[i][6])
+    ctx.infer_host_wait(0)                             # idle lane: nothing to do
+    # misuse
+    submit(0)
+    with pytest.raises(capi.S2VError) as e:
+        submit(0)                                      # lane 0 still holds a batch
+    assert e.value.status == -1
+    with pytest.raises(capi.S2VError):
+        eng.infer_host(engine.build_host_batch(batches[0]))   # the synchronous entries use lane 0
+    ctx.infer_host_wait(0)
+    with pytest.raises(capi.S2VError):
+        ctx.infer_host_wait(2)
+    # a bad tag in a submitted batch is reported at the wait, and the lane is free again afterwards
+    b, es, ed, gp, tg, want_l, want_p, got_l, got_p = jobs[1]
+    bad = tg.clone()
+    bad[3] = b.num_tags
+    ctx.infer_edges_host_submit(1, eng.model, b.num_graphs, b.num_nodes, es.numpy(), ed.numpy(), gp.numpy(), bad.numpy(), got_l, got_p)
+    with pytest.raises(capi.S2VError) as e:
+        ctx.infer_host_wait(1)
+    assert e.value.status == -1 and "tag outside" in str(e.value)
+    ctx.infer_edges_host_submit(1, eng.model, b.num_graphs, b.num_nodes, es.numpy(), ed.numpy(), gp.numpy(), tg.numpy(), got_l, got_p)
+    ctx.infer_host_wait(1)
+    assert np.array_equal(got_l, want_l) and np.array_equal(got_p, want_p)
