@@ -274,7 +274,7 @@ class ClassifierStep:
         else:
             self.ha = torch.empty((N, d), device=dev)
             self.hbuf = torch.empty((N, d), device=dev)
-            self.first_fused = d in (64, 128) and N >= 16384
+            self.first_fused = d in (4, 8, 16, 32, 64, 128)      # the library runs level 1 from the tags for these widths
         self.events = []      # (kind, start, end) of the launches bracketed by profile()
 
     def __call__(self, timed: bool = False):
@@ -294,6 +294,8 @@ class ClassifierStep:
     def profile(self, iters: int = 10):
         """The kernels of a step, launch by launch, each between two CUDA events."""
         ctx, db, w, st, L = self.ctx, self.db, self.eng.w, self.stream.cuda_stream, self.b.levels
+        if not self.tiles and self.first_fused:   # untimed first call: the entry point allocates its product table once
+            ctx.level_first(db.row_ptr, db.col_idx, None, w["p_node_conv"], w["w_n2l"], db.tags, self.hbuf, stream=st)
         for _ in range(iters):
             if self.tiles:
                 self._timed("tiles", lambda: ctx.graph_tiles(L, db.row_ptr, db.col_idx, None, db.graph_ptr, db.tags, w["w_n2l"],
@@ -577,7 +579,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             if "level_first" in kms:
                 f_ms, f_n = kms["level_first"]
                 fb = level_bytes(N, E, d, "compulsory", "lookup", h_form="table")
-                line["roofline_first_level"] = {"kernel": "first level straight from the tags (no H0 in memory)", "bound": "hbm",
+                line["roofline_first_level"] = {"kernel": "first level from the tags: product table ReLU(W_in)*W (tiny launch) + gather-sum over its rows, no per-row product", "bound": "hbm",
                                                 "achieved": fb / (f_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                                 "frac": fb / (f_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "ms_per_launch": f_ms,
                                                 "launches": f_n, "bytes_per_launch": fb, "traffic": None}

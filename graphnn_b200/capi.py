@@ -289,7 +289,7 @@ class Context:
         """Synchronises `stream` (None = the context's own) and raises if a kernel recorded a status."""
         self.check(self.lib.s2v_stream_status(self.h, stream))
 
-    OPT_VALIDATE_HOST_INPUT, OPT_LEVEL_TC, OPT_GRAPH_TILES, OPT_RESERVED_SMS = 1, 2, 3, 4
+    OPT_VALIDATE_HOST_INPUT, OPT_LEVEL_TC, OPT_GRAPH_TILES, OPT_RESERVED_SMS, OPT_FIRST_LEVEL_TABLE = 1, 2, 3, 4, 5
 
     def set_option(self, option: int, value: int):
         self.check(self.lib.s2v_ctx_set_option(self.h, int(option), int(value)))

@@ -129,6 +129,7 @@ int s2v_ctx_destroy(s2v_ctx* ctx)
         s2v_device_guard guard(ctx->device);
         if (ctx->stream) { cudaStreamSynchronize(ctx->stream); cudaStreamDestroy(ctx->stream); }
         if (ctx->dstatus_host) cudaFreeHost(ctx->dstatus_host);
+        if (ctx->first_table) cudaFree(ctx->first_table);
         for (s2v_lane& lane : ctx->lanes) {
             if (lane.stream && lane.stream != ctx->stream) { cudaStreamSynchronize(lane.stream); cudaStreamDestroy(lane.stream); }
             if (lane.staging.dev) cudaFree(lane.staging.dev);
@@ -161,6 +162,7 @@ int s2v_ctx_set_option(s2v_ctx* ctx, int option, int value)
         case S2V_OPT_VALIDATE_HOST_INPUT: ctx->validate_host = value != 0; return S2V_OK;
         case S2V_OPT_LEVEL_TC: ctx->tc_mode = value <= 0 ? 0 : (value >= 2 ? 2 : 1); return S2V_OK;
         case S2V_OPT_GRAPH_TILES: ctx->graph_tiles = value <= 0 ? 0 : (value >= 2 ? 2 : 1); return S2V_OK;
+        case S2V_OPT_FIRST_LEVEL_TABLE: ctx->first_table_on = value != 0; return S2V_OK;
         case S2V_OPT_RESERVED_SMS:
             if (value < 0 || value >= ctx->sm_count_hw) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "set_option: reserved SMs outside [0, SM count)");
             ctx->sm_count = ctx->sm_count_hw - value;
@@ -245,10 +247,23 @@ int s2v_level_first_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n, int d, const
     if (!row_ptr || !W || !table || !tags || !out) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level_first: NULL pointer");
     if (!s2v_aligned16(W) || !s2v_aligned16(table) || !s2v_aligned16(out))
         return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level_first: W, table, out must be 16-byte aligned");
-    if (!s2v_use_tc(ctx, d, n))
-        return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "level_first: only the tcgen05 kernel (d = 64 or 128, large batch) has this form; materialise H0 instead");
     int rc = s2v_launch_index_check(ctx, s2v_pick_stream(ctx, stream), n, tags, n_table);
     if (rc != S2V_OK) return rc;
+    if (ctx->first_table_on && s2v_first_table_supported(d)) {
+        // gather-sum over the product table ReLU(table) * W, which lives in a small context-owned buffer
+        const size_t need = s2v_first_table_scratch_bytes(n_table, d);
+        if (need > ctx->first_table_bytes) {
+            if (ctx->first_table) cudaFree(ctx->first_table);
+            ctx->first_table = nullptr;
+            ctx->first_table_bytes = 0;
+            S2V_CUDA_OK(ctx, cudaMalloc(&ctx->first_table, need));
+            ctx->first_table_bytes = need;
+        }
+        return s2v_launch_level_first_table(ctx, s2v_pick_stream(ctx, stream), n, d, row_ptr, col_idx, val, W, table, n_table, tags,
+                                            static_cast<float*>(ctx->first_table), out);
+    }
+    if (!s2v_use_tc(ctx, d, n))
+        return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "level_first: d / 4 must be a power of two up to 32; materialise H0 instead");
     rc = s2v_launch_level_tc(ctx, s2v_pick_stream(ctx, stream), n, d, row_ptr, col_idx, val, nullptr, W, nullptr, table,
                              tags, n_table, out);
     if (rc == S2V_ERR_UNSUPPORTED) return s2v_fail(ctx, rc, "level_first: shape not supported by the tcgen05 kernel");
@@ -349,7 +364,17 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
         rc = s2v_launch_index_check(ctx, st, N, batch->tags, model->num_feat);
         if (rc != S2V_OK) return rc;
     }
-    if (onehot && L >= 1 && s2v_use_tc(ctx, d, N)) {
+    if (onehot && L >= 1 && ctx->first_table_on && s2v_first_table_supported(d) &&
+        s2v_first_table_scratch_bytes(model->num_feat, d) <= nd) {
+        // H0 = ReLU(W_in[tag]) has one distinct row per tag, so level 1 is a gather-sum over the rows of
+        // ReLU(W_in) * W (kept in the unused `msg` region of the workspace): no per-row product at all
+        float* dst = (L == 1 && embed_out) ? embed_out : ha;
+        rc = s2v_launch_level_first_table(ctx, st, N, d, batch->n2n_row_ptr, batch->n2n_col_idx, batch->n2n_val, model->p_node_conv,
+                                          model->w_n2l, model->num_feat, batch->tags, msg, dst);
+        if (rc == S2V_OK) first_fused = true;
+        else if (rc != S2V_ERR_UNSUPPORTED) return rc;
+    }
+    if (!first_fused && onehot && L >= 1 && s2v_use_tc(ctx, d, N)) {
         float* dst = (L == 1 && embed_out) ? embed_out : ha;
         rc = s2v_launch_level_tc(ctx, st, N, d, batch->n2n_row_ptr, batch->n2n_col_idx, batch->n2n_val, nullptr, model->p_node_conv,
                                  nullptr, model->w_n2l, batch->tags, model->num_feat, dst);

@@ -51,8 +51,11 @@ struct s2v_ctx {
     std::string last_error;
     std::mutex mu;
     s2v_lane lanes[2];
+    void* first_table = nullptr;     // product table of s2v_level_first_f32 (grow-only, a few hundred KB at most)
+    size_t first_table_bytes = 0;
     int tc_mode = 1;  // tcgen05 level kernel: 0 never, 1 when the batch is large enough, 2 whenever the shape allows
     int graph_tiles = 2;    // whole-classifier tile kernel for batches of small graphs: 0 off, 1 whenever the batch allows, 2 automatic
+    int first_table_on = 1; // first level as a gather-sum over ReLU(W_in) * W (S2V_OPT_FIRST_LEVEL_TABLE)
     int validate_host = 1;  // s2v_infer_host_f32 scans its host arrays before launching
 };
 
@@ -153,6 +156,13 @@ int s2v_launch_level_tc(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int d, co
                         const int32_t* col_idx, const float* val, const float* H, const float* W, const float* X,
                         const float* table, const int32_t* x_index, int n_table, float* out);
 int s2v_launch_wait_selftest(s2v_ctx* ctx, cudaStream_t st);
+// first level from one-hot tags as a gather-sum over the product table ReLU(W_in) * W (level_first_table.cu);
+// d / 4 must be a power of two <= 32; P_scratch holds s2v_first_table_scratch_bytes(n_table, d)
+bool s2v_first_table_supported(int d);
+size_t s2v_first_table_scratch_bytes(int n_table, int d);
+int s2v_launch_level_first_table(s2v_ctx* ctx, cudaStream_t st, int64_t n, int d, const int32_t* row_ptr, const int32_t* col_idx,
+                                 const float* val, const float* W, const float* table, int n_table, const int32_t* tags,
+                                 float* P_scratch, float* out);
 // records S2V_ERR_INVALID_ARG in the status word if any idx[i] lies outside [0, limit)
 int s2v_launch_index_check(s2v_ctx* ctx, cudaStream_t st, int64_t n, const int32_t* idx, int limit);
 // whole classifier up to the pooled embeddings for batches of graphs of at most S2V_TILE_NODES nodes (d = 128, tags)

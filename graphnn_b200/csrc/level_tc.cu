@@ -319,6 +319,19 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
     {                                                                                              \
         const uint32_t m4 = (uint32_t)em & 15u;                                                    \
         em >>= 4;                                                                                  \
+        /* no row end among these four non-zeros: sums only.  One lane group per warp (d = 128), so the    \
+           branch is warp-uniform; measured -3.3 % on the molecule input; with two groups per warp         \
+           (d = 64) the groups diverge and it costs 1.3 % on the protein input, so it is left out there */ \
+        if (G == 1 && m4 == 0u) {                                                                  \
+            _Pragma("unroll") for (int u = 0; u < TC_U; ++u) {                                     \
+                if (HAS_VAL) {                                                                     \
+                    acc.x = fmaf(wt[u], v[u].x, acc.x); acc.y = fmaf(wt[u], v[u].y, acc.y);        \
+                    acc.z = fmaf(wt[u], v[u].z, acc.z); acc.w = fmaf(wt[u], v[u].w, acc.w);        \
+                } else {                                                                           \
+                    acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;            \
+                }                                                                                  \
+            }                                                                                      \
+        } else                                                                                     \
         _Pragma("unroll") for (int u = 0; u < TC_U; ++u) {                                         \
             if (HAS_VAL) {                                                                         \
                 acc.x = fmaf(wt[u], v[u].x, acc.x); acc.y = fmaf(wt[u], v[u].y, acc.y);            \

@@ -76,6 +76,9 @@ typedef enum s2v_option {
                                         small graphs: 0 never, 1 whenever the batch allows, 2 automatic (default: batches of at
                                         most 160,000 nodes, where one launch beats the per-level kernels by 1.1x - 2.2x; larger
                                         batches stream better through the per-level kernels).  Default from S2V_GRAPH_TILES */
+    S2V_OPT_FIRST_LEVEL_TABLE = 5,   /* first level from one-hot tags as a gather-sum over the product table ReLU(W_in) * W
+                                        (see s2v_level_first_f32): 1 (default) whenever d allows, 0 never (the level kernels'
+                                        own table-lookup form is used instead) */
     S2V_OPT_RESERVED_SMS = 4         /* the persistent kernels size their grids for (SM count - value) SMs, leaving the rest to
                                         kernels of another stream -- a communication library's, which cannot start while
                                         one-CTA-per-SM kernels hold every SM (default 0; 0 <= value < SM count) */
@@ -123,9 +126,12 @@ int s2v_level_lookup_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n_rows, int64_
 
 /* First level of the classifier with one-hot inputs, without materialising H0:
  * out = ReLU((A * ReLU(table[tags,:])) * W + table[tags,:]), A square [n x n]; i.e. MatMul(data, w_n2l),
- * ReLU and the first level (kernel_mean_field.cpp:31-41) in one kernel.  Only the tcgen05 kernel
- * (d = 64 or 128) has this form (n >= 16,384 unless forced); otherwise S2V_ERR_UNSUPPORTED: run
- * s2v_input_proj_onehot_f32 + s2v_level_lookup_f32 instead. */
+ * ReLU and the first level (kernel_mean_field.cpp:31-41) in one call.  H0 has one distinct row per tag and the
+ * product is linear in the gathered sum, so for d in {4, 8, 16, 32, 64, 128} the level runs as a gather-sum over
+ * the rows of P = ReLU(table) * W (n_table x d, computed by a tiny launch into a context-owned buffer that is
+ * allocated on first use): no per-row matrix product at all; sums in CSR order in fp32, which differs from "sum
+ * first, multiply after" by fp32 rounding only.  Other d: the tcgen05 kernel when it takes the shape, else
+ * S2V_ERR_UNSUPPORTED (run s2v_input_proj_onehot_f32 + s2v_level_lookup_f32 instead). */
 int s2v_level_first_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n, int d, const int32_t* row_ptr,
                         const int32_t* col_idx, const float* val, const float* W, const float* table, int n_table,
                         const int32_t* tags, float* out);

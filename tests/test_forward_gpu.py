@@ -54,7 +54,9 @@ def test_classifier_matches_oracle(oracle_lib, maker):
     _, hb, logits, probs, pred, embed = run(b)
     assert np.array_equal(hb.row_ptr.numpy(), o["n2n_row_ptr"])
     assert np.array_equal(hb.col_idx.numpy(), o["n2n_col_idx"])
-    assert_close(embed, o["levels"][-1], "embeddings")
+    # the last level's values reach tens (proteins: 43): like the logits they are held to 1e-5 of their scale; fp32
+    # arithmetic in any order is itself 9e-6 away from the float64 restatement on the largest of these batches
+    assert_close(embed, o["levels"][-1], "embeddings", scale=max(1.0, float(np.abs(o["levels"][-1]).max())))
     assert_close(logits, o["logits"], "logits", scale=max(1.0, float(np.abs(o["logits"]).max())))
     assert_close(probs, o["probs"], "probs")
     margin = np.sort(o["logits"], axis=1)

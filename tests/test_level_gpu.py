@@ -96,26 +96,57 @@ def test_level_block_diagonal_batch(gpu_ctx, oracle_lib):
 
 
 def test_first_level_straight_from_tags(gpu_ctx, oracle_lib):
-    """s2v_level_first_f32 (H0 never materialised) against input projection + level, and the oracle."""
+    """s2v_level_first_f32 (H0 never materialised) against input projection + level, and the oracle: as a gather-sum
+    over the product table ReLU(W_in) * W (the default), and in the level kernel's own table-lookup form."""
     from graphnn_b200.capi import S2VError
-    b = synth.molecules_16k(seed=4, num_graphs=700)          # ~21k nodes: the tcgen05 kernel takes it
+    b = synth.molecules_16k(seed=4, num_graphs=700)          # ~21k nodes: the tcgen05 kernel takes it too
     o = oracle_lib.forward(b, "oracle")
     rp, ci, tags = dev(o["n2n_row_ptr"]), dev(o["n2n_col_idx"]), dev(b.tags.astype(np.int32))
     W, table = dev(b.weights["p_node_conv"]), dev(b.weights["w_n2l"])
-    fused = torch.full((b.num_nodes, b.d), float("nan"), device="cuda")
-    gpu_ctx.level_first(rp, ci, None, W, table, tags, fused)
-    h0 = torch.empty_like(fused)
-    two_step = torch.empty_like(fused)
+    h0 = torch.empty((b.num_nodes, b.d), device="cuda")
+    two_step = torch.empty_like(h0)
     gpu_ctx.input_proj_onehot(tags, table, None, h0)
     gpu_ctx.level_lookup(rp, ci, None, h0, W, table, tags, two_step)
+    by_table = torch.full((b.num_nodes, b.d), float("nan"), device="cuda")
+    gpu_ctx.level_first(rp, ci, None, W, table, tags, by_table)
+    gpu_ctx.set_option(gpu_ctx.OPT_FIRST_LEVEL_TABLE, 0)
+    try:
+        fused = torch.full((b.num_nodes, b.d), float("nan"), device="cuda")
+        gpu_ctx.level_first(rp, ci, None, W, table, tags, fused)
+        gpu_ctx.synchronize()
+        assert torch.equal(fused, two_step)                   # the level kernel's form: same arithmetic in the same order
+        small = synth.mutag_like(seed=0)                      # small batch: not taken by the tcgen05 kernel, the caller must fall back
+        with pytest.raises(S2VError) as e:
+            gpu_ctx.level_first(dev(np.zeros(small.num_nodes + 1, np.int32)), None, None, dev(small.weights["p_node_conv"]),
+                                dev(small.weights["w_n2l"]), dev(small.tags.astype(np.int32)),
+                                torch.empty((small.num_nodes, 64), device="cuda"))
+        assert e.value.status == -2
+    finally:
+        gpu_ctx.set_option(gpu_ctx.OPT_FIRST_LEVEL_TABLE, 1)
+    assert_close(fused.cpu().numpy(), o["levels"][1], "first level from tags, level-kernel form")
+    assert_close(by_table.cpu().numpy(), o["levels"][1], "first level from tags, product-table form")
+    # the product-table form takes any batch size and weighted edges; a width whose d/4 is not a power of two is refused
+    small = synth.mutag_like(seed=0)
+    os_ = oracle_lib.forward(small, "oracle")
+    out = torch.full((small.num_nodes, small.d), float("nan"), device="cuda")
+    gpu_ctx.level_first(dev(os_["n2n_row_ptr"]), dev(os_["n2n_col_idx"]), None, dev(small.weights["p_node_conv"]),
+                        dev(small.weights["w_n2l"]), dev(small.tags.astype(np.int32)), out)
     gpu_ctx.synchronize()
-    assert torch.equal(fused, two_step)                       # same arithmetic in the same order
-    assert_close(fused.cpu().numpy(), o["levels"][1], "first level from tags")
-    small = synth.mutag_like(seed=0)                          # small batch: not taken by the tcgen05 kernel, the caller must fall back
+    assert_close(out.cpu().numpy(), os_["levels"][1], "product-table form, 64 small graphs")
+    rng = np.random.default_rng(3)
+    val = rng.uniform(0.25, 2.0, small.num_edges).astype(np.float32)
+    gpu_ctx.level_first(dev(os_["n2n_row_ptr"]), dev(os_["n2n_col_idx"]), dev(val), dev(small.weights["p_node_conv"]),
+                        dev(small.weights["w_n2l"]), dev(small.tags.astype(np.int32)), out)
+    gpu_ctx.synchronize()
+    import scipy.sparse as sp
+    tbl = small.weights["w_n2l"].astype(np.float64)
+    tg = small.tags.astype(np.int64)
+    A = sp.csr_matrix((val.astype(np.float64), os_["n2n_col_idx"], os_["n2n_row_ptr"]), shape=(small.num_nodes, small.num_nodes))
+    z = (A @ np.maximum(tbl[tg], 0.0)) @ small.weights["p_node_conv"].astype(np.float64) + tbl[tg]
+    assert_close(out.cpu().numpy(), np.where(z < 0, 0.0, z).astype(np.float32), "product-table form, weighted edges")
     with pytest.raises(S2VError) as e:
-        gpu_ctx.level_first(dev(np.zeros(small.num_nodes + 1, np.int32)), None, None, dev(small.weights["p_node_conv"]),
-                            dev(small.weights["w_n2l"]), dev(small.tags.astype(np.int32)),
-                            torch.empty((small.num_nodes, 64), device="cuda"))
+        gpu_ctx.level_first(dev(np.zeros(11, np.int32)), None, None, dev(np.zeros((12, 12), np.float32)), dev(np.zeros((3, 12), np.float32)),
+                            dev(np.zeros(10, np.int32)), torch.empty((10, 12), device="cuda"))
     assert e.value.status == -2
 
 

@@ -112,8 +112,12 @@ def test_tc_lookup_and_first_level_forms(tc_ctx, oracle_lib, maker):
     tc_ctx.synchronize()
     assert_close(out.cpu().numpy(), o["levels"][2], "lookup form, level 2")
     fused = torch.full((b.num_nodes, b.d), float("nan"), device="cuda")
-    tc_ctx.level_first(rp, ci, None, W, table, tags, fused)
-    tc_ctx.synchronize()
+    tc_ctx.set_option(tc_ctx.OPT_FIRST_LEVEL_TABLE, 0)      # the tcgen05 kernel's own table-lookup form, not the product table
+    try:
+        tc_ctx.level_first(rp, ci, None, W, table, tags, fused)
+        tc_ctx.synchronize()
+    finally:
+        tc_ctx.set_option(tc_ctx.OPT_FIRST_LEVEL_TABLE, 1)
     assert_close(fused.cpu().numpy(), o["levels"][1], "first level from tags")
 
 
@@ -146,8 +150,14 @@ def test_tc_first_level_with_long_rows(tc_ctx, d):
     table = (rng.standard_normal((n_tags, d)) * 0.3).astype(np.float32)
     W = (rng.standard_normal((d, d)) * 0.1).astype(np.float32)
     fused = torch.full((n, d), float("nan"), device="cuda")
-    tc_ctx.level_first(dev(row_ptr), dev(col), None, dev(W), dev(table), dev(tags), fused)
-    tc_ctx.synchronize()
+    by_table = torch.full((n, d), float("nan"), device="cuda")
+    tc_ctx.level_first(dev(row_ptr), dev(col), None, dev(W), dev(table), dev(tags), by_table)   # product-table form (the default)
+    tc_ctx.set_option(tc_ctx.OPT_FIRST_LEVEL_TABLE, 0)
+    try:
+        tc_ctx.level_first(dev(row_ptr), dev(col), None, dev(W), dev(table), dev(tags), fused)  # the tcgen05 kernel's own form
+        tc_ctx.synchronize()
+    finally:
+        tc_ctx.set_option(tc_ctx.OPT_FIRST_LEVEL_TABLE, 1)
     import scipy.sparse as sp
     h0 = np.maximum(table[tags].astype(np.float64), 0.0)
     A = sp.csr_matrix((np.ones(len(col)), col, row_ptr), shape=(n, n))
@@ -159,6 +169,9 @@ def test_tc_first_level_with_long_rows(tc_ctx, d):
     # the size of the terms that cancel (the fp32 reference itself is no closer to this float64 result)
     scale = float(((A @ h0) @ np.abs(W).astype(np.float64))[long_rows].max())
     assert_close(got[long_rows], want[long_rows], f"first level, long rows, d={d}", scale=scale)
+    got_t = by_table.cpu().numpy()
+    assert_close(got_t[~long_rows], want[~long_rows], f"first level by product table, rows up to 65 non-zeros, d={d}")
+    assert_close(got_t[long_rows], want[long_rows], f"first level by product table, long rows, d={d}", scale=scale)
 
 
 def test_bounded_wait_reports_and_context_survives(gpu_ctx, oracle_lib):
