@@ -41,8 +41,8 @@ __global__ void __launch_bounds__(256) first_table_product_kernel(int d, const f
 constexpr int FT_CAP = 256;
 constexpr int FT_WARPS = 8;
 
-template <bool HAS_VAL>
-__global__ void __launch_bounds__(FT_WARPS * 32) first_level_table_kernel(int64_t n, int lpr, const int32_t* __restrict__ row_ptr,
+template <bool HAS_VAL, int LPR_T>   // LPR_T: d/4 fixed at compile time (32, 16, 8), or 0 = read it from the argument
+__global__ void __launch_bounds__(FT_WARPS * 32) first_level_table_kernel(int64_t n, int lpr_arg, const int32_t* __restrict__ row_ptr,
                                                                          const int32_t* __restrict__ col_idx, const float* __restrict__ val,
                                                                          const int32_t* __restrict__ tags, int n_table,
                                                                          const float4* __restrict__ P, const float4* __restrict__ table,
@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(FT_WARPS * 32) first_level_table_kernel(int64_
 {
     __shared__ int s_tag[FT_WARPS][FT_CAP];
     __shared__ float s_val[HAS_VAL ? FT_WARPS : 1][HAS_VAL ? FT_CAP : 1];
+    const int lpr = LPR_T ? LPR_T : lpr_arg;
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const int rows_per_warp = 32 / lpr;
     const int sub = lane / lpr, sl = lane - sub * lpr;
@@ -120,13 +121,13 @@ __global__ void __launch_bounds__(FT_WARPS * 32) first_level_table_kernel(int64_
                 const int b = __shfl_sync(FULL, rp_lo, rs) - start, e = __shfl_sync(FULL, rp_hi, rs) - start;
                 const unsigned tg_row = __shfl_sync(FULL, row_tag, rs);
                 if (have) {
-                    const float4 x = __ldg(table + (int64_t)tg_row * lpr + sl);
+                    const float4 x = __ldg(table + ((int)tg_row * lpr + sl));
                     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
                     int t = b;
                     for (; t + 4 <= e; t += 4) {
                         float4 p[4];
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) p[u] = __ldg(P + (int64_t)my_tags[t + u] * lpr + sl);
+                        for (int u = 0; u < 4; ++u) p[u] = __ldg(P + (my_tags[t + u] * lpr + sl));
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
                             if (HAS_VAL) {
@@ -139,7 +140,7 @@ __global__ void __launch_bounds__(FT_WARPS * 32) first_level_table_kernel(int64_
                         }
                     }
                     for (; t < e; ++t) {
-                        const float4 p = __ldg(P + (int64_t)my_tags[t] * lpr + sl);
+                        const float4 p = __ldg(P + (my_tags[t] * lpr + sl));
                         if (HAS_VAL) {
                             const float w = my_vals[t];
                             acc.x = fmaf(w, p.x, acc.x); acc.y = fmaf(w, p.y, acc.y); acc.z = fmaf(w, p.z, acc.z); acc.w = fmaf(w, p.w, acc.w);
@@ -188,10 +189,13 @@ int s2v_launch_level_first_table(s2v_ctx* ctx, cudaStream_t st, int64_t n, int d
     const float4* P4 = reinterpret_cast<const float4*>(P_scratch);
     const float4* T4 = reinterpret_cast<const float4*>(table);
     float4* O4 = reinterpret_cast<float4*>(out);
-    if (val)
-        first_level_table_kernel<true><<<(unsigned)blocks, FT_WARPS * 32, 0, st>>>(n, lpr, row_ptr, col_idx, val, tags, n_table, P4, T4, O4);
-    else
-        first_level_table_kernel<false><<<(unsigned)blocks, FT_WARPS * 32, 0, st>>>(n, lpr, row_ptr, col_idx, nullptr, tags, n_table, P4, T4, O4);
+#define FT_LAUNCH(HV, L) first_level_table_kernel<HV, L><<<(unsigned)blocks, FT_WARPS * 32, 0, st>>>(n, lpr, row_ptr, col_idx, val, tags, n_table, P4, T4, O4)
+    if (val) {
+        if (lpr == 32) FT_LAUNCH(true, 32); else if (lpr == 16) FT_LAUNCH(true, 16); else if (lpr == 8) FT_LAUNCH(true, 8); else FT_LAUNCH(true, 0);
+    } else {
+        if (lpr == 32) FT_LAUNCH(false, 32); else if (lpr == 16) FT_LAUNCH(false, 16); else if (lpr == 8) FT_LAUNCH(false, 8); else FT_LAUNCH(false, 0);
+    }
+#undef FT_LAUNCH
     S2V_CHECK_LAUNCH(ctx, "first_level_table_kernel");
     return S2V_OK;
 }
