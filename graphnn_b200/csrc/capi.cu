@@ -292,8 +292,21 @@ int s2v_graph_tiles_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int
     if (!workspace || workspace_bytes < s2v_graph_tiles_workspace_bytes(num_graphs))
         return s2v_fail(ctx, S2V_ERR_WORKSPACE, "graph_tiles: workspace smaller than s2v_graph_tiles_workspace_bytes");
     void* plan = reinterpret_cast<void*>(align_up(reinterpret_cast<uintptr_t>(workspace), 256));
+    // the product table of the first level ((num_tags + 1) x d floats) lives in a small context-owned buffer
+    float* P = nullptr;
+    if (ctx->first_table_on) {
+        const size_t need = s2v_first_table_scratch_bytes(num_tags + 1, d);
+        if (need > ctx->first_table_bytes) {
+            if (ctx->first_table) cudaFree(ctx->first_table);
+            ctx->first_table = nullptr;
+            ctx->first_table_bytes = 0;
+            S2V_CUDA_OK(ctx, cudaMalloc(&ctx->first_table, need));
+            ctx->first_table_bytes = need;
+        }
+        P = static_cast<float*>(ctx->first_table);
+    }
     const int rc = s2v_launch_graph_tiles(ctx, s2v_pick_stream(ctx, stream), num_graphs, row_ptr, col_idx, val, graph_ptr, tags,
-                                          num_tags, W_in, W, levels, pool_average, plan, Y, embed_out);
+                                          num_tags, W_in, W, levels, pool_average, plan, P, Y, embed_out);
     if (rc == S2V_ERR_UNSUPPORTED) return s2v_fail(ctx, rc, "graph_tiles: this device cannot hold the kernel's shared memory");
     return rc;
 }
@@ -337,17 +350,19 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
     int rc;
     // Batches of small graphs (the caller vouches for the largest one): the whole classifier up to the pooled
     // embeddings is one kernel that keeps the node embeddings of a tile of whole graphs in shared memory.
-    // Measured on 20-40-node graphs, d = 128, 4 levels: one launch beats the per-level kernels by 2.2x at 16 k nodes,
-    // 1.2x at 62 k, 1.13x at 123 k, and loses 4 % at 491 k (the per-level kernels stream better once every SM has
-    // dozens of tiles), so the automatic mode takes it up to S2V_TILE_AUTO_MAX_NODES nodes.
+    // Measured on 20-40-node graphs, d = 128, 4 levels: one launch beats the per-level kernels by 2.0x at 16 k nodes,
+    // 1.11x at 62 k, 1.05x at 123 k, and loses 11 % at 246 k and 17 % at 491 k (the per-level kernels stream better
+    // once every SM has dozens of tiles), so the automatic mode takes it up to S2V_TILE_AUTO_MAX_NODES nodes.
     const bool want_tiles = ctx->graph_tiles == 1 || (ctx->graph_tiles == 2 && N <= S2V_TILE_AUTO_MAX_NODES);
     if (want_tiles && d == 128 && L >= 1 && batch->tags && batch->max_graph_nodes >= 1 &&
         batch->max_graph_nodes <= S2V_TILE_NODES && N > 0 && G < (int64_t)INT32_MAX) {
         if (!s2v_aligned16(model->w_n2l) || !s2v_aligned16(model->p_node_conv) || (embed_out && !s2v_aligned16(embed_out)))
             return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "forward: weights and embed_out must be 16-byte aligned");
+        // the first level's product table goes into the `msg` region of the workspace, which one-hot inputs leave unused
+        float* P = (ctx->first_table_on && s2v_first_table_scratch_bytes(model->num_feat + 1, d) <= nd) ? msg : nullptr;
         rc = s2v_launch_graph_tiles(ctx, st, G, batch->n2n_row_ptr, batch->n2n_col_idx, batch->n2n_val, batch->graph_ptr,
                                     batch->tags, model->num_feat, model->w_n2l, model->p_node_conv, L, model->pool_average,
-                                    plan, y, embed_out);
+                                    plan, P, y, embed_out);
         if (rc == S2V_OK)
             return s2v_readout_f32(ctx, st, G, d, model->hidden, model->num_class, y, model->h1_weight, model->h2_weight,
                                    logits, probs, pred);

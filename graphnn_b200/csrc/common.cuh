@@ -160,6 +160,8 @@ int s2v_launch_wait_selftest(s2v_ctx* ctx, cudaStream_t st);
 // d / 4 must be a power of two <= 32; P_scratch holds s2v_first_table_scratch_bytes(n_table, d)
 bool s2v_first_table_supported(int d);
 size_t s2v_first_table_scratch_bytes(int n_table, int d);
+int s2v_launch_first_table_product(s2v_ctx* ctx, cudaStream_t st, int n_table, int d, const float* table, const float* W,
+                                   float* P, bool extra_zero_row);
 int s2v_launch_level_first_table(s2v_ctx* ctx, cudaStream_t st, int64_t n, int d, const int32_t* row_ptr, const int32_t* col_idx,
                                  const float* val, const float* W, const float* table, int n_table, const int32_t* tags,
                                  float* P_scratch, float* out);
@@ -171,8 +173,8 @@ constexpr int64_t S2V_TILE_AUTO_MAX_NODES = 160000;   // automatic mode: batches
 size_t s2v_graph_tiles_plan_bytes(int64_t num_graphs);
 int s2v_launch_graph_tiles(s2v_ctx* ctx, cudaStream_t st, int64_t G, const int32_t* row_ptr, const int32_t* col_idx,
                            const float* val, const int32_t* graph_ptr, const int32_t* tags, int num_tags,
-                           const float* W_in, const float* W, int levels, int pool_average, void* plan, float* Y,
-                           float* embed_out);
+                           const float* W_in, const float* W, int levels, int pool_average, void* plan, float* P_scratch,
+                           float* Y, float* embed_out);   // P_scratch: (num_tags + 1) * 128 floats, or NULL (first level through the MMAs)
 int s2v_launch_level(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int64_t n_src, int d, const void* row_ptr,
                      bool rp64, const int32_t* col_idx, const float* val, const float* H, const float* W,
                      const float* X, const float* table, const int32_t* x_index, int n_table, float* out);

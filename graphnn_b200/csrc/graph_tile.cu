@@ -214,7 +214,7 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
                       const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ col_idx,
                       const float* __restrict__ val, const int32_t* __restrict__ graph_ptr,
                       const int32_t* __restrict__ tags, int num_tags, const float* __restrict__ W_in,
-                      const float* __restrict__ W, int levels, int pool_average, float* __restrict__ Y,
+                      const float* __restrict__ W, const float* __restrict__ P, int levels, int pool_average, float* __restrict__ Y,
                       float* __restrict__ embed_out, s2v_device_status* status)
 {
     const int num_tiles = *tile_count_p;
@@ -361,14 +361,89 @@ s2v_graph_tile_kernel(const int2* __restrict__ tile_range, const int* __restrict
                     if (HAS_VAL) lval[e] = __ldg(val + base + e);
                 }
             }
+            if (!P) {   // H0 = ReLU(W_in[tag]); `levels` MMA levels follow
 #pragma unroll 4
-            for (int rr = 0; rr < GT_ROWS_PER_WARP; ++rr) {
-                const int r = GT_ROWS_PER_WARP * gw + rr;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (r < nrows) v = relu4(__ldg(Win4 + (int64_t)gt_checked_tag(__ldg(tags + node0 + r), num_tags, bad_index) * 32 + lane));
-                H4s[r * 32 + lane] = v;
+                for (int rr = 0; rr < GT_ROWS_PER_WARP; ++rr) {
+                    const int r = GT_ROWS_PER_WARP * gw + rr;
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (r < nrows) v = relu4(__ldg(Win4 + (int64_t)gt_checked_tag(__ldg(tags + node0 + r), num_tags, bad_index) * 32 + lane));
+                    H4s[r * 32 + lane] = v;
+                }
             }
             if (!gsync(30)) { alive = false; break; }
+            if (P) {
+                // The first level needs no product: H0 has one distinct row per tag, so (sum_t H0[col t]) * W is a sum of
+                // rows of P = ReLU(W_in) * W (row num_tags of P is zero: unused slots add it).  The tile starts at
+                // H1 = ReLU(sum_t P[tag[col t]] + W_in[tag]) and `levels` counts the MMA levels that follow.
+                const float4* __restrict__ P4 = reinterpret_cast<const float4*>(P);
+                constexpr int GT_P1_ROWS = 2;   // rows whose table loads are in flight together (more spills registers)
+#pragma unroll 1
+                for (int r4 = 0; r4 < GT_ROWS_PER_WARP; r4 += GT_P1_ROWS) {
+                    int pt[GT_P1_ROWS][4], dg[GT_P1_ROWS], bg[GT_P1_ROWS];
+#pragma unroll
+                    for (int a = 0; a < GT_P1_ROWS; ++a) {
+                        const int r = GT_ROWS_PER_WARP * gw + r4 + a;
+                        bg[a] = lrp[r];
+                        dg[a] = r < nrows ? lrp[r + 1] - bg[a] : 0;
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            int c = 0;
+                            if (u < dg[a]) {
+                                if (cached) c = lcol[bg[a] + u];
+                                else {
+                                    c = __ldg(col_idx + base + bg[a] + u) - node0;
+                                    if ((unsigned)c >= (unsigned)nrows) c = 0;   // reported when the gather records are built
+                                }
+                            }
+                            pt[a][u] = u < dg[a] ? tag_s[c] : num_tags;
+                        }
+                    }
+                    float4 pv[GT_P1_ROWS][4], xv[GT_P1_ROWS];
+#pragma unroll
+                    for (int a = 0; a < GT_P1_ROWS; ++a) {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) pv[a][u] = __ldg(P4 + pt[a][u] * 32 + lane);
+                        xv[a] = __ldg(Win4 + tag_s[GT_ROWS_PER_WARP * gw + r4 + a] * 32 + lane);
+                    }
+#pragma unroll
+                    for (int a = 0; a < GT_P1_ROWS; ++a) {
+                        const int r = GT_ROWS_PER_WARP * gw + r4 + a;
+                        float4 acc;
+                        if (HAS_VAL) {
+                            float w[4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) w[u] = u < dg[a] ? (cached ? lval[bg[a] + u] : __ldg(val + base + bg[a] + u)) : 0.f;
+                            acc = make_float4(w[0] * pv[a][0].x, w[0] * pv[a][0].y, w[0] * pv[a][0].z, w[0] * pv[a][0].w);
+#pragma unroll
+                            for (int u = 1; u < 4; ++u) {
+                                acc.x = fmaf(w[u], pv[a][u].x, acc.x); acc.y = fmaf(w[u], pv[a][u].y, acc.y);
+                                acc.z = fmaf(w[u], pv[a][u].z, acc.z); acc.w = fmaf(w[u], pv[a][u].w, acc.w);
+                            }
+                        } else {   // adds in CSR order; an unused slot adds the row of zeros
+                            acc = make_float4((((pv[a][0].x + pv[a][1].x) + pv[a][2].x) + pv[a][3].x), (((pv[a][0].y + pv[a][1].y) + pv[a][2].y) + pv[a][3].y),
+                                              (((pv[a][0].z + pv[a][1].z) + pv[a][2].z) + pv[a][3].z), (((pv[a][0].w + pv[a][1].w) + pv[a][2].w) + pv[a][3].w));
+                        }
+                        for (int t = 4; t < dg[a]; ++t) {   // rows with more than four neighbours
+                            int c;
+                            if (cached) c = lcol[bg[a] + t];
+                            else {
+                                c = __ldg(col_idx + base + bg[a] + t) - node0;
+                                if ((unsigned)c >= (unsigned)nrows) c = 0;
+                            }
+                            const float4 pp = __ldg(P4 + tag_s[c] * 32 + lane);
+                            if (HAS_VAL) {
+                                const float w = cached ? lval[bg[a] + t] : __ldg(val + base + bg[a] + t);
+                                acc.x = fmaf(w, pp.x, acc.x); acc.y = fmaf(w, pp.y, acc.y); acc.z = fmaf(w, pp.z, acc.z); acc.w = fmaf(w, pp.w, acc.w);
+                            } else {
+                                acc.x += pp.x; acc.y += pp.y; acc.z += pp.z; acc.w += pp.w;
+                            }
+                        }
+                        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (r < nrows) v = make_float4(relu_ref(acc.x + xv[a].x), relu_ref(acc.y + xv[a].y), relu_ref(acc.z + xv[a].z), relu_ref(acc.w + xv[a].w));
+                        H4s[r * 32 + lane] = v;
+                    }
+                }
+            }
             // gather record of row r: offsets (from the shared-memory base) of the rows of its first four neighbours;
             // unused slots point at the row of zeros, so the gather needs no test per slot
             if (gtix < GT_NODES) {
@@ -616,10 +691,20 @@ size_t s2v_graph_tiles_plan_bytes(int64_t num_graphs)
 // scratch of s2v_graph_tiles_plan_bytes(G) bytes, 256-byte aligned.
 int s2v_launch_graph_tiles(s2v_ctx* ctx, cudaStream_t st, int64_t G, const int32_t* row_ptr, const int32_t* col_idx,
                            const float* val, const int32_t* graph_ptr, const int32_t* tags, int num_tags,
-                           const float* W_in, const float* W, int levels, int pool_average, void* plan, float* Y,
-                           float* embed_out)
+                           const float* W_in, const float* W, int levels, int pool_average, void* plan, float* P_scratch,
+                           float* Y, float* embed_out)
 {
     if (GT_SMEM_BYTES > ctx->smem_optin || PLAN_SMEM > ctx->smem_optin) return S2V_ERR_UNSUPPORTED;
+    // With a scratch for the product table ((num_tags + 1) x 128 floats) the first level is done in the tile prologue
+    // as a sum of table rows, and the kernel runs levels - 1 MMA levels.
+    const float* P = nullptr;
+    int mma_levels = levels;
+    if (P_scratch && levels >= 1) {
+        const int rc = s2v_launch_first_table_product(ctx, st, num_tags, GT_D, W_in, W, P_scratch, true);
+        if (rc != S2V_OK) return rc;
+        P = P_scratch;
+        mma_levels = levels - 1;
+    }
     int* tile_count = static_cast<int*>(plan);
     int2* tile_range = reinterpret_cast<int2*>(static_cast<unsigned char*>(plan) + 256);
     S2V_CUDA_OK(ctx, cudaFuncSetAttribute(gt_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PLAN_SMEM));
@@ -631,13 +716,13 @@ int s2v_launch_graph_tiles(s2v_ctx* ctx, cudaStream_t st, int64_t G, const int32
         auto kern = s2v_graph_tile_kernel<true>;
         S2V_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM_BYTES));
         kern<<<(unsigned)blocks, GT_THREADS, GT_SMEM_BYTES, st>>>(tile_range, tile_count, row_ptr, col_idx, val, graph_ptr, tags,
-                                                                  num_tags, W_in, W, levels, pool_average, Y, embed_out,
+                                                                  num_tags, W_in, W, P, mma_levels, pool_average, Y, embed_out,
                                                                   ctx->dstatus_dev);
     } else {
         auto kern = s2v_graph_tile_kernel<false>;
         S2V_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM_BYTES));
         kern<<<(unsigned)blocks, GT_THREADS, GT_SMEM_BYTES, st>>>(tile_range, tile_count, row_ptr, col_idx, val, graph_ptr, tags,
-                                                                  num_tags, W_in, W, levels, pool_average, Y, embed_out,
+                                                                  num_tags, W_in, W, P, mma_levels, pool_average, Y, embed_out,
                                                                   ctx->dstatus_dev);
     }
     S2V_CHECK_LAUNCH(ctx, "s2v_graph_tile_kernel");

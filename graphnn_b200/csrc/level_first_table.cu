@@ -19,16 +19,21 @@ namespace
 {
 
 // P[t, j] = sum_k ReLU(table[t, k]) * W[k, j], k ascending, one CTA per table row, one thread per column (strided).
-__global__ void __launch_bounds__(256) first_table_product_kernel(int d, const float* __restrict__ table, const float* __restrict__ W,
-                                                                  float* __restrict__ P)
+__global__ void __launch_bounds__(256) first_table_product_kernel(int n_table, int d, const float* __restrict__ table,
+                                                                  const float* __restrict__ W, float* __restrict__ P)
 {
     extern __shared__ float h0[];
     const int t = blockIdx.x;
+    if (t >= n_table) {   // the extra row some callers ask for: zeros (what an unused gather slot adds)
+        for (int j = threadIdx.x; j < d; j += blockDim.x) P[(int64_t)t * d + j] = 0.f;
+        return;
+    }
     for (int k = threadIdx.x; k < d; k += blockDim.x) h0[k] = relu_ref(__ldg(table + (int64_t)t * d + k));
     __syncthreads();
     for (int j = threadIdx.x; j < d; j += blockDim.x) {
         float acc = 0.f;
-        for (int k = 0; k < d; ++k) acc = fmaf(h0[k], __ldg(W + (int64_t)k * d + j), acc);
+#pragma unroll 16
+        for (int k = 0; k < d; ++k) acc = fmaf(h0[k], __ldg(W + (int64_t)k * d + j), acc);   // the loads of 16 steps go out together
         P[(int64_t)t * d + j] = acc;
     }
 }
@@ -172,14 +177,24 @@ size_t s2v_first_table_scratch_bytes(int n_table, int d)
     return sizeof(float) * (size_t)n_table * (size_t)d;
 }
 
+// P[t,:] = ReLU(table[t,:]) * W for the n_table rows of the table; with extra_zero_row one more row of zeros follows.
+int s2v_launch_first_table_product(s2v_ctx* ctx, cudaStream_t st, int n_table, int d, const float* table, const float* W,
+                                   float* P, bool extra_zero_row)
+{
+    first_table_product_kernel<<<n_table + (extra_zero_row ? 1 : 0), d < 256 ? ((d + 31) / 32) * 32 : 256, sizeof(float) * (size_t)d, st>>>(
+        n_table, d, table, W, P);
+    S2V_CHECK_LAUNCH(ctx, "first_table_product_kernel");
+    return S2V_OK;
+}
+
 // out = the first level for all n rows; P_scratch holds n_table * d floats (overwritten).
 int s2v_launch_level_first_table(s2v_ctx* ctx, cudaStream_t st, int64_t n, int d, const int32_t* row_ptr, const int32_t* col_idx,
                                  const float* val, const float* W, const float* table, int n_table, const int32_t* tags,
                                  float* P_scratch, float* out)
 {
     if (!s2v_first_table_supported(d)) return S2V_ERR_UNSUPPORTED;
-    first_table_product_kernel<<<n_table, d < 256 ? ((d + 31) / 32) * 32 : 256, sizeof(float) * (size_t)d, st>>>(d, table, W, P_scratch);
-    S2V_CHECK_LAUNCH(ctx, "first_table_product_kernel");
+    const int rc = s2v_launch_first_table_product(ctx, st, n_table, d, table, W, P_scratch, false);
+    if (rc != S2V_OK) return rc;
     const int lpr = d / 4;
     const int64_t rows_per_block = (int64_t)FT_WARPS * 32;   // a warp takes 32 rows at a time
     int64_t blocks = (n + rows_per_block - 1) / rows_per_block;

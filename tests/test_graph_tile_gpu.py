@@ -13,9 +13,10 @@ from graphnn_b200 import capi, engine, synth
 pytestmark = pytest.mark.gpu
 
 
-def forward(batch, tiles=True, val=None, pool_average=False, hint=None, levels=None, check_status=True):
+def forward(batch, tiles=True, val=None, pool_average=False, hint=None, levels=None, check_status=True, first_table=True):
     eng = engine.S2VInference(batch.weights, batch.levels if levels is None else levels, pool_average=pool_average)
     eng.ctx.set_option(eng.ctx.OPT_GRAPH_TILES, 1 if tiles else 0)
+    eng.ctx.set_option(eng.ctx.OPT_FIRST_LEVEL_TABLE, 1 if first_table else 0)
     hb = engine.build_host_batch(batch)
     db = eng.to_device(hb)
     if val is not None:
@@ -86,16 +87,21 @@ def test_tile_kernel_matches_oracle_on_molecules(oracle_lib):
     b = synth.molecules_16k(seed=1, num_graphs=700)
     o = oracle_lib.forward(b, "oracle")
     r = forward(b)
-    assert r["launches"] == 3                     # tile plan, tile kernel, readout
+    assert r["launches"] == 4                     # first-level product table, tile plan, tile kernel, readout
     assert_close(r["embed"].cpu().numpy(), o["levels"][-1], "embeddings")
     assert_close(r["logits"].cpu().numpy(), o["logits"], "logits", scale=max(1.0, float(np.abs(o["logits"]).max())))
     assert_close(r["probs"].cpu().numpy(), o["probs"], "probs")
     margin = np.sort(o["logits"], axis=1)
     safe = (margin[:, -1] - margin[:, -2]) > 1e-4 * np.abs(o["logits"]).max()
     assert np.array_equal(r["pred"].cpu().numpy()[safe], o["argmax"][safe]) and safe.mean() > 0.9
+    # the same kernel with its first level pushed through the MMA pipeline like the others (S2V_OPT_FIRST_LEVEL_TABLE = 0)
+    q = forward(b, first_table=False)
+    assert q["launches"] == 3                     # tile plan, tile kernel, readout
+    assert_close(q["embed"].cpu().numpy(), o["levels"][-1], "embeddings, first level through the MMAs")
+    assert_close(q["logits"].cpu().numpy(), o["logits"], "logits, first level through the MMAs", scale=max(1.0, float(np.abs(o["logits"]).max())))
     # the per-level kernels of the same library agree inside the same bar
     p = forward(b, tiles=False)
-    assert p["launches"] > 3
+    assert p["launches"] > 4
     assert_close(r["embed"].cpu().numpy(), p["embed"].cpu().numpy(), "tile kernel vs per-level kernels")
 
 
@@ -124,7 +130,7 @@ def test_tile_kernel_edge_cases(name, sizes, edge_fn):
     std = 0.004 if edge_fn is clique_edges else 0.05      # keep 4 levels of 100-neighbour sums in range
     b = custom_batch(sizes, edge_fn, seed=len(sizes), std=std)
     r = forward(b)
-    assert r["launches"] == 3
+    assert r["launches"] == 4
     want_h, want_logits = f64_forward(b, r["hb"])
     scale_h = max(1.0, float(np.abs(want_h).max()))
     assert_close(r["embed"].cpu().numpy(), want_h, f"{name}: embeddings", scale=scale_h)
@@ -139,7 +145,7 @@ def test_tile_kernel_weighted_edges_and_mean_pooling(levels):
     rng = np.random.default_rng(9)
     val = (rng.random(b.num_edges, dtype=np.float32) * 0.6 + 0.2).astype(np.float32)
     r = forward(b, val=val, pool_average=True, levels=levels)
-    assert r["launches"] == 3
+    assert r["launches"] == 4
     want_h, want_logits = f64_forward(b, r["hb"], val=val, pool_average=True, levels=levels)
     assert_close(r["embed"].cpu().numpy(), want_h, "weighted embeddings", scale=max(1.0, float(np.abs(want_h).max())))
     assert_close(r["logits"].cpu().numpy(), want_logits, "mean-pooled logits", scale=max(1.0, float(np.abs(want_logits).max())))
