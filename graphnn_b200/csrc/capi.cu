@@ -350,8 +350,8 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
     int rc;
     // Batches of small graphs (the caller vouches for the largest one): the whole classifier up to the pooled
     // embeddings is one kernel that keeps the node embeddings of a tile of whole graphs in shared memory.
-    // Measured on 20-40-node graphs, d = 128, 4 levels: one launch beats the per-level kernels by 2.0x at 16 k nodes,
-    // 1.11x at 62 k, 1.05x at 123 k, and loses 11 % at 246 k and 17 % at 491 k (the per-level kernels stream better
+    // Measured on 20-40-node graphs, d = 128, 4 levels: one launch beats the per-level kernels by 1.9x at 16 k nodes,
+    // 1.15x at 62 k, 1.09x at 123 k, and loses 5 % at 246 k and 11 % at 491 k (the per-level kernels stream better
     // once every SM has dozens of tiles), so the automatic mode takes it up to S2V_TILE_AUTO_MAX_NODES nodes.
     const bool want_tiles = ctx->graph_tiles == 1 || (ctx->graph_tiles == 2 && N <= S2V_TILE_AUTO_MAX_NODES);
     if (want_tiles && d == 128 && L >= 1 && batch->tags && batch->max_graph_nodes >= 1 &&

@@ -74,7 +74,7 @@ typedef enum s2v_option {
                                         (default from S2V_LEVEL_TC) */
     S2V_OPT_GRAPH_TILES = 3,         /* whole-classifier tile kernel (s2v_graph_tiles_f32) inside s2v_forward_f32 for batches of
                                         small graphs: 0 never, 1 whenever the batch allows, 2 automatic (default: batches of at
-                                        most 160,000 nodes, where one launch beats the per-level kernels by 1.05x - 2x; larger
+                                        most 160,000 nodes, where one launch beats the per-level kernels by 1.1x - 1.9x; larger
                                         batches stream better through the per-level kernels).  Default from S2V_GRAPH_TILES */
     S2V_OPT_FIRST_LEVEL_TABLE = 5,   /* first level from one-hot tags as a gather-sum over the product table ReLU(W_in) * W
                                         (see s2v_level_first_f32): 1 (default) whenever d allows, 0 never (the level kernels'
