@@ -280,7 +280,7 @@ __global__ void __launch_bounds__(256) readout_v4_kernel(int64_t G, int d, int h
 // truncation, small terms first, fp32 accumulate), then ReLU into the shared hidden tile.  The second layer
 // (hidden x C, C small) and softmax / argmax follow as in the register-tiled form: one warp per graph.
 template <int NT /* 8-column MMA tiles per warp = hidden / 32 */>
-__global__ void __launch_bounds__(256) readout_mma_kernel(int64_t G, int d, int C, const float* __restrict__ Y,
+__global__ void __launch_bounds__(256, 4) readout_mma_kernel(int64_t G, int d, int C, const float* __restrict__ Y,
                                                           const float* __restrict__ W1, const float* __restrict__ W2,
                                                           float* __restrict__ logits, float* __restrict__ probs,
                                                           int32_t* __restrict__ pred)
@@ -453,7 +453,8 @@ int s2v_readout_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int d, 
     const size_t smem4 = sizeof(float) * (size_t)TG4 * ((size_t)d + 4 + hidden + 4 + num_class);
     if (d % 8 == 0 && (hidden == 256 || hidden == 128) && smem4 <= 96 * 1024 && s2v_aligned16(Y) && num_graphs >= 256) {
         // batches of hundreds of graphs and the two hidden sizes of the path: first layer on the tensor cores
-        const unsigned grid = grid_cap(ctx, (num_graphs + TG4 - 1) / TG4, 3);
+        // four CTAs per SM (64 registers, 50 KB of shared memory each): the 512 tiles of a 16,384-graph batch run as one wave
+        const unsigned grid = grid_cap(ctx, (num_graphs + TG4 - 1) / TG4, 4);
         if (hidden == 256) {
             S2V_CUDA_OK(ctx, cudaFuncSetAttribute(readout_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4));
             readout_mma_kernel<8><<<grid, 256, smem4, s2v_pick_stream(ctx, stream)>>>(num_graphs, d, num_class, Y, W1, W2, logits, probs, pred);
