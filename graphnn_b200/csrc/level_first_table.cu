@@ -11,8 +11,9 @@
 // P is a few dozen rows, computed once per call by a tiny launch; the level itself becomes a gather-sum from a table
 // that sits in L1, plus the X lookup and the ReLU: no split, no tensor-memory round trip, no MMA.  The launch is
 // then bounded by writing H1 (N*d*4 bytes); the dependent chain row offset -> column -> tag -> table row is cut to
-// three latencies per 32 rows by staging the neighbours' tags in shared memory a warp-load at a time.  Sums run over the non-zeros in CSR order in fp32, so the result is deterministic; it differs from the
-// "sum first, multiply after" order of the other kernels by fp32 rounding only.
+// three latencies per 32 rows by staging the neighbours' tags in shared memory a warp-load at a time.  Sums run over
+// the non-zeros in CSR order in fp32, so the result is deterministic; it differs from the "sum first, multiply
+// after" order of the other kernels by fp32 rounding only.
 #include "common.cuh"
 
 namespace

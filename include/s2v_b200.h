@@ -76,12 +76,12 @@ typedef enum s2v_option {
                                         small graphs: 0 never, 1 whenever the batch allows, 2 automatic (default: batches of at
                                         most 160,000 nodes, where one launch beats the per-level kernels by 1.1x - 1.9x; larger
                                         batches stream better through the per-level kernels).  Default from S2V_GRAPH_TILES */
-    S2V_OPT_FIRST_LEVEL_TABLE = 5,   /* first level from one-hot tags as a gather-sum over the product table ReLU(W_in) * W
-                                        (see s2v_level_first_f32): 1 (default) whenever d allows, 0 never (the level kernels'
-                                        own table-lookup form is used instead) */
-    S2V_OPT_RESERVED_SMS = 4         /* the persistent kernels size their grids for (SM count - value) SMs, leaving the rest to
+    S2V_OPT_RESERVED_SMS = 4,        /* the persistent kernels size their grids for (SM count - value) SMs, leaving the rest to
                                         kernels of another stream -- a communication library's, which cannot start while
                                         one-CTA-per-SM kernels hold every SM (default 0; 0 <= value < SM count) */
+    S2V_OPT_FIRST_LEVEL_TABLE = 5    /* first level from one-hot tags as a gather-sum over the product table ReLU(W_in) * W
+                                        (see s2v_level_first_f32): 1 (default) whenever d allows, 0 never (the level kernels'
+                                        own table-lookup form is used instead) */
 } s2v_option;
 int s2v_ctx_set_option(s2v_ctx* ctx, int option, int value);
 /* Diagnostic, no counterpart in the reference: launches a two-warp kernel whose bounded barrier waits (the
