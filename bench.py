@@ -837,6 +837,7 @@ def run_case(args):
     mol_d128    per-level kernel on 16,384 molecule-like graphs, d=128, X looked up from W_in by tag
     prot_d64    per-level kernel on 2,048 protein-like graphs, d=64
     mol_first   first level straight from the tags (product table + gather-sum) on 16,384 molecule-like graphs, d=128
+    prot_first  the same on 2,048 protein-like graphs, d=64
     mol_tiles   tile kernel (projection + 4 levels + pooling) on 16,384 molecule-like graphs;  mol_tiles_small: 4,096 graphs
     mol_paths   whole forward pass (s2v_forward_f32) on 512 .. 16,384 molecule-like graphs through the per-level kernels
                 and through the tile kernel, one line per batch size"""
@@ -884,7 +885,7 @@ def run_case(args):
         launch = lambda: ctx.level(rp, ci, None, H, W, X, out, stream=st)
         desc = f"{p.name}: n={p.n_rows} nnz={p.nnz}"
     else:
-        if args.case == "prot_d64":
+        if args.case in ("prot_d64", "prot_first"):
             b = synth.proteins_4k(seed=0, num_graphs=2048)
         else:
             b = synth.molecules_16k(seed=0, num_graphs=4096 if args.case.endswith("small") else 16384)
@@ -892,7 +893,7 @@ def run_case(args):
         rp, ci, tags, gp = up(rp_h), up(ci_h), up(b.tags.astype(np.int32)), up(b.graph_offsets())
         W, table = up(b.weights["p_node_conv"]), up(b.weights["w_n2l"])
         desc = f"{b.name}: G={b.num_graphs} N={b.num_nodes} nnz={b.num_edges} d={b.d}"
-        if args.case == "mol_first":
+        if args.case in ("mol_first", "prot_first"):
             out = torch.empty((b.num_nodes, b.d), device=dev)
             launch = lambda: ctx.level_first(rp, ci, None, W, table, tags, out, stream=st)
         elif args.case.startswith("mol_tiles"):
@@ -936,7 +937,7 @@ def main():
     ap.add_argument("--tiles", type=int, default=2, choices=[0, 1, 2],
                     help="S2V_OPT_GRAPH_TILES: 0 per-level kernels only, 1 whole-classifier tile kernel whenever the batch allows, "
                          "2 the library's default (tile kernel for batches of at most 160,000 nodes)")
-    ap.add_argument("--case", default=None, choices=["er_d64", "er_d64_full", "mol_d128", "prot_d64", "mol_first", "mol_tiles", "mol_tiles_small", "mol_paths"],
+    ap.add_argument("--case", default=None, choices=["er_d64", "er_d64_full", "mol_d128", "prot_d64", "mol_first", "prot_first", "mol_tiles", "mol_tiles_small", "mol_paths"],
                     help="run one small launch case (for profiler captures) instead of the benchmark")
     ap.add_argument("--launches", type=int, default=3)
     args = ap.parse_args()
