@@ -319,10 +319,13 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
     {                                                                                              \
         const uint32_t m4 = (uint32_t)em & 15u;                                                    \
         em >>= 4;                                                                                  \
-        /* no row end among these four non-zeros: sums only.  One lane group per warp (d = 128), so the    \
-           branch is warp-uniform; measured -3.3 % on the molecule input; with two groups per warp         \
-           (d = 64) the groups diverge and it costs 1.3 % on the protein input, so it is left out there */ \
-        if (G == 1 && m4 == 0u) {                                                                  \
+        const uint32_t m4w = (G == 1) ? m4 : ((uint32_t)em_warp & 15u);   /* row ends of ANY lane group */ \
+        if (G > 1) em_warp >>= 4;                                                                  \
+        /* no row end among these four non-zeros in ANY lane group of the warp: sums only (the test is   \
+           warp-uniform).  Measured: -3.3 % on the molecule input (d = 128, one group per warp), -2.2 % on   \
+           the Erdos-Renyi d = 64 problem, -0.3 % on the protein input; testing only the lane's own group   \
+           at d = 64 made the two groups diverge and cost 1.3 % there */                                   \
+        if (m4w == 0u) {                                                                           \
             _Pragma("unroll") for (int u = 0; u < TC_U; ++u) {                                     \
                 if (HAS_VAL) {                                                                     \
                     acc.x = fmaf(wt[u], v[u].x, acc.x); acc.y = fmaf(wt[u], v[u].y, acc.y);        \
@@ -359,15 +362,19 @@ s2v_level_tc_kernel(int64_t n_rows, int64_t num_tiles, const int32_t* __restrict
                         __syncwarp();
                     }
                     // "the p-th non-zero of this segment is the last of its row", per lane group
-                    uint32_t em_lo = 0, em_hi = 0;
+                    uint32_t em_lo = 0, em_hi = 0, any_lo = 0, any_hi = 0;
 #pragma unroll
                     for (int gg = 0; gg < G; ++gg) {
                         const bool here = ne_row && rg == gg && (pos >> 6) == k;
                         const uint32_t lo = __reduce_or_sync(0xffffffffu, (here && (pos & 63) < 32) ? (1u << (pos & 31)) : 0u);
                         const uint32_t hi = __reduce_or_sync(0xffffffffu, (here && (pos & 63) >= 32) ? (1u << (pos & 31)) : 0u);
                         if (gg == sub) { em_lo = lo; em_hi = hi; }
+                        any_lo |= lo;
+                        any_hi |= hi;
                     }
                     unsigned long long em = ((unsigned long long)em_hi << 32) | em_lo;
+                    unsigned long long em_warp = ((unsigned long long)any_hi << 32) | any_lo;   // the same for every lane of the warp
+                    (void)em_warp;
                     const int seg_n = min(WSZ, cnt - WSZ * k);   // my group's non-zeros in this segment (may be <= 0)
                     if (seg_n > 0) {
                         const int cz = win[0];
