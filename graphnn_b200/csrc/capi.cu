@@ -247,9 +247,8 @@ int s2v_level_first_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n, int d, const
     if (!row_ptr || !W || !table || !tags || !out) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level_first: NULL pointer");
     if (!s2v_aligned16(W) || !s2v_aligned16(table) || !s2v_aligned16(out))
         return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "level_first: W, table, out must be 16-byte aligned");
-    int rc = s2v_launch_index_check(ctx, s2v_pick_stream(ctx, stream), n, tags, n_table);
-    if (rc != S2V_OK) return rc;
-    if (ctx->first_table_on && s2v_first_table_supported(d)) {
+    int rc;
+    if (ctx->first_table_on && s2v_first_table_supported(d)) {   // (this kernel range-checks the tags itself)
         // gather-sum over the product table ReLU(table) * W, which lives in a small context-owned buffer
         const size_t need = s2v_first_table_scratch_bytes(n_table, d);
         if (need > ctx->first_table_bytes) {
@@ -264,6 +263,8 @@ int s2v_level_first_f32(s2v_ctx* ctx, s2v_stream stream, int64_t n, int d, const
     }
     if (!s2v_use_tc(ctx, d, n))
         return s2v_fail(ctx, S2V_ERR_UNSUPPORTED, "level_first: d / 4 must be a power of two up to 32; materialise H0 instead");
+    rc = s2v_launch_index_check(ctx, s2v_pick_stream(ctx, stream), n, tags, n_table);
+    if (rc != S2V_OK) return rc;
     rc = s2v_launch_level_tc(ctx, s2v_pick_stream(ctx, stream), n, d, row_ptr, col_idx, val, nullptr, W, nullptr, table,
                              tags, n_table, out);
     if (rc == S2V_ERR_UNSUPPORTED) return s2v_fail(ctx, rc, "level_first: shape not supported by the tcgen05 kernel");
@@ -373,12 +374,11 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
     const bool onehot = batch->tags != nullptr && d % 4 == 0;
     // first level straight from the tags (no H0 in memory) when the tcgen05 kernel takes this shape
     bool first_fused = false;
-    if (onehot) {   // the tags are range-checked once per batch; the level kernels only clamp them
+    if (onehot) {
         if (!s2v_aligned16(model->w_n2l) || !s2v_aligned16(model->p_node_conv) || (embed_out && !s2v_aligned16(embed_out)))
             return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "forward: weights and embed_out must be 16-byte aligned");
-        rc = s2v_launch_index_check(ctx, st, N, batch->tags, model->num_feat);
-        if (rc != S2V_OK) return rc;
     }
+    bool tags_checked = false;
     if (onehot && L >= 1 && ctx->first_table_on && s2v_first_table_supported(d) &&
         s2v_first_table_scratch_bytes(model->num_feat, d) <= nd) {
         // H0 = ReLU(W_in[tag]) has one distinct row per tag, so level 1 is a gather-sum over the rows of
@@ -386,8 +386,12 @@ int s2v_forward_f32(s2v_ctx* ctx, s2v_stream stream, const s2v_model* model, con
         float* dst = (L == 1 && embed_out) ? embed_out : ha;
         rc = s2v_launch_level_first_table(ctx, st, N, d, batch->n2n_row_ptr, batch->n2n_col_idx, batch->n2n_val, model->p_node_conv,
                                           model->w_n2l, model->num_feat, batch->tags, msg, dst);
-        if (rc == S2V_OK) first_fused = true;
+        if (rc == S2V_OK) first_fused = tags_checked = true;   // that kernel range-checks every tag itself
         else if (rc != S2V_ERR_UNSUPPORTED) return rc;
+    }
+    if (onehot && !tags_checked) {   // the tags are range-checked once per batch; the level kernels only clamp them
+        rc = s2v_launch_index_check(ctx, st, N, batch->tags, model->num_feat);
+        if (rc != S2V_OK) return rc;
     }
     if (!first_fused && onehot && L >= 1 && s2v_use_tc(ctx, d, N)) {
         float* dst = (L == 1 && embed_out) ? embed_out : ha;

@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(FT_WARPS * 32) first_level_table_kernel(int64_
                                                                          const int32_t* __restrict__ col_idx, const float* __restrict__ val,
                                                                          const int32_t* __restrict__ tags, int n_table,
                                                                          const float4* __restrict__ P, const float4* __restrict__ table,
-                                                                         float4* __restrict__ out)
+                                                                         float4* __restrict__ out, s2v_device_status* status)
 {
     __shared__ int s_tag[FT_WARPS][FT_CAP];
     __shared__ float s_val[HAS_VAL ? FT_WARPS : 1][HAS_VAL ? FT_CAP : 1];
@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(FT_WARPS * 32) first_level_table_kernel(int64_
     int* const my_tags = s_tag[wib];
     float* const my_vals = s_val[HAS_VAL ? wib : 0];
     const unsigned FULL = 0xffffffffu;
+    bool bad_tag = false;
 
     for (int64_t base = warp * 32; base < n; base += warps * 32) {
         const int nrows = (int)((n - base) < 32 ? (n - base) : 32);
@@ -73,7 +74,11 @@ __global__ void __launch_bounds__(FT_WARPS * 32) first_level_table_kernel(int64_
         const int64_t ri = base + (lane < nrows ? lane : nrows);
         const int32_t rp_lo = __ldg(row_ptr + ri);
         const int32_t rp_hi = lane < nrows ? __ldg(row_ptr + ri + 1) : rp_lo;
-        const unsigned row_tag = lane < nrows ? min((unsigned)__ldg(tags + base + lane), top) : 0u;
+        // every node is a row here, so checking the rows' own tags checks all of them: a tag outside the table is
+        // clamped where it is used and reported once, at the end of the kernel (S2V_ERR_INVALID_ARG)
+        const unsigned raw_tag = lane < nrows ? (unsigned)__ldg(tags + base + lane) : 0u;
+        bad_tag |= raw_tag > top;
+        const unsigned row_tag = min(raw_tag, top);
         int r0 = 0;
         while (r0 < nrows) {
             const int32_t start = __shfl_sync(FULL, rp_lo, r0);
@@ -163,6 +168,10 @@ __global__ void __launch_bounds__(FT_WARPS * 32) first_level_table_kernel(int64_
             r0 = r1;
         }
     }
+    if (bad_tag) {   // record, do not fault
+        status->code = S2V_ERR_INVALID_ARG;
+        status->where = 2;
+    }
 }
 
 }  // namespace
@@ -188,7 +197,8 @@ int s2v_launch_first_table_product(s2v_ctx* ctx, cudaStream_t st, int n_table, i
     return S2V_OK;
 }
 
-// out = the first level for all n rows; P_scratch holds n_table * d floats (overwritten).
+// out = the first level for all n rows; P_scratch holds n_table * d floats (overwritten).  The kernel also range-checks
+// all n tags (it reads each of them as a row's own tag), so no separate checking launch is needed beside it.
 int s2v_launch_level_first_table(s2v_ctx* ctx, cudaStream_t st, int64_t n, int d, const int32_t* row_ptr, const int32_t* col_idx,
                                  const float* val, const float* W, const float* table, int n_table, const int32_t* tags,
                                  float* P_scratch, float* out)
@@ -205,7 +215,7 @@ int s2v_launch_level_first_table(s2v_ctx* ctx, cudaStream_t st, int64_t n, int d
     const float4* P4 = reinterpret_cast<const float4*>(P_scratch);
     const float4* T4 = reinterpret_cast<const float4*>(table);
     float4* O4 = reinterpret_cast<float4*>(out);
-#define FT_LAUNCH(HV, L) first_level_table_kernel<HV, L><<<(unsigned)blocks, FT_WARPS * 32, 0, st>>>(n, lpr, row_ptr, col_idx, val, tags, n_table, P4, T4, O4)
+#define FT_LAUNCH(HV, L) first_level_table_kernel<HV, L><<<(unsigned)blocks, FT_WARPS * 32, 0, st>>>(n, lpr, row_ptr, col_idx, val, tags, n_table, P4, T4, O4, ctx->dstatus_dev)
     if (val) {
         if (lpr == 32) FT_LAUNCH(true, 32); else if (lpr == 16) FT_LAUNCH(true, 16); else if (lpr == 8) FT_LAUNCH(true, 8); else FT_LAUNCH(true, 0);
     } else {
