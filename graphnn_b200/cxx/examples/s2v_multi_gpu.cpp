@@ -8,12 +8,15 @@
 //       hidden, C}, nodes_per_graph, edge_src, edge_dst, tags, four weight matrices).
 //       out.bin: logits[G*C] (fp32), pred[G] (int32) as gathered on rank 0.
 //
-//   s2v_multi_gpu giant <graph.bin> <out.bin> [--gpus N] [--levels L] [--chunks C] [--iters K]
+//   s2v_multi_gpu giant <graph.bin> <out.bin> [--gpus N] [--levels L] [--chunks C] [--iters K] [--exchange referenced]
 //       One graph partitioned by rows: GPU p owns rows [p*N/P, (p+1)*N/P) of A and of H; a level is the fused level
 //       kernel on the local rows (all of H as the gather source) and one all-gather of the new rows.  The local rows
 //       are cut into C blocks and block k is exchanged (s2v_allgather_rows_f32, in place, on a second stream) while
 //       block k+1 is computed.  H is stored block-major ([block][rank][rows of the block][d]) so that every exchange
 //       is one contiguous range; the column indices are renumbered to that layout once.
+//       With --exchange referenced every GPU fetches only the rows of H that its own rows name: its table is
+//       [own rows | referenced remote rows in ascending order]; per block the owner packs the rows each peer asked for
+//       (s2v_input_proj_onehot_f32 is the row lookup) and one s2v_exchange_rows_f32 drops them into the peers' tables.
 //       graph.bin: int64 header {N, nnz, d}, row_ptr int64[N+1], col_idx int32[nnz], H0 fp32[N*d], W fp32[d*d].
 //       out.bin: H_L fp32[N*d] in row order.
 //
@@ -235,7 +238,11 @@ int run_shard(const char* in_path, const char* out_path, int P, int iters)
 }
 
 // ------------------------------------------------------------------ giant graph, partitioned by rows
-int run_giant(const char* in_path, const char* out_path, int P, int levels, int chunks, int iters)
+int run_giant_referenced(int64_t N, int d, const std::vector<int64_t>& row_ptr, const std::vector<int32_t>& col_idx,
+                         const std::vector<float>& H0, const std::vector<float>& W, const char* out_path, int P, int levels, int chunks,
+                         int iters);
+
+int run_giant(const char* in_path, const char* out_path, int P, int levels, int chunks, int iters, bool referenced)
 {
     FILE* f = fopen(in_path, "rb");
     if (!f) die(std::string("cannot open ") + in_path);
@@ -252,6 +259,7 @@ int run_giant(const char* in_path, const char* out_path, int P, int levels, int 
     read_vec(f, W, (size_t)d * d);
     fclose(f);
     if (N % P) die("the number of rows must divide over the GPUs (pad the graph with isolated nodes)");
+    if (referenced) return run_giant_referenced(N, d, row_ptr, col_idx, H0, W, out_path, P, levels, chunks, iters);
     const int64_t rows = N / P;
     chunks = (int)std::max<int64_t>(1, std::min<int64_t>(chunks, rows));
     std::vector<int64_t> edge(chunks + 1);
@@ -363,11 +371,164 @@ int run_giant(const char* in_path, const char* out_path, int P, int levels, int 
     return 0;
 }
 
+// The same levels with every GPU fetching only the rows of H its own rows reference.
+int run_giant_referenced(int64_t N, int d, const std::vector<int64_t>& row_ptr, const std::vector<int32_t>& col_idx,
+                         const std::vector<float>& H0, const std::vector<float>& W, const char* out_path, int P, int levels, int chunks,
+                         int iters)
+{
+    const int64_t rows = N / P;
+    chunks = (int)std::max<int64_t>(1, std::min<int64_t>(chunks, rows));
+    std::vector<int64_t> edge(chunks + 1);
+    for (int k = 0; k <= chunks; ++k) edge[k] = rows * k / chunks;
+    std::vector<int> devs(P);
+    for (int p = 0; p < P; ++p) devs[p] = p;
+    std::vector<s2v_comm*> comms(P, nullptr);
+    ok_comm(s2v_comm_create(P, devs.data(), comms.data()), nullptr, "s2v_comm_create");
+    std::vector<float> out((size_t)N * d);
+    std::vector<float> ms(P, 0.f);
+    std::vector<std::vector<int64_t>> needs(P);   // needs[p]: the remote rows GPU p references, ascending (shared by the threads)
+    SpinBarrier barrier(P);
+
+    auto worker = [&](int p) {
+        ok_cuda(cudaSetDevice(devs[p]), "cudaSetDevice");
+        s2v_ctx* ctx = nullptr;
+        ok_s2v(s2v_ctx_create(devs[p], &ctx), nullptr, "s2v_ctx_create");
+        const int64_t r_lo = p * rows;
+        const int64_t my_nnz = row_ptr[r_lo + rows] - row_ptr[r_lo];
+        {   // which remote rows do my rows name?
+            std::vector<char> mark((size_t)N, 0);
+            for (int64_t t = 0; t < my_nnz; ++t) mark[(size_t)col_idx[row_ptr[r_lo] + t]] = 1;
+            for (int64_t g = 0; g < N; ++g)
+                if (mark[(size_t)g] && (g < r_lo || g >= r_lo + rows)) needs[p].push_back(g);
+        }
+        barrier.wait();   // every GPU's list is known to every thread from here on
+        const std::vector<int64_t>& need = needs[p];
+        const int64_t n_need = (int64_t)need.size(), n_table = rows + n_need;
+        auto position = [&](int64_t g) -> int64_t {   // own rows first, then the referenced remote rows
+            if (g >= r_lo && g < r_lo + rows) return g - r_lo;
+            return rows + (std::lower_bound(need.begin(), need.end(), g) - need.begin());
+        };
+        std::vector<int32_t> cols((size_t)my_nnz);
+        for (size_t t = 0; t < cols.size(); ++t) cols[t] = (int32_t)position(col_idx[row_ptr[r_lo] + t]);
+        std::vector<int64_t> rp((size_t)rows + chunks), rp_at(chunks), nnz_at(chunks);
+        {
+            size_t w = 0;
+            for (int k = 0; k < chunks; ++k) {
+                rp_at[k] = (int64_t)w;
+                const int64_t b0 = row_ptr[r_lo + edge[k]];
+                nnz_at[k] = b0 - row_ptr[r_lo];
+                for (int64_t i = edge[k]; i <= edge[k + 1]; ++i) rp[w++] = row_ptr[r_lo + i] - b0;
+            }
+        }
+        // per block: what I receive from every owner (a range of `need`), and what every peer asked of my block
+        std::vector<std::vector<int64_t>> recv_off(chunks, std::vector<int64_t>(P, 0)), recv_cnt(chunks, std::vector<int64_t>(P, 0)),
+            send_off(chunks, std::vector<int64_t>(P + 1, 0));
+        std::vector<std::vector<int32_t>> send_idx(chunks);
+        size_t max_send = 1;
+        for (int k = 0; k < chunks; ++k) {
+            for (int s = 0; s < P; ++s) {
+                if (s == p) continue;
+                const auto a = std::lower_bound(need.begin(), need.end(), s * rows + edge[k]);
+                const auto b = std::lower_bound(need.begin(), need.end(), s * rows + edge[k + 1]);
+                recv_off[k][s] = rows + (a - need.begin());
+                recv_cnt[k][s] = b - a;
+            }
+            for (int t = 0; t < P; ++t) {
+                send_off[k][t + 1] = send_off[k][t];
+                if (t == p) continue;
+                const auto a = std::lower_bound(needs[t].begin(), needs[t].end(), r_lo + edge[k]);
+                const auto b = std::lower_bound(needs[t].begin(), needs[t].end(), r_lo + edge[k + 1]);
+                for (auto it = a; it != b; ++it) send_idx[k].push_back((int32_t)(*it - r_lo));
+                send_off[k][t + 1] += b - a;
+            }
+            max_send = std::max(max_send, send_idx[k].size());
+        }
+        int64_t* d_rp = to_device(rp);
+        int32_t* d_cols = to_device(cols);
+        float* d_W = to_device(W);
+        std::vector<int32_t*> d_send_idx(chunks, nullptr);
+        for (int k = 0; k < chunks; ++k)
+            if (!send_idx[k].empty()) d_send_idx[k] = to_device(send_idx[k]);
+        float* sendbuf = nullptr;
+        ok_cuda(cudaMalloc(&sendbuf, sizeof(float) * max_send * d), "cudaMalloc send buffer");
+        // table[0] holds H0 (own rows + the referenced remote rows, taken from the host copy) and is never written
+        float* table[3];
+        for (int i = 0; i < 3; ++i) ok_cuda(cudaMalloc(&table[i], sizeof(float) * (size_t)n_table * d), "cudaMalloc H");
+        {
+            std::vector<float> h0((size_t)n_table * d);
+            memcpy(h0.data(), &H0[(size_t)r_lo * d], sizeof(float) * (size_t)rows * d);
+            for (int64_t i = 0; i < n_need; ++i) memcpy(&h0[(size_t)(rows + i) * d], &H0[(size_t)need[i] * d], sizeof(float) * d);
+            ok_cuda(cudaMemcpy(table[0], h0.data(), sizeof(float) * h0.size(), cudaMemcpyHostToDevice), "cudaMemcpy H0");
+        }
+        cudaStream_t compute = (cudaStream_t)s2v_ctx_stream(ctx), exchange;
+        ok_cuda(cudaStreamCreateWithFlags(&exchange, cudaStreamNonBlocking), "cudaStreamCreate");
+        std::vector<cudaEvent_t> computed(chunks), landed(chunks);
+        for (int k = 0; k < chunks; ++k) {
+            ok_cuda(cudaEventCreateWithFlags(&computed[k], cudaEventDisableTiming), "cudaEventCreate");
+            ok_cuda(cudaEventCreateWithFlags(&landed[k], cudaEventDisableTiming), "cudaEventCreate");
+        }
+        cudaEvent_t e0, e1;
+        ok_cuda(cudaEventCreate(&e0), "cudaEventCreate");
+        ok_cuda(cudaEventCreate(&e1), "cudaEventCreate");
+        float total = 0.f;
+        int last = 0;
+        for (int it = 0; it < iters + 1; ++it) {
+            barrier.wait();
+            ok_cuda(cudaEventRecord(e0, compute), "cudaEventRecord");
+            int cur = 0;
+            for (int lv = 0; lv < levels; ++lv) {
+                const int nxt = cur != 1 ? 1 : 2;
+                for (int k = 0; k < chunks; ++k) {
+                    const int64_t rk = edge[k + 1] - edge[k];
+                    float* piece = table[nxt] + (size_t)edge[k] * d;   // my rows of block k, in place in my table
+                    ok_s2v(s2v_level_rp64_f32(ctx, compute, rk, n_table, d, d_rp + rp_at[k], d_cols + nnz_at[k], nullptr, table[cur], d_W, nullptr,
+                                              piece), ctx, "s2v_level_rp64_f32");
+                    ok_cuda(cudaEventRecord(computed[k], compute), "cudaEventRecord");
+                    ok_cuda(cudaStreamWaitEvent(exchange, computed[k], 0), "cudaStreamWaitEvent");
+                    const int64_t n_send = send_off[k][P];
+                    if (n_send > 0)   // the rows of this block that the peers asked for, packed peer by peer
+                        ok_s2v(s2v_input_proj_onehot_f32(ctx, exchange, n_send, (int)rows, d, d_send_idx[k], table[nxt], sendbuf, nullptr), ctx,
+                               "s2v_input_proj_onehot_f32 (row lookup)");
+                    ok_comm(s2v_exchange_rows_f32(comms[p], exchange, d, sendbuf, send_off[k].data(), table[nxt], recv_off[k].data(),
+                                                  recv_cnt[k].data()), comms[p], "s2v_exchange_rows_f32");
+                    ok_cuda(cudaEventRecord(landed[k], exchange), "cudaEventRecord");
+                }
+                for (int k = 0; k < chunks; ++k) ok_cuda(cudaStreamWaitEvent(compute, landed[k], 0), "cudaStreamWaitEvent");   // the next level reads the whole table
+                cur = nxt;
+            }
+            last = cur;
+            ok_cuda(cudaEventRecord(e1, compute), "cudaEventRecord");
+            ok_s2v(s2v_stream_status(ctx, compute), ctx, "device status");
+            ok_s2v(s2v_stream_status(ctx, exchange), ctx, "device status (exchange stream)");
+            float t = 0.f;
+            ok_cuda(cudaEventElapsedTime(&t, e0, e1), "cudaEventElapsedTime");
+            if (it > 0) total += t;
+        }
+        ms[p] = total / iters;
+        ok_cuda(cudaMemcpy(&out[(size_t)r_lo * d], table[last], sizeof(float) * (size_t)rows * d, cudaMemcpyDeviceToHost), "cudaMemcpy");
+        barrier.wait();
+        s2v_ctx_destroy(ctx);
+    };
+    std::vector<std::thread> threads;
+    for (int p = 0; p < P; ++p) threads.emplace_back(worker, p);
+    for (auto& t : threads) t.join();
+    for (int p = 0; p < P; ++p) s2v_comm_destroy(comms[p]);
+    FILE* fo = fopen(out_path, "wb");
+    if (!fo) die(std::string("cannot write ") + out_path);
+    fwrite(out.data(), sizeof(float), out.size(), fo);
+    fclose(fo);
+    int64_t need_total = 0;
+    for (int p = 0; p < P; ++p) need_total += (int64_t)needs[p].size();
+    printf("giant gpus %d ms_per_iter %.4f referenced_remote_rows %.4f\n", P, *std::max_element(ms.begin(), ms.end()),
+           P > 1 ? (double)need_total / ((double)P * (double)(N - rows)) : 0.0);
+    return 0;
+}
+
 }  // namespace
 
 int main(int argc, char** argv)
 {
-    if (argc < 4) die("usage: s2v_multi_gpu shard|giant <in.bin> <out.bin> [--gpus N] [--iters K] [--levels L] [--chunks C]");
+    if (argc < 4) die("usage: s2v_multi_gpu shard|giant <in.bin> <out.bin> [--gpus N] [--iters K] [--levels L] [--chunks C] [--exchange referenced]");
     int have = 0;
     if (cudaGetDeviceCount(&have) != cudaSuccess || have == 0) die("no CUDA device");
     const int P = arg_int(argc, argv, "--gpus", 1);
@@ -375,6 +536,11 @@ int main(int argc, char** argv)
     const int iters = std::max(1, arg_int(argc, argv, "--iters", 3));
     if (!strcmp(argv[1], "shard")) return run_shard(argv[2], argv[3], P, iters);
     if (!strcmp(argv[1], "giant"))
-        return run_giant(argv[2], argv[3], P, std::max(1, arg_int(argc, argv, "--levels", 2)), arg_int(argc, argv, "--chunks", 4), iters);
+    {
+        bool referenced = false;
+        for (int i = 4; i + 1 < argc; ++i)
+            if (!strcmp(argv[i], "--exchange")) referenced = !strcmp(argv[i + 1], "referenced");
+        return run_giant(argv[2], argv[3], P, std::max(1, arg_int(argc, argv, "--levels", 2)), arg_int(argc, argv, "--chunks", 4), iters, referenced);
+    }
     die("the first argument must be shard or giant");
 }

@@ -194,9 +194,11 @@ def test_multi_gpu_host_program_shard_by_graph(cxx_bins, oracle_lib, tmp_path):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("exchange", ["allgather", "referenced"])
 @pytest.mark.parametrize("d,chunks", [(64, 3), (128, 1)])
-def test_multi_gpu_host_program_giant_graph(cxx_bins, oracle_lib, tmp_path, d, chunks):
-    """Row-partitioned single graph from the same C++ host: block-major H, one in-place all-gather per block and level."""
+def test_multi_gpu_host_program_giant_graph(cxx_bins, oracle_lib, tmp_path, d, chunks, exchange):
+    """Row-partitioned single graph from the same C++ host: block-major H with one in-place all-gather per block and
+    level, or (exchange = referenced) every GPU fetching only the rows it references through s2v_exchange_rows_f32."""
     from graphnn_b200.synth import LevelProblem
     p = synth.rmat_level(scale=12, edge_factor=8, d=d, seed=4)
     with open(tmp_path / "graph.bin", "wb") as f:
@@ -207,10 +209,13 @@ def test_multi_gpu_host_program_giant_graph(cxx_bins, oracle_lib, tmp_path, d, c
         f.write(np.ascontiguousarray(p.W, np.float32).tobytes())
     P = _gpus_for_test()
     r = subprocess.run([cxx_bins["s2v_multi_gpu"], "giant", str(tmp_path / "graph.bin"), str(tmp_path / "out.bin"), "--gpus", str(P),
-                        "--levels", "2", "--chunks", str(chunks), "--iters", "2"], capture_output=True, text=True, timeout=300)
+                        "--levels", "2", "--chunks", str(chunks), "--iters", "2"] + (["--exchange", "referenced"] if exchange == "referenced" else []),
+                       capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout + r.stderr
     got = np.fromfile(tmp_path / "out.bin", np.float32).reshape(p.n_rows, d)
     H = p.H
     for _ in range(2):
         H, _ = oracle_lib.level(LevelProblem(p.n_rows, p.n_src, p.row_ptr, p.col_idx, H, p.W, None), "oracle")
-    assert_close(got, H, f"giant graph on {P} GPU(s)", scale=max(1.0, float(np.abs(H).max())))
+    assert_close(got, H, f"giant graph on {P} GPU(s), exchange {exchange}", scale=max(1.0, float(np.abs(H).max())))
+    if exchange == "referenced":
+        assert "referenced_remote_rows" in r.stdout
