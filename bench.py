@@ -839,6 +839,7 @@ def run_case(args):
     mol_first   first level straight from the tags (product table + gather-sum) on 16,384 molecule-like graphs, d=128
     prot_first  the same on 2,048 protein-like graphs, d=64
     mol_tiles   tile kernel (projection + 4 levels + pooling) on 16,384 molecule-like graphs;  mol_tiles_small: 4,096 graphs
+    readout     readout (two layers + softmax / argmax) of 16,384 pooled embeddings, d=128, hidden=256, 2 classes
     mol_paths   whole forward pass (s2v_forward_f32) on 512 .. 16,384 molecule-like graphs through the per-level kernels
                 and through the tile kernel, one line per batch size"""
     import torch
@@ -877,7 +878,16 @@ def run_case(args):
     def up(a):
         return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
 
-    if args.case.startswith("er_d64"):
+    if args.case == "readout":
+        rng = np.random.default_rng(0)
+        G, d_, hid, C_ = 16384, 128, 256, 2
+        Yd = up(rng.standard_normal((G, d_), dtype=np.float32))
+        W1d, W2d = up(rng.standard_normal((d_, hid), dtype=np.float32) * 0.1), up(rng.standard_normal((hid, C_), dtype=np.float32) * 0.1)
+        lg, pr = torch.empty((G, C_), device=dev), torch.empty((G, C_), device=dev)
+        pd = torch.empty(G, dtype=torch.int32, device=dev)
+        launch = lambda: ctx.readout(Yd, W1d, W2d, lg, pr, pd, stream=st)
+        desc = f"readout: G={G} d={d_} hidden={hid} C={C_}"
+    elif args.case.startswith("er_d64"):
         full = args.case.endswith("full")
         p = synth.erdos_renyi_level(n=1 << (20 if full else 19), nnz=1 << (23 if full else 22), d=64)
         rp, ci, H, W, X = up(p.row_ptr), up(p.col_idx), up(p.H), up(p.W), up(p.X)
@@ -937,7 +947,7 @@ def main():
     ap.add_argument("--tiles", type=int, default=2, choices=[0, 1, 2],
                     help="S2V_OPT_GRAPH_TILES: 0 per-level kernels only, 1 whole-classifier tile kernel whenever the batch allows, "
                          "2 the library's default (tile kernel for batches of at most 160,000 nodes)")
-    ap.add_argument("--case", default=None, choices=["er_d64", "er_d64_full", "mol_d128", "prot_d64", "mol_first", "prot_first", "mol_tiles", "mol_tiles_small", "mol_paths"],
+    ap.add_argument("--case", default=None, choices=["er_d64", "er_d64_full", "mol_d128", "prot_d64", "mol_first", "prot_first", "readout", "mol_tiles", "mol_tiles_small", "mol_paths"],
                     help="run one small launch case (for profiler captures) instead of the benchmark")
     ap.add_argument("--launches", type=int, default=3)
     args = ap.parse_args()

@@ -156,6 +156,11 @@ int s2v_launch_level_tc(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int d, co
                         const int32_t* col_idx, const float* val, const float* H, const float* W, const float* X,
                         const float* table, const int32_t* x_index, int n_table, float* out);
 int s2v_launch_wait_selftest(s2v_ctx* ctx, cudaStream_t st);
+// readout (two layers + softmax / argmax) with the first layer on tcgen05 (readout_tc.cu): d in {64, 128},
+// hidden in {128, 256}, at most 8 classes, batches of at least 512 graphs
+bool s2v_readout_tc_supported(const s2v_ctx* ctx, int64_t G, int d, int hidden, int C);
+int s2v_launch_readout_tc(s2v_ctx* ctx, cudaStream_t st, int64_t G, int d, int hidden, int C, const float* Y, const float* W1,
+                          const float* W2, float* logits, float* probs, int32_t* pred);
 // first level from one-hot tags as a gather-sum over the product table ReLU(W_in) * W (level_first_table.cu);
 // d / 4 must be a power of two <= 32; P_scratch holds s2v_first_table_scratch_bytes(n_table, d)
 bool s2v_first_table_supported(int d);

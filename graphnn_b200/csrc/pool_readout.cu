@@ -450,6 +450,11 @@ int s2v_readout_f32(s2v_ctx* ctx, s2v_stream stream, int64_t num_graphs, int d, 
         return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "readout: bad shape");
     if (num_graphs == 0) return S2V_OK;
     if (!Y || !W1 || !W2 || !logits) return s2v_fail(ctx, S2V_ERR_INVALID_ARG, "readout: NULL pointer");
+    if (s2v_readout_tc_supported(ctx, num_graphs, d, hidden, num_class) && s2v_aligned16(Y)) {
+        // batches of hundreds of graphs and the widths of the path: first layer on the 5th-generation tensor cores
+        const int rc = s2v_launch_readout_tc(ctx, s2v_pick_stream(ctx, stream), num_graphs, d, hidden, num_class, Y, W1, W2, logits, probs, pred);
+        if (rc != S2V_ERR_UNSUPPORTED) return rc;
+    }
     const size_t smem4 = sizeof(float) * (size_t)TG4 * ((size_t)d + 4 + hidden + 4 + num_class);
     if (d % 8 == 0 && (hidden == 256 || hidden == 128) && smem4 <= 96 * 1024 && s2v_aligned16(Y) && num_graphs >= 256) {
         // batches of hundreds of graphs and the two hidden sizes of the path: first layer on the tensor cores

@@ -111,10 +111,12 @@ def test_pooling_and_readout_separately(gpu_ctx, oracle_lib):
         assert np.array_equal(pred.cpu().numpy(), logits.cpu().numpy().argmax(1))
 
 
-@pytest.mark.parametrize("G,d,hidden,C", [(2048, 128, 256, 2), (5000, 64, 128, 3), (2049, 128, 256, 2)])
+@pytest.mark.parametrize("G,d,hidden,C", [(2048, 128, 256, 2), (5000, 64, 128, 3), (2049, 128, 256, 2),
+                                          (148 * 128 * 2 + 77, 128, 256, 8),     # more tiles than SMs: a CTA takes several, 8 classes
+                                          (300, 128, 256, 2), (40000, 64, 256, 5)])
 def test_readout_large_batch(gpu_ctx, G, d, hidden, C):
-    """Readout on batches of thousands of graphs (several 32-graph tiles per CTA); the last tile is
-    ragged in two of the cases."""
+    """Readout on batches of hundreds to tens of thousands of graphs: from 512 graphs on the first layer runs on the
+    tcgen05 kernel (128-graph tiles, the last one ragged in most cases), below that on the mma.sync kernel."""
     rng = np.random.default_rng(G)
     Y = rng.standard_normal((G, d), dtype=np.float32) * 3.0
     W1 = rng.standard_normal((d, hidden), dtype=np.float32) * 0.1
