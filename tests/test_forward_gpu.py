@@ -113,10 +113,10 @@ def test_pooling_and_readout_separately(gpu_ctx, oracle_lib):
 
 @pytest.mark.parametrize("G,d,hidden,C", [(2048, 128, 256, 2), (5000, 64, 128, 3), (2049, 128, 256, 2),
                                           (148 * 128 * 2 + 77, 128, 256, 8),     # more tiles than SMs: a CTA takes several, 8 classes
-                                          (300, 128, 256, 2), (40000, 64, 256, 5)])
+                                          (300, 128, 256, 2), (40000, 64, 256, 5), (20011, 128, 128, 3)])
 def test_readout_large_batch(gpu_ctx, G, d, hidden, C):
-    """Readout on batches of hundreds to tens of thousands of graphs: from 512 graphs on the first layer runs on the
-    tcgen05 kernel (128-graph tiles, the last one ragged in most cases), below that on the mma.sync kernel."""
+    """Readout on batches of hundreds to tens of thousands of graphs: from 10,240 graphs on the first layer runs on
+    the tcgen05 kernel (128-graph tiles, the last one ragged), below that on the mma.sync kernel."""
     rng = np.random.default_rng(G)
     Y = rng.standard_normal((G, d), dtype=np.float32) * 3.0
     W1 = rng.standard_normal((d, hidden), dtype=np.float32) * 0.1

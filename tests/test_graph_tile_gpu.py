@@ -108,8 +108,8 @@ def test_tile_kernel_matches_oracle_on_molecules(oracle_lib):
 def test_tile_results_do_not_depend_on_the_packing():
     """A graph's rows never mix with another graph's in the arithmetic, so the same graphs packed into
     different tiles (a sub-batch starts its own packing) give bit-identical embeddings and logits."""
-    b = synth.molecules_16k(seed=3, num_graphs=1800)      # (a third of them is still above the 512 graphs from which the
-    full = forward(b)                                      # readout takes its tcgen05 form: the same kernels in both runs)
+    b = synth.molecules_16k(seed=3, num_graphs=1800)      # (both runs are below the batch size from which the readout
+    full = forward(b)                                      # takes its tcgen05 form: the same kernels in both)
     lo, hi = synth.shard_bounds(b.nodes_per_graph, 3)[1]
     part = forward(b.shard(1, 3))
     off = b.graph_offsets()

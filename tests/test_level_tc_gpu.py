@@ -204,3 +204,23 @@ def test_reserved_sms_change_the_grid_not_the_result(tc_ctx):
     finally:
         tc_ctx.set_option(tc_ctx.OPT_RESERVED_SMS, 0)
     assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("G,d,hidden,C", [(513, 128, 256, 2), (2049, 64, 128, 3), (700, 64, 256, 8)])
+def test_tc_readout_small_batches(tc_ctx, G, d, hidden, C):
+    """The tcgen05 readout on batches below the size from which the library picks it by itself (the context forces
+    the tensor-core kernels): ragged last tile, both hidden widths, both input widths, up to 8 classes."""
+    rng = np.random.default_rng(G)
+    Y = rng.standard_normal((G, d), dtype=np.float32) * 3.0
+    W1 = rng.standard_normal((d, hidden), dtype=np.float32) * 0.1
+    W2 = rng.standard_normal((hidden, C), dtype=np.float32) * 0.1
+    logits = torch.full((G, C), float("nan"), device="cuda")
+    probs = torch.empty((G, C), device="cuda")
+    pred = torch.empty(G, dtype=torch.int32, device="cuda")
+    tc_ctx.readout(dev(Y), dev(W1), dev(W2), logits, probs, pred)
+    tc_ctx.synchronize()
+    lg = np.maximum(Y.astype(np.float64) @ W1.astype(np.float64), 0) @ W2.astype(np.float64)
+    assert_close(logits.cpu().numpy(), lg, "tcgen05 readout logits", scale=8)
+    e = np.exp(lg - lg.max(1, keepdims=True))
+    assert_close(probs.cpu().numpy(), e / e.sum(1, keepdims=True), "tcgen05 readout probs", scale=8)
+    assert np.array_equal(pred.cpu().numpy(), logits.cpu().numpy().argmax(1))
