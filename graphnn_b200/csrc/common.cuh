@@ -157,7 +157,7 @@ int s2v_launch_level_tc(s2v_ctx* ctx, cudaStream_t st, int64_t n_rows, int d, co
                         const float* table, const int32_t* x_index, int n_table, float* out);
 int s2v_launch_wait_selftest(s2v_ctx* ctx, cudaStream_t st);
 // readout (two layers + softmax / argmax) with the first layer on tcgen05 (readout_tc.cu): d in {64, 128},
-// hidden in {128, 256}, at most 8 classes, batches of at least 10,240 graphs (512 when S2V_OPT_LEVEL_TC = 2)
+// hidden in {128, 256}, at most 8 classes, batches of at least 6,144 graphs (512 when S2V_OPT_LEVEL_TC = 2)
 bool s2v_readout_tc_supported(const s2v_ctx* ctx, int64_t G, int d, int hidden, int C);
 int s2v_launch_readout_tc(s2v_ctx* ctx, cudaStream_t st, int64_t G, int d, int hidden, int C, const float* Y, const float* W1,
                           const float* W2, float* logits, float* probs, int32_t* pred);

@@ -228,8 +228,9 @@ readout_tc_kernel(int64_t G, int d, int C, const float* __restrict__ Y, const fl
 bool s2v_readout_tc_supported(const s2v_ctx* ctx, int64_t G, int d, int hidden, int C)
 {
     // A launch lasts at least the latency of one tile (about 23 us), which the mma.sync form (32-graph tiles, four CTAs
-    // per SM) undercuts up to roughly ten thousand graphs (0.019 - 0.021 ms at 2,048 - 4,096 graphs, 0.039 ms at 16,384).
-    const int64_t min_graphs = ctx->tc_mode == 2 ? 512 : 10240;
+    // per SM) undercuts on small batches: 0.019 - 0.021 ms at 2,048 - 4,096 graphs, but 0.033 ms at 8,192 and 0.039 ms
+    // at 16,384.
+    const int64_t min_graphs = ctx->tc_mode == 2 ? 512 : 6144;
     return ctx->tc_mode != 0 && G >= min_graphs && (d == 64 || d == 128) && (hidden == 128 || hidden == 256) && C >= 1 && C <= RT_MAX_C &&
            RtCfg<256>::SMEM_BYTES <= ctx->smem_optin;
 }

@@ -115,7 +115,7 @@ def test_pooling_and_readout_separately(gpu_ctx, oracle_lib):
                                           (148 * 128 * 2 + 77, 128, 256, 8),     # more tiles than SMs: a CTA takes several, 8 classes
                                           (300, 128, 256, 2), (40000, 64, 256, 5), (20011, 128, 128, 3)])
 def test_readout_large_batch(gpu_ctx, G, d, hidden, C):
-    """Readout on batches of hundreds to tens of thousands of graphs: from 10,240 graphs on the first layer runs on
+    """Readout on batches of hundreds to tens of thousands of graphs: from 6,144 graphs on the first layer runs on
     the tcgen05 kernel (128-graph tiles, the last one ragged), below that on the mma.sync kernel."""
     rng = np.random.default_rng(G)
     Y = rng.standard_normal((G, d), dtype=np.float32) * 3.0
